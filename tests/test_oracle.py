@@ -1,0 +1,174 @@
+"""Pin the CPU oracles (numpy and C) to vectors produced by the reference.
+
+The ``.npz`` files under tests/golden were written by running the reference's
+own packer, CPU unpacker and (through Triton's interpreter) GEMV / dot
+kernels; see tests/golden/make_golden.py.
+"""
+import numpy as np
+import pytest
+
+from oracle import feather_oracle as O
+from tests.golden_inputs import DOT_CASES, GEMV_CASES, dot_case, gemv_case, sample_f32
+
+MODES = ("E5M2", "E4M3")
+IMPLS = ("numpy", "c")
+
+
+def _pack(impl, c_oracle, x, mode):
+    return O.pack_fp8_ndarray(x, mode) if impl == "numpy" else c_oracle.pack(x, mode)
+
+
+def _same_floats(a, b):
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    nan = np.isnan(a)
+    return np.array_equal(nan, np.isnan(b)) and np.array_equal(
+        a.view(np.uint32)[~nan], b.view(np.uint32)[~nan])
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("mode", MODES)
+def test_encode_every_fp16_pattern(golden, c_oracle, impl, mode):
+    h = np.arange(65536, dtype=np.uint16).view(np.float16)
+    got = _pack(impl, c_oracle, h, mode).view(np.uint8)
+    assert np.array_equal(got, golden("encode")[f"fp16_all_{mode}"])
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_e5m2_closed_form_agrees(golden, mode):
+    if mode != "E5M2":
+        pytest.skip("closed form exists for E5M2 only")
+    got = O.encode_e5m2_from_fp16_bits(np.arange(65536, dtype=np.uint16))
+    assert np.array_equal(got, golden("encode")["fp16_all_E5M2"])
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("kind,seed", [("bits", 11), ("lognormal", 12)])
+def test_encode_fp32_samples(golden, c_oracle, impl, mode, kind, seed):
+    x = sample_f32(kind, 131072, seed)
+    got = _pack(impl, c_oracle, x, mode).view(np.uint8)
+    assert np.array_equal(got, golden("encode")[f"fp32_{kind}_{mode}"])
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("mode", MODES)
+def test_encode_fp32_edges(golden, c_oracle, impl, mode):
+    g = golden("encode")
+    x = g["fp32_edge_input_bits"].view(np.float32)
+    got = _pack(impl, c_oracle, x, mode).view(np.uint8)[: x.size]
+    assert np.array_equal(got, g[f"fp32_edge_{mode}"])
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("mode", MODES)
+def test_pack_layout_ragged_and_2d(golden, c_oracle, impl, mode):
+    g = golden("encode")
+    t = sample_f32("lognormal", 31, 13).astype(np.float16)
+    assert np.array_equal(_pack(impl, c_oracle, t, mode), g[f"ragged31_{mode}"])
+    assert np.array_equal(_pack(impl, c_oracle, t[:28].reshape(7, 4), mode), g[f"matrix7x4_{mode}"])
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("mode", MODES)
+def test_decode_tables(golden, c_oracle, impl, mode):
+    g = golden("decode")
+    tab = (O if impl == "numpy" else c_oracle).decode_table
+    # The vector lane holds the code of 1.0 and the other lanes are zero, so the
+    # reference kernel returned decode(code) * 1 + 0 + 0 + 0 (which maps -0 to +0).
+    with np.errstate(invalid="ignore"):
+        expect = tab(mode, "kernel") * np.float32(1.0) + np.float32(0.0)
+    for lane in range(4):
+        assert _same_floats(expect, g[f"kernel_{mode}_lane{lane}"])
+    assert _same_floats(tab(mode, "ieee"), g[f"ieee_{mode}"])
+
+
+def test_e4m3_kernel_decode_differs_from_ieee_on_16_codes():
+    k, i = O.decode_table("E4M3", "kernel"), O.decode_table("E4M3", "ieee")
+    differ = [c for c in range(256) if not _same_floats(k[c:c + 1], i[c:c + 1])]
+    assert differ == list(range(1, 8)) + [0x7F] + list(range(0x81, 0x88)) + [0xFF]
+    assert k[0x7F] == 480.0 and k[0xFF] == -480.0 and k[0x01] == 2.0 ** -17
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("mode", MODES)
+def test_gemv_docstring_example(golden, c_oracle, impl, mode):
+    a = np.array([[1, 1, -2, 0], [-3, -3, -2, -3], [0, 1, 1, -2], [2, 0, -1, 2]], dtype=np.float16)
+    b = np.array([2, 2, -1, 2], dtype=np.float16)
+    gemv = O.gemv if impl == "numpy" else c_oracle.gemv
+    y = gemv(_pack(impl, c_oracle, a, mode), _pack(impl, c_oracle, b, mode), (4, 4), mode)
+    assert np.array_equal(y, np.array([6, -16, -3, 9], dtype=np.float32))
+    assert np.array_equal(y, golden("gemv")[f"doc_{mode}"])
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("case", sorted(GEMV_CASES))
+def test_gemv_matches_reference_kernel(golden, c_oracle, impl, mode, case):
+    g = golden("gemv")
+    A, v = gemv_case(case)
+    mw, vw = _pack(impl, c_oracle, A, mode), _pack(impl, c_oracle, v, mode)
+    assert np.array_equal(mw, g[f"{case}_{mode}_m"])  # packed bytes bit-exact
+    assert np.array_equal(vw, g[f"{case}_{mode}_v"])
+    gemv = O.gemv if impl == "numpy" else c_oracle.gemv
+    y = gemv(mw, vw, A.shape, mode)
+    ref = g[f"{case}_{mode}_out"]
+    if case.startswith("int"):
+        assert np.array_equal(y, ref)  # integer data: every order is exact
+        assert np.array_equal(y, A.astype(np.float32) @ v.astype(np.float32))
+    else:
+        # tolerance from the north star: max relative (scale-normalised) 1e-5
+        assert O.normalised_error(y, ref) < 1e-5
+        assert O.normalised_error(gemv(mw, vw, A.shape, mode, acc="f64"), ref) < 1e-5
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("mode", MODES)
+def test_gemv_raw_bits_nonfinite_pattern(golden, c_oracle, impl, mode):
+    """Random words: inf/NaN codes meet every code.  Non-finite outputs must
+    agree in class; finite ones within tolerance."""
+    g = golden("gemv")
+    gemv = O.gemv if impl == "numpy" else c_oracle.gemv
+    y = gemv(g["rawbits_m"], g["rawbits_v"], (8, 2048), mode)
+    ref = g[f"rawbits_{mode}_out"]
+    assert np.array_equal(np.isnan(y), np.isnan(ref))
+    assert np.array_equal(np.isinf(y), np.isinf(ref))
+    fin = np.isfinite(ref)
+    if fin.any():
+        assert O.normalised_error(y[fin], ref[fin]) < 1e-5
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_dot_matches_reference_kernel(golden, c_oracle, impl):
+    g = golden("dot")
+    dot = O.dot if impl == "numpy" else c_oracle.dot
+    a = _pack(impl, c_oracle, np.array([2, 0, -3, 1], dtype=np.float16), "E5M2")
+    b = _pack(impl, c_oracle, np.array([-1, 0, -3, 1], dtype=np.float16), "E5M2")
+    assert dot(a, b) == 8.0 == g["doc"]
+    for n, seed in DOT_CASES:
+        x1, x2 = dot_case(n, seed)
+        a, b = _pack(impl, c_oracle, x1, "E5M2"), _pack(impl, c_oracle, x2, "E5M2")
+        sums = np.array([a.astype(np.uint64).sum(), b.astype(np.uint64).sum()], dtype=np.uint64)
+        assert np.array_equal(sums, g[f"n{n}_wordsum"])
+        if f"n{n}_a" in g:
+            assert np.array_equal(a, g[f"n{n}_a"]) and np.array_equal(b, g[f"n{n}_b"])
+        ref = float(g[f"n{n}_out"])
+        # scale for a dot product: sum of |products|
+        scale = float(np.abs(O.unpack(a) * O.unpack(b)).sum())
+        assert abs(float(dot(a, b)) - ref) / scale < 1e-5
+        assert abs(float(dot(a, b, acc="f64")) - ref) / scale < 1e-5
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_numpy_and_c_oracles_agree_bitwise(c_oracle, mode):
+    rng = np.random.default_rng(5)
+    A = rng.standard_normal((19, 4104)).astype(np.float16)
+    v = rng.standard_normal(4104).astype(np.float16)
+    mw, vw = O.pack_fp8_ndarray(A, mode), O.pack_fp8_ndarray(v, mode)
+    assert np.array_equal(O.gemv(mw, vw, A.shape, mode), c_oracle.gemv(mw, vw, A.shape, mode))
+    assert O.dot(mw[:5000], mw[5000:10000], mode) == c_oracle.dot(mw[:5000], mw[5000:10000], mode)
+    assert np.array_equal(O.unpack(mw, mode), c_oracle.unpack(mw, mode))
+
+
+def test_unknown_mode_raises():
+    with pytest.raises(NotImplementedError):
+        O.pack_fp8_ndarray(np.zeros(4, np.float16), "E3M4")
