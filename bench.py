@@ -1,0 +1,477 @@
+#!/usr/bin/env python
+"""Benchmark of the packed-FP8 GEMV path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Metric: achieved HBM GB/s of the packed-FP8 GEMV (algorithmic bytes = packed
+matrix + packed vector + FP32 output, divided by time), whole job.
+
+* N = 1: the single-GPU E5M2 GEMV, 16384 x 16384, seed 1 (256 MiB packed).  A
+  step is one GEMV call; four distinct packed matrices are rotated so that no
+  step finds its matrix in the 126 MB L2.
+* N > 1 (launched by torch.distributed.run, one rank per GPU): the row-sharded
+  E5M2 GEMV, 65536 x 65536 (4 GiB packed), rows split in contiguous blocks,
+  vector replicated, output slices exchanged with an NCCL all-gather.  A step
+  is local GEMV + all-gather; time is the max over ranks.  Total work is fixed
+  ("strong" scaling).
+* --impl reference: the reference's CPU path (decode with the kernel bit
+  semantics + FP32 matvec, the C restatement in oracle/) on the host cores.
+
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "packed_fp8_gemv_hbm_gbps"
+UNIT = "GB/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes per launch of gemv_stream_kernel at 16384 x 16384 from an ncu
+# capture (dram__bytes_read.sum + dram__bytes_write.sum, profiles/); None until
+# a capture exists.
+NCU_TRAFFIC_BYTES_16384 = None
+
+
+def gemv_bytes(M: int, N: int) -> int:
+    """Algorithmic bytes of one GEMV: packed matrix + packed vector + output."""
+    return M * N + 4 * ((N + 3) // 4) + 4 * M
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Poll SM clock and throttle reasons through NVML while the timed region
+    runs (read-only queries)."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _once(self):
+        nv = self._nv
+        self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+        r = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40,
+                 "sw_thermal_slowdown": 0x20, "hw_power_brake_slowdown": 0x80,
+                 "applications_clocks_setting": 0x2}
+        for k, bit in names.items():
+            if r & bit:
+                self.reasons.add(k)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self._once()
+            except Exception:
+                break
+            self._stop.wait(0.002)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        if self._nv is not None and not self.samples:
+            try:
+                self._once()
+            except Exception:
+                pass
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except Exception:
+            return local
+    return local
+
+
+# ------------------------------------------------------------------ CPU arm --
+def cpu_gemv_gbps(M: int, N: int, mode: str, budget_s: float, seed: int = 1):
+    """Time the C oracle's GEMV (reference CPU path: kernel-semantics decode +
+    FP32 matvec) on all host threads over a bounded row sample of the M x N
+    workload.  Returns (GB/s, threads, description, seconds per pass)."""
+    import numpy as np
+
+    from oracle import c_oracle as C
+    C.build()
+    threads = C.num_threads()
+    rng = np.random.default_rng(seed)
+    rows = min(M, 2048)
+    A = rng.standard_normal((rows, N)).astype(np.float16)
+    v = rng.standard_normal(N).astype(np.float16)
+    t0 = time.perf_counter()
+    mw = C.pack(A, mode)
+    pack_s = time.perf_counter() - t0
+    vw = C.pack(v, mode)
+    C.gemv(mw, vw, (rows, N), mode)  # warm
+    t0 = time.perf_counter()
+    C.gemv(mw, vw, (rows, N), mode)
+    t_probe = time.perf_counter() - t0
+    # a pass over `rows` rows costs t_probe; repeat passes to fill the budget
+    reps = max(3, min(200, int(budget_s / max(t_probe, 1e-6))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        C.gemv(mw, vw, (rows, N), mode)
+    dt = (time.perf_counter() - t0) / reps
+    gbps = gemv_bytes(rows, N) / dt / 1e9
+    sample = (f"{rows} of {M} rows x {N} cols {mode}, {reps} passes, C restatement of the "
+              f"reference decode + FP32 matvec (OpenMP); packing those rows took {pack_s:.3f} s "
+              f"({rows * N / pack_s / 1e9:.2f} Gelem/s)")
+    return gbps, threads, sample, dt
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    M, N = (16384, 16384) if args.gpus == 1 else (65536, 65536)
+    workload = ("gemv_e5m2_16384x16384" if args.gpus == 1 else "row_sharded_gemv_e5m2_65536x65536")
+    import numpy as np
+
+    from oracle import c_oracle as C
+    C.build()
+    threads = C.num_threads()
+    rng = np.random.default_rng(1)
+    # bounded sample: rows chosen so that warmup + steps end within ~2 minutes
+    rows = min(M, 4096)
+    A = rng.standard_normal((rows, N)).astype(np.float16)
+    mw, vw = C.pack(A, "E5M2"), C.pack(rng.standard_normal(N).astype(np.float16), "E5M2")
+    t0 = time.perf_counter()
+    C.gemv(mw, vw, (rows, N), "E5M2")
+    t1 = time.perf_counter() - t0
+    total = (args.steps + args.warmup) * t1
+    if total > 120.0:
+        rows = max(64, int(rows * 120.0 / total))
+        mw = mw[: rows * (N // 4)]
+    for _ in range(args.warmup):
+        C.gemv(mw, vw, (rows, N), "E5M2")
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        C.gemv(mw, vw, (rows, N), "E5M2")
+    dt = (time.perf_counter() - t0) / max(args.steps, 1)
+    gbps = gemv_bytes(rows, N) / dt / 1e9
+    sample = f"{rows} of {M} rows x {N} cols per step, all host threads"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(gbps, 3), "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(dt * 1e3, 4), "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": workload, "M": M, "N": N, "mode": "E5M2"},
+        "cpu_baseline": {"value": round(gbps, 3), "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(gbps, 3), "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------ GPU arm --
+def time_calls(torch, fn, n_iter: int, warmup: int) -> float:
+    """Average milliseconds per call with CUDA events on the current stream."""
+    for _ in range(warmup):
+        fn()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(n_iter):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / n_iter
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import feather_b200 as fb
+    from feather_b200.sharded import RowShardedGemv
+
+    fb._lib.load()  # fail loudly if the CUDA library is missing
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    K, W = args.steps, args.warmup
+    peak, peak_kind = measured_peak()
+    mode = "E5M2"
+    gen = torch.Generator(device=dev)
+
+    def make_packed(rows: int, cols: int, seed: int, mode: str, dtype=torch.float16):
+        gen.manual_seed(seed)
+        out = torch.empty(rows * (cols // 4), dtype=torch.int32, device=dev).view(torch.uint32)
+        blk = max(1, min(rows, (1 << 28) // cols))
+        for r0 in range(0, rows, blk):
+            r1 = min(rows, r0 + blk)
+            a = torch.randn(r1 - r0, cols, device=dev, generator=gen, dtype=dtype)
+            out[r0 * (cols // 4): r1 * (cols // 4)] = fb.pack_fp8_tensor(a, mode)
+        return out
+
+    extra = {}
+    if world == 1:
+        M = N = 16384
+        workload = "gemv_e5m2_16384x16384"
+        n_buf = 4
+        mats = [make_packed(M, N, 1 + 100 * i, mode) for i in range(n_buf)]
+        gen.manual_seed(1)
+        v_f16 = torch.randn(N, device=dev, generator=gen, dtype=torch.float16)
+        vw = fb.pack_fp8_tensor(v_f16, mode)
+        out = torch.empty(M, dtype=torch.float32, device=dev)
+        step_bytes = gemv_bytes(M, N)
+        state = {"i": 0}
+
+        def step():
+            fb.gemv_fp8_acc_fp32_gpu(mats[state["i"] % n_buf], vw, (M, N), mode, out=out)
+            state["i"] += 1
+        l2_note = f"{n_buf} distinct 256 MiB packed matrices rotated (each larger than L2)"
+    else:
+        M = N = 65536
+        workload = "row_sharded_gemv_e5m2_65536x65536"
+        rows = M // world
+        m_local = make_packed(rows, N, 5 + rank, mode)
+        gen.manual_seed(5)
+        vw = fb.pack_fp8_tensor(torch.randn(N, device=dev, generator=gen, dtype=torch.float16), mode)
+        op = RowShardedGemv(m_local, (M, N), mode)
+        step_bytes = gemv_bytes(M, N)
+
+        def step():
+            op(vw)
+        l2_note = f"per-rank block {rows * N >> 20} MiB, larger than L2"
+
+    # ---- the timed region: W warm-up steps, then exactly K steps -----------
+    for _ in range(W):
+        step()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+        start.record()
+        for _ in range(K):
+            step()
+        end.record()
+        torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms_total = start.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_per_step = ms_total / K
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- kernel-only duration for the roofline (local GEMV kernel) ---------
+    if world == 1:
+        kern_ms = ms_per_step
+        kern_bytes = step_bytes
+        kern_name = "gemv_stream_kernel<E5M2>"
+    else:
+        kern_ms = time_calls(torch, lambda: op.local(vw), max(20, K), 5)
+        kern_bytes = gemv_bytes(M // world, N)
+        kern_name = "gemv_stream_kernel<E5M2> (per-rank block)"
+    achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": kern_name, "achieved": round(achieved, 1),
+                "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+                "frac": round(achieved / peak, 4),
+                "frac_of_nominal_8TBs": round(achieved / NOMINAL_HBM_GBS, 4),
+                "algorithmic_bytes": kern_bytes, "us_per_launch": round(kern_ms * 1e3, 3),
+                "traffic": NCU_TRAFFIC_BYTES_16384 if world == 1 else None}
+
+    # ---- end to end: host buffers in, host result out, every step ----------
+    if world == 1:
+        m_host = mats[0].view(torch.int32).cpu().pin_memory()
+        v_host = vw.view(torch.int32).cpu().pin_memory()
+        out_host = torch.empty(M, dtype=torch.float32).pin_memory()
+        m_dev = torch.empty_like(mats[0].view(torch.int32))
+        v_dev = torch.empty_like(vw.view(torch.int32))
+
+        def e2e_step():
+            m_dev.copy_(m_host, non_blocking=True)
+            v_dev.copy_(v_host, non_blocking=True)
+            y = fb.gemv(m_dev, v_dev, original_shape=(M, N), mode=mode)
+            out_host.copy_(y, non_blocking=True)
+        h2d, d2h = m_host.numel() * 4 + v_host.numel() * 4, M * 4
+        e2e_iters = max(3, min(K, 20))
+    else:
+        rows = M // world
+        m_host = m_local.view(torch.int32).cpu().pin_memory()
+        v_host = vw.view(torch.int32).cpu().pin_memory()
+        out_host = torch.empty(M, dtype=torch.float32).pin_memory()
+        v_dev = torch.empty_like(vw.view(torch.int32))
+
+        def e2e_step():
+            op.m_local.view(torch.int32).copy_(m_host, non_blocking=True)
+            v_dev.copy_(v_host, non_blocking=True)
+            out_host.copy_(op(v_dev), non_blocking=True)
+        h2d, d2h = m_host.numel() * 4 + v_host.numel() * 4, M * 4
+        e2e_iters = max(2, min(K, 5))
+    e2e_ms = time_calls(torch, e2e_step, e2e_iters, 1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e = {"value": round(step_bytes / (e2e_ms * 1e-3) / 1e9, 3), "unit": UNIT,
+           "ms_per_step": round(e2e_ms, 4), "h2d_bytes_per_step": h2d * world,
+           "d2h_bytes_per_step": d2h * world,
+           "path": "pinned host packed matrix+vector -> H2D -> feather.gemv -> D2H of the FP32 result"}
+
+    # ---- other kernels of the path (single GPU only; outside the timed region)
+    if world == 1:
+        del m_host, m_dev
+        n_it = max(20, min(K, 200))
+        # E4M3 GEMV on the configuration-3 style data, same shape
+        gen.manual_seed(4)
+        m4 = []
+        for i in range(n_buf):
+            x = 4.0 * torch.randn(M, N, device=dev, generator=gen)
+            u = torch.rand(M, N, device=dev, generator=gen)
+            x = torch.where(u < 0.05, torch.copysign(2.0 ** -9 + u * 20 * (2.0 ** -6 - 2.0 ** -9), x),
+                            torch.where(u < 0.10, torch.copysign(448.0 + (u - 0.05) * 20 * 552.0, x), x))
+            m4.append(fb.pack_fp8_tensor(x, "E4M3"))
+            del x, u
+        v4 = fb.pack_fp8_tensor(v_f16, "E4M3")
+        st = {"i": 0}
+
+        def step4():
+            fb.gemv_fp8_acc_fp32_gpu(m4[st["i"] % n_buf], v4, (M, N), "E4M3", out=out)
+            st["i"] += 1
+        ms4 = time_calls(torch, step4, n_it, 10)
+        extra["gemv_e4m3_16384x16384"] = {
+            "us_per_call": round(ms4 * 1e3, 3), "GB/s": round(step_bytes / ms4 / 1e6, 1),
+            "frac_of_peak": round(step_bytes / ms4 / 1e6 / peak, 4)}
+        for shape in ((8192, 8192), (16384, 8192)):
+            mm, nn = shape
+            views = [m4[i][: mm * nn // 4] for i in range(n_buf)]
+            vv = v4[: nn // 4]
+            o2 = out[:mm]
+            st2 = {"i": 0}
+
+            def step_s():
+                fb.gemv_fp8_acc_fp32_gpu(views[st2["i"] % n_buf], vv, shape, "E4M3", out=o2)
+                st2["i"] += 1
+            ms_s = time_calls(torch, step_s, n_it, 10)
+            b = gemv_bytes(mm, nn)
+            extra[f"gemv_e4m3_{mm}x{nn}"] = {"us_per_call": round(ms_s * 1e3, 3),
+                                             "GB/s": round(b / ms_s / 1e6, 1),
+                                             "frac_of_peak": round(b / ms_s / 1e6 / peak, 4)}
+        del m4
+        # dot on two 2^26-element E5M2 vectors: reuse the packed matrices as operands
+        n_words = 1 << 24
+        ops = [(mats[i][:n_words], mats[i][n_words:2 * n_words]) for i in range(n_buf)]
+        st3 = {"i": 0}
+
+        def step_d():
+            a, b = ops[st3["i"] % n_buf]
+            fb.dot_fp8_acc_fp32_gpu(a, b, "E5M2")
+            st3["i"] += 1
+        ms_d = time_calls(torch, step_d, n_it, 10)
+        db = 2 * n_words * 4 + 4
+        extra["dot_e5m2_2pow26"] = {"us_per_call": round(ms_d * 1e3, 3),
+                                    "GB/s": round(db / ms_d / 1e6, 1),
+                                    "frac_of_peak": round(db / ms_d / 1e6 / peak, 4)}
+        # encoder: fp16 16384^2 -> E5M2 (reads 2 B, writes 1 B per element)
+        gen.manual_seed(9)
+        src = torch.randn(M, N, device=dev, generator=gen, dtype=torch.float16)
+        ms_e = time_calls(torch, lambda: fb.pack_fp8_tensor(src, "E5M2"), 20, 3)
+        extra["encode_fp16_to_e5m2_16384x16384"] = {
+            "us_per_call": round(ms_e * 1e3, 3), "GB/s": round(3 * M * N / ms_e / 1e6, 1),
+            "frac_of_peak": round(3 * M * N / ms_e / 1e6 / peak, 4)}
+        del src
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    # ---- CPU baseline beside it (rank 0, bounded sample) --------------------
+    cpu = None
+    if world == 1:
+        gbps, threads, sample, _ = cpu_gemv_gbps(M, N, mode, budget_s=12.0)
+        cpu = {"value": round(gbps, 3), "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": sample}
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": round(ms_per_step, 6), "higher_is_better": True,
+        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": workload, "M": M, "N": N, "mode": mode,
+                   "bytes_per_step": step_bytes, "l2": l2_note,
+                   "parallelism": f"rows/{world}" if world > 1 else "1 GPU"},
+        "us_per_call": round(ms_per_step * 1e3, 3),
+        "frac_of_nominal_8TBs": round(value / world / NOMINAL_HBM_GBS, 4),
+        "roofline": roofline, "e2e": e2e, "gpu_launches": K,
+        "clocks": clocks.summary(), "extra": extra,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    args = ap.parse_args()
+    if args.steps < 1 or args.warmup < 0:
+        raise SystemExit("--steps must be >= 1 and --warmup >= 0")
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

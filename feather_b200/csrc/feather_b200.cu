@@ -1,0 +1,391 @@
+// C ABI of libfeather_b200.so (declared in include/feather_b200.h): argument
+// checks, launch geometry and the encode / decode kernels.  The GEMV and dot
+// kernels live in gemv_kernels.cuh / dot_kernels.cuh.
+#include <cuda_runtime.h>
+
+#include <atomic>
+
+#include "../../include/feather_b200.h"
+#include "dot_kernels.cuh"
+#include "fp8_codec.cuh"
+#include "gemv_kernels.cuh"
+#include "gemv_ring.cuh"
+
+namespace feather {
+
+// ------------------------------------------------------------ encode -------
+// One thread per 16 elements: 128-bit loads of the source, one 128-bit store
+// of sixteen codes (feather/packers/fp8.py:123-134: element 4k + i goes to
+// byte i of word k, i.e. the packed buffer is the code stream in element
+// order).
+template <int MODE>
+__device__ __forceinline__ uint32_t pack4(float a, float b, float c, float d) {
+    return encode_f32<MODE>(a) | (encode_f32<MODE>(b) << 8) | (encode_f32<MODE>(c) << 16) |
+           (encode_f32<MODE>(d) << 24);
+}
+
+// fp16 -> fp32 widening is exact, but the hardware conversion may hand back a
+// canonical NaN; the sign is therefore taken from the fp16 bits themselves
+// (the reference keeps the sign of a NaN: 0xFE / 0xFF codes).
+template <int MODE>
+__device__ __forceinline__ uint32_t encode_h(uint32_t h16) {
+    const float x = __half2float(__ushort_as_half((unsigned short)h16));
+    const uint32_t u = (__float_as_uint(x) & 0x7FFFFFFFu) | ((h16 & 0x8000u) << 16);
+    return MODE == kE5M2 ? encode_e5m2(u) : encode_e4m3(u);
+}
+
+template <int MODE>
+__device__ __forceinline__ uint32_t pack4_h(uint2 h) {  // four fp16 values
+    return encode_h<MODE>(h.x & 0xFFFFu) | (encode_h<MODE>(h.x >> 16) << 8) |
+           (encode_h<MODE>(h.y & 0xFFFFu) << 16) | (encode_h<MODE>(h.y >> 16) << 24);
+}
+
+template <int MODE, bool F32>
+__global__ void __launch_bounds__(256)
+encode_vec_kernel(const void* __restrict__ src, uint4* __restrict__ dst, long long n_groups) {
+    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= n_groups) return;
+    uint4 o;
+    if (F32) {
+        const float4* s = reinterpret_cast<const float4*>(src) + g * 4;
+        const float4 a = __ldcs(s), b = __ldcs(s + 1), c = __ldcs(s + 2), d = __ldcs(s + 3);
+        o.x = pack4<MODE>(a.x, a.y, a.z, a.w);
+        o.y = pack4<MODE>(b.x, b.y, b.z, b.w);
+        o.z = pack4<MODE>(c.x, c.y, c.z, c.w);
+        o.w = pack4<MODE>(d.x, d.y, d.z, d.w);
+    } else {
+        const uint4* s = reinterpret_cast<const uint4*>(src) + g * 2;
+        const uint4 a = __ldcs(s), b = __ldcs(s + 1);
+        o.x = pack4_h<MODE>(make_uint2(a.x, a.y));
+        o.y = pack4_h<MODE>(make_uint2(a.z, a.w));
+        o.z = pack4_h<MODE>(make_uint2(b.x, b.y));
+        o.w = pack4_h<MODE>(make_uint2(b.z, b.w));
+    }
+    dst[g] = o;
+}
+
+// One thread per word, element loads: unaligned buffers and the ragged tail
+// (elements past n_elems encode as code 0, fp8.py:200-204).
+template <int MODE, bool F32>
+__global__ void __launch_bounds__(256)
+encode_word_kernel(const void* __restrict__ src, uint32_t* __restrict__ dst, long long first_word,
+                   long long n_words, long long n_elems) {
+    const long long w = first_word + (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (w >= n_words) return;
+    uint32_t code[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const long long e = w * 4 + i;
+        if (e >= n_elems) code[i] = 0u;
+        else if (F32) code[i] = encode_f32<MODE>(reinterpret_cast<const float*>(src)[e]);
+        else code[i] = encode_h<MODE>(reinterpret_cast<const unsigned short*>(src)[e]);
+    }
+    dst[w] = code[0] | (code[1] << 8) | (code[2] << 16) | (code[3] << 24);
+}
+
+// ------------------------------------------------------------ decode -------
+template <int MODE, bool IEEE>
+__device__ __forceinline__ float4 decode4(uint32_t w) {
+    if (MODE == kE4M3 && IEEE)
+        return make_float4(decode_e4m3_ieee(w & 0xFF), decode_e4m3_ieee((w >> 8) & 0xFF),
+                           decode_e4m3_ieee((w >> 16) & 0xFF), decode_e4m3_ieee(w >> 24));
+    return decode_word_ordered<MODE>(w);  // E5M2: both semantics coincide
+}
+
+template <int MODE, bool IEEE>
+__global__ void __launch_bounds__(256)
+decode_kernel(const uint32_t* __restrict__ src, float* __restrict__ dst, long long n_elems) {
+    const long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long e = w * 4;
+    if (e >= n_elems) return;
+    const float4 f = decode4<MODE, IEEE>(__ldg(src + w));
+    if (e + 4 <= n_elems && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        reinterpret_cast<float4*>(dst)[w] = f;
+    } else {
+        const float x[4] = {f.x, f.y, f.z, f.w};
+        for (int i = 0; i < 4 && e + i < n_elems; ++i) dst[e + i] = x[i];
+    }
+}
+
+// ------------------------------------------------------------ host side ----
+struct DeviceInfo {
+    std::atomic<int> state{0};  // 0 unknown, 1 ok, -1 wrong architecture
+    int sm_count = 0;
+};
+static DeviceInfo g_dev[64];
+
+static int device_info(const DeviceInfo** info) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FEATHER_ERR_LAUNCH;
+    DeviceInfo& d = g_dev[dev];
+    int st = d.state.load(std::memory_order_acquire);
+    if (st == 0) {
+        int major = 0, sms = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            return FEATHER_ERR_LAUNCH;
+        d.sm_count = sms;
+        st = (major == 10) ? 1 : -1;
+        d.state.store(st, std::memory_order_release);
+    }
+    *info = &d;
+    return st == 1 ? FEATHER_OK : FEATHER_ERR_ARCH;
+}
+
+static inline bool aligned(const void* p, uintptr_t a) {
+    return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0;
+}
+
+static inline int launch_status() {
+    return cudaGetLastError() == cudaSuccess ? FEATHER_OK : FEATHER_ERR_LAUNCH;
+}
+
+template <int MODE, bool F32>
+static int encode_launch(const void* src, uint32_t* dst, long long n, cudaStream_t s) {
+    const long long n_words = (n + 3) / 4;
+    long long vec_groups = 0;
+    if (aligned(src, 16) && aligned(dst, 16)) vec_groups = n / 16;
+    if (vec_groups > 0) {
+        const long long blocks = (vec_groups + 255) / 256;
+        encode_vec_kernel<MODE, F32><<<(unsigned)blocks, 256, 0, s>>>(
+            src, reinterpret_cast<uint4*>(dst), vec_groups);
+    }
+    const long long rest = n_words - vec_groups * 4;
+    if (rest > 0) {
+        const long long blocks = (rest + 255) / 256;
+        encode_word_kernel<MODE, F32><<<(unsigned)blocks, 256, 0, s>>>(src, dst, vec_groups * 4,
+                                                                         n_words, n);
+    }
+    return launch_status();
+}
+
+// Sticky status word raised by a kernel whose bounded wait gave up
+// (gemv_ring.cuh).  Read and cleared by feather_device_status().
+__device__ unsigned int g_wait_status;
+
+static int status_word(unsigned int** ptr) {
+    static std::atomic<unsigned int*> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FEATHER_ERR_LAUNCH;
+    unsigned int* p = cached[dev].load(std::memory_order_acquire);
+    if (!p) {
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_wait_status) != cudaSuccess)
+            return FEATHER_ERR_LAUNCH;
+        cached[dev].store(p, std::memory_order_release);
+    }
+    *ptr = p;
+    return FEATHER_OK;
+}
+
+// Launch geometry.
+//   ring kernel (large matrices): 16 consumer warps x 1 row, 4 KiB of a row per
+//   bulk copy, 3 stages of 64 KiB, FP16 vector tile of 16384 codes, 1 CTA/SM.
+//   stream kernel (mid-size): 8 warps, 4 rows per group, 2 CTAs/SM.
+constexpr int kRingCW = 16, kRingRW = 1, kRingCL = 8, kRingStages = 3, kRingTile = 16384;
+constexpr int kGemvWarps = 8;
+constexpr int kGemvRows = 4;
+constexpr int kGemvCtasPerSm = 2;
+constexpr int kGemvTileCodes = 16384;
+
+template <typename K>
+static int ensure_smem(K kernel, int smem, std::atomic<unsigned long long>& configured) {
+    int devid = 0;
+    if (cudaGetDevice(&devid) != cudaSuccess) return FEATHER_ERR_LAUNCH;
+    if (!((configured.load(std::memory_order_acquire) >> devid) & 1ull)) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+            cudaSuccess)
+            return FEATHER_ERR_LAUNCH;
+        configured.fetch_or(1ull << devid, std::memory_order_release);
+    }
+    return FEATHER_OK;
+}
+
+template <int MODE>
+static int gemv_ring_launch(const uint32_t* m, const uint32_t* v, float* out, long long M,
+                            long long N, const DeviceInfo& dev, cudaStream_t s) {
+    using G = RingGeometry<kRingCW, kRingRW, kRingCL, kRingStages, kRingTile>;
+    auto kernel = gemv_ring_kernel<MODE, kRingCW, kRingRW, kRingCL, kRingStages, kRingTile, 1, false>;
+    static std::atomic<unsigned long long> configured{0};
+    if (int st = ensure_smem(kernel, G::kSmemBytes, configured)) return st;
+    unsigned int* status = nullptr;
+    if (int st = status_word(&status)) return st;
+    long long grid = dev.sm_count;
+    const long long max_useful = (M + G::kTaskRows - 1) / G::kTaskRows;
+    if (grid > max_useful) grid = max_useful;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(G::kThreads);
+    cfg.dynamicSmemBytes = G::kSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const unsigned char*>(m),
+                                             v, out, (int)M, (int)(N / 16), status);
+    return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
+}
+
+template <int MODE>
+static int gemv_launch(const uint32_t* m, const uint32_t* v, float* out, long long M, long long N,
+                       const DeviceInfo& dev, cudaStream_t s) {
+    const bool vec_ok = (N % 16 == 0) && aligned(m, 16);
+    // ring: every SM gets at least two full tasks and rows are long enough for 4 KiB copies
+    if (vec_ok && N >= 4096 && M >= 2ll * dev.sm_count * kRingCW * kRingRW)
+        return gemv_ring_launch<MODE>(m, v, out, M, N, dev, s);
+    const bool fast = vec_ok && M * (N / 16) >= 4096;
+    if (!fast) {
+        const long long blocks = (M + 7) / 8;  // 8 warps per CTA, one row per warp
+        const long long cap = (long long)dev.sm_count * 8;
+        gemv_general_kernel<MODE><<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(
+            m, v, out, (int)M, (int)(N / 4));
+        return launch_status();
+    }
+    auto kernel = gemv_stream_kernel<MODE, kGemvWarps, kGemvRows, kGemvCtasPerSm, kGemvTileCodes>;
+    constexpr int smem = gemv_stream_smem_bytes(kGemvTileCodes, kGemvWarps, kGemvRows);
+    static std::atomic<unsigned long long> configured{0};
+    if (int st = ensure_smem(kernel, smem, configured)) return st;
+    long long grid = (long long)dev.sm_count * kGemvCtasPerSm;
+    const long long max_useful = (M + kGemvRows - 1) / kGemvRows;
+    if (grid > max_useful) grid = max_useful;
+    kernel<<<(unsigned)grid, kGemvWarps * 32, smem, s>>>(reinterpret_cast<const uint4*>(m), v, out,
+                                                         (int)M, (int)(N / 16));
+    return launch_status();
+}
+
+template <int MODE>
+static int dot_launch(const uint32_t* a, const uint32_t* b, float* out, void* workspace,
+                      long long n_words, const DeviceInfo& dev, cudaStream_t s) {
+    unsigned int* ticket = reinterpret_cast<unsigned int*>(workspace);
+    float* partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 16);
+    long long grid = (long long)dev.sm_count * 4;
+    const long long need = (n_words / 4 + kDotThreads - 1) / kDotThreads;
+    if (grid > need) grid = need;
+    if (grid < 1) grid = 1;
+    if (grid > kDotMaxCtas) grid = kDotMaxCtas;
+    if (aligned(a, 16) && aligned(b, 16))
+        dot_kernel<MODE, true, 4><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket, partial,
+                                                                          n_words);
+    else
+        dot_kernel<MODE, false, 1><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket,
+                                                                           partial, n_words);
+    return launch_status();
+}
+
+}  // namespace feather
+
+using namespace feather;
+
+extern "C" {
+
+int feather_version(void) { return 100; /* 0.1.0 */ }
+
+const char* feather_strerror(int status) {
+    switch (status) {
+        case FEATHER_OK: return "success";
+        case FEATHER_ERR_BAD_ARG: return "bad argument (null pointer, negative size, or N not a multiple of 4)";
+        case FEATHER_ERR_MISALIGNED: return "pointer is not aligned as the entry point requires";
+        case FEATHER_ERR_MODE: return "unknown mode, source dtype or decode semantics";
+        case FEATHER_ERR_ARCH: return "current device is not a compute-capability 10.x (B200) GPU";
+        case FEATHER_ERR_LAUNCH: return "CUDA reported an error at launch";
+        case FEATHER_ERR_WORKSPACE: return "workspace is missing or too small";
+        case FEATHER_ERR_TIMEOUT: return "a bounded device-side wait gave up";
+        default: return "unknown feather status";
+    }
+}
+
+int feather_encode_fp8(const void* src, int src_dtype, uint32_t* dst, int64_t n_elems, int mode,
+                       void* stream) {
+    if (n_elems < 0) return FEATHER_ERR_BAD_ARG;
+    if ((mode != FEATHER_MODE_E5M2 && mode != FEATHER_MODE_E4M3) ||
+        (src_dtype != FEATHER_SRC_F16 && src_dtype != FEATHER_SRC_F32))
+        return FEATHER_ERR_MODE;
+    if (n_elems == 0) return FEATHER_OK;
+    if (!src || !dst) return FEATHER_ERR_BAD_ARG;
+    if (!aligned(src, src_dtype == FEATHER_SRC_F16 ? 2 : 4) || !aligned(dst, 4))
+        return FEATHER_ERR_MISALIGNED;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (mode == FEATHER_MODE_E5M2)
+        return src_dtype == FEATHER_SRC_F32 ? encode_launch<kE5M2, true>(src, dst, n_elems, s)
+                                            : encode_launch<kE5M2, false>(src, dst, n_elems, s);
+    return src_dtype == FEATHER_SRC_F32 ? encode_launch<kE4M3, true>(src, dst, n_elems, s)
+                                        : encode_launch<kE4M3, false>(src, dst, n_elems, s);
+}
+
+int feather_decode_fp8(const uint32_t* src, float* dst, int64_t n_elems, int mode, int semantics,
+                       void* stream) {
+    if (n_elems < 0) return FEATHER_ERR_BAD_ARG;
+    if ((mode != FEATHER_MODE_E5M2 && mode != FEATHER_MODE_E4M3) ||
+        (semantics != FEATHER_DECODE_KERNEL && semantics != FEATHER_DECODE_IEEE))
+        return FEATHER_ERR_MODE;
+    if (n_elems == 0) return FEATHER_OK;
+    if (!src || !dst) return FEATHER_ERR_BAD_ARG;
+    if (!aligned(src, 4) || !aligned(dst, 4)) return FEATHER_ERR_MISALIGNED;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const long long n_words = (n_elems + 3) / 4;
+    const unsigned blocks = (unsigned)((n_words + 255) / 256);
+    if (mode == FEATHER_MODE_E5M2)
+        decode_kernel<kE5M2, false><<<blocks, 256, 0, s>>>(src, dst, n_elems);
+    else if (semantics == FEATHER_DECODE_KERNEL)
+        decode_kernel<kE4M3, false><<<blocks, 256, 0, s>>>(src, dst, n_elems);
+    else
+        decode_kernel<kE4M3, true><<<blocks, 256, 0, s>>>(src, dst, n_elems);
+    return launch_status();
+}
+
+int feather_gemv_fp8(const uint32_t* m, const uint32_t* v, float* out, int64_t M, int64_t N,
+                     int mode, void* stream) {
+    if (M < 0 || N < 0 || (N & 3) || M > 0x7FFFFFFF || N > 0x7FFFFFFFll * 4) return FEATHER_ERR_BAD_ARG;
+    if (mode != FEATHER_MODE_E5M2 && mode != FEATHER_MODE_E4M3) return FEATHER_ERR_MODE;
+    if (M == 0) return FEATHER_OK;
+    if (!out || (N > 0 && (!m || !v))) return FEATHER_ERR_BAD_ARG;
+    if (!aligned(m, 4) || !aligned(v, 4) || !aligned(out, 4)) return FEATHER_ERR_MISALIGNED;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (N == 0)
+        return cudaMemsetAsync(out, 0, sizeof(float) * (size_t)M, s) == cudaSuccess
+                   ? FEATHER_OK : FEATHER_ERR_LAUNCH;
+    return mode == FEATHER_MODE_E5M2 ? gemv_launch<kE5M2>(m, v, out, M, N, *dev, s)
+                                     : gemv_launch<kE4M3>(m, v, out, M, N, *dev, s);
+}
+
+int feather_device_status(void* stream) {
+    unsigned int* status = nullptr;
+    if (int st = status_word(&status)) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned int host = 0;
+    if (cudaMemcpyAsync(&host, status, sizeof(host), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess)
+        return FEATHER_ERR_LAUNCH;
+    if (host == 0) return FEATHER_OK;
+    if (cudaMemsetAsync(status, 0, sizeof(host), s) != cudaSuccess) return FEATHER_ERR_LAUNCH;
+    return FEATHER_ERR_TIMEOUT;
+}
+
+int64_t feather_dot_workspace_bytes(int64_t n_words) {
+    (void)n_words;  // one partial slot per CTA of the largest grid, plus the ticket
+    return kDotWorkspaceBytes;
+}
+
+int feather_dot_fp8(const uint32_t* a, const uint32_t* b, float* out, void* workspace,
+                    int64_t n_words, int mode, void* stream) {
+    if (n_words < 0) return FEATHER_ERR_BAD_ARG;
+    if (mode != FEATHER_MODE_E5M2 && mode != FEATHER_MODE_E4M3) return FEATHER_ERR_MODE;
+    if (!out || (n_words > 0 && (!a || !b))) return FEATHER_ERR_BAD_ARG;
+    if (!workspace) return FEATHER_ERR_WORKSPACE;
+    if (!aligned(a, 4) || !aligned(b, 4) || !aligned(out, 4) || !aligned(workspace, 16))
+        return FEATHER_ERR_MISALIGNED;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return mode == FEATHER_MODE_E5M2 ? dot_launch<kE5M2>(a, b, out, workspace, n_words, *dev, s)
+                                     : dot_launch<kE4M3>(a, b, out, workspace, n_words, *dev, s);
+}
+
+}  // extern "C"

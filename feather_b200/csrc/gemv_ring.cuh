@@ -1,0 +1,357 @@
+// gemv_ring_kernel: the packed-FP8 GEMV as a bulk-async-copy ring (sm_100a).
+//
+//   out[r] = sum_j decode(m[r, j]) * decode(v[j])     FP32 accumulation
+//   (reference kernels: feather/routines/gemv.py:8-61 and :91-133)
+//
+// Why a ring: the kernel is HBM-bound, and B200 needs >40 KB of loads in flight
+// per SM all the time to keep HBM3e busy.  Register-held loads tie that amount
+// to occupancy and drain at every reduction.  Here one producer warp keeps a
+// ring of STAGES shared-memory stages full with cp.async.bulk (the TMA engine's
+// 1-D bulk copy, completion counted on an mbarrier), so ~190 KB per SM are in
+// flight regardless of what the consumer warps are doing.
+//
+// Work split
+//   * persistent grid, one CTA per SM; CTA b owns the contiguous rows
+//     [M*b/G, M*(b+1)/G) and walks them in tasks of CW*RW rows;
+//   * a stage holds, for every row of the task, the same SEGB = CL*512 bytes
+//     of columns (one bulk copy per row and stage, issued by the lanes of the
+//     producer warp in parallel);
+//   * consumer warp w OWNS rows w*RW .. w*RW+RW-1 of the task for all columns,
+//     so a row's sum never leaves the warp: no CTA-wide barrier in the loop,
+//     only mbarrier waits, and one shuffle butterfly per task;
+//   * the vector is decoded ONCE per CTA and column tile to FP16 pairs in
+//     shared memory (the decoded values of both formats are FP16 numbers), in
+//     a layout whose 128-bit reads are conflict-free;
+//   * matrix codes are decoded in registers to FP16 pairs (fp8_codec.cuh) and
+//     multiplied with the mixed-precision FMA fma.rn.f32.f16 (FP16 operands,
+//     FP32 accumulator, one rounding): the product of two FP16 numbers is
+//     exact in FP32, so this equals the reference's convert-then-multiply.
+//
+// Every wait is bounded: after kWaitLimitNs without progress a thread raises
+// the status word and stops waiting; the host reads the word with
+// feather_device_status().  No multicast copies are used anywhere.
+#pragma once
+#include "fp8_codec.cuh"
+
+namespace feather {
+
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait.  Returns false (and raises *status) if the phase did not
+// complete within kWaitLimitNs.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned int* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > kWaitLimitNs) {
+            atomicOr(status, 1u);
+            return false;
+        }
+    }
+}
+// 1-D bulk copy global -> this CTA's shared memory, completion on `bar`.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// Barrier over the threads counted by `bar` (arrive, then a bounded wait).
+__device__ __forceinline__ bool mbar_sync(uint32_t bar, uint32_t& parity, unsigned int* status) {
+    mbar_arrive(bar);
+    const bool ok = mbar_wait(bar, parity, status);
+    parity ^= 1u;
+    return ok;
+}
+
+// acc += a.lo * b.lo ; acc2 += a.hi * b.hi   (FP16 operands, FP32 accumulate)
+__device__ __forceinline__ void fma_h2(uint32_t a, uint32_t b, float& acc_lo, float& acc_hi) {
+    asm("{ .reg .b16 a0, a1, b0, b1;\n"
+        "  mov.b32 {a0, a1}, %2; mov.b32 {b0, b1}, %3;\n"
+        "  fma.rn.f32.f16 %0, a0, b0, %0;\n"
+        "  fma.rn.f32.f16 %1, a1, b1, %1; }"
+        : "+f"(acc_lo), "+f"(acc_hi) : "r"(a), "r"(b));
+}
+
+// Decode the four codes of a word to two FP16 pairs (same pairing for the
+// matrix and the vector): E5M2 lo=(c0,c1) hi=(c2,c3); E4M3 lo=(c0,c2) hi=(c1,c3).
+template <int MODE>
+__device__ __forceinline__ void decode_word_h2(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    if (MODE == kE5M2) {
+        lo = prmt(w, 0u, 0x1404u);
+        hi = prmt(w, 0u, 0x3424u);
+    } else {
+        lo = e4m3_pair_to_h2(w << 8);
+        hi = e4m3_pair_to_h2(w);
+    }
+}
+
+// One 16-byte chunk of a row (16 codes) times the matching 16 vector values
+// (va, vb: eight FP16 pairs in decode_word_h2's pairing) into four accumulators.
+template <int MODE>
+__device__ __forceinline__ void fma_chunk(const uint4 mw, const uint4 va, const uint4 vb,
+                                          float (&acc)[4]) {
+    uint32_t lo, hi;
+    decode_word_h2<MODE>(mw.x, lo, hi);
+    fma_h2(lo, va.x, acc[0], acc[1]);
+    fma_h2(hi, va.y, acc[2], acc[3]);
+    decode_word_h2<MODE>(mw.y, lo, hi);
+    fma_h2(lo, va.z, acc[0], acc[1]);
+    fma_h2(hi, va.w, acc[2], acc[3]);
+    decode_word_h2<MODE>(mw.z, lo, hi);
+    fma_h2(lo, vb.x, acc[0], acc[1]);
+    fma_h2(hi, vb.y, acc[2], acc[3]);
+    decode_word_h2<MODE>(mw.w, lo, hi);
+    fma_h2(lo, vb.z, acc[0], acc[1]);
+    fma_h2(hi, vb.w, acc[2], acc[3]);
+}
+
+// Sum RW per-lane values over the warp with a halving butterfly: after it, the
+// lanes with lane % (32/RW) == 0 hold the total of row lane / (32/RW) in v[0].
+template <int RW>
+__device__ __forceinline__ void warp_reduce_rows(float (&v)[RW], int lane) {
+    int o = 16;
+#pragma unroll
+    for (int n = RW; n > 1; n >>= 1, o >>= 1) {
+        const bool upper = (lane & o) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+            const float send = upper ? v[i] : v[i + n / 2];
+            const float keep = upper ? v[i + n / 2] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, o);
+        }
+    }
+    for (; o > 0; o >>= 1) v[0] += __shfl_xor_sync(0xFFFFFFFFu, v[0], o);
+}
+
+template <int CW, int RW, int CL, int STAGES, int TILE>
+struct RingGeometry {
+    static constexpr int kTaskRows = CW * RW;          // rows per task (= per stage)
+    static constexpr int kSegChunks = CL * 32;         // 16-byte chunks per row and stage
+    static constexpr int kSegBytes = kSegChunks * 16;
+    static constexpr int kStageBytes = kTaskRows * kSegBytes;
+    static constexpr int kTileChunks = TILE / 16;
+    static constexpr int kVecBytes = TILE * 2;         // FP16 vector tile
+    static constexpr int kSmemBytes = kVecBytes + STAGES * kStageBytes + (2 * STAGES + 1) * 8;
+    static constexpr int kThreads = (CW + 1) * 32;
+    static_assert(kTileChunks % kSegChunks == 0, "a tile holds whole segments");
+};
+
+// CTAS: CTAs resident per SM the launch is sized for.  PREFETCH: the producer
+// also asks L2 for the next task's rows (cp.async.bulk.prefetch.L2) when it
+// starts a task, so HBM reads run a whole task ahead of the ring.
+template <int MODE, int CW, int RW, int CL, int STAGES, int TILE, int CTAS, bool PREFETCH>
+__global__ void __launch_bounds__((CW + 1) * 32, CTAS)
+gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict__ v,
+                 float* __restrict__ out, int M, int n16, unsigned int* __restrict__ status) {
+    using G = RingGeometry<CW, RW, CL, STAGES, TILE>;
+    // Programmatic dependent launch: let the next kernel of the stream be
+    // scheduled onto SMs as they free up, and wait for everything before this
+    // kernel (in stream order) to have completed and become visible before any
+    // global memory is touched.  Without the launch attribute both are no-ops.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint4* vec = reinterpret_cast<uint4*>(smem);
+    unsigned char* ring = smem + G::kVecBytes;
+    const uint32_t ring_s = smem_u32(ring);
+    const uint32_t bars = smem_u32(ring + STAGES * G::kStageBytes);  // full[STAGES], empty[STAGES]
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    const uint32_t tile_bar = bars + 8u * (2 * STAGES);  // all consumer threads
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row_begin = (int)(((long long)M * blockIdx.x) / gridDim.x);
+    const int row_end = (int)(((long long)M * (blockIdx.x + 1)) / gridDim.x);
+    const int n_tasks = (row_end - row_begin + G::kTaskRows - 1) / G::kTaskRows;
+    const int n_tiles = (n16 + G::kTileChunks - 1) / G::kTileChunks;
+    const size_t row_bytes = (size_t)n16 * 16;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);     // the producer's arrive + the copied bytes
+            mbar_init(empty_bar(s), CW);   // one arrive per consumer warp
+        }
+        mbar_init(tile_bar, CW * 32);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (n_tasks == 0) return;
+
+    if (warp == CW) {
+        // ------------------------------------------------------- producer --
+        int s = 0;               // ring slot of the next stage
+        uint32_t round = 0;      // how many times the ring has wrapped
+        bool alive = true;
+        for (int tile = 0; tile < n_tiles && alive; ++tile) {
+            const int tile_chunks = min(G::kTileChunks, n16 - tile * G::kTileChunks);
+            const int n_seg = (tile_chunks + G::kSegChunks - 1) / G::kSegChunks;
+            for (int task = 0; task < n_tasks && alive; ++task) {
+                const int row0 = row_begin + task * G::kTaskRows;
+                const int valid_rows = min(G::kTaskRows, row_end - row0);
+                if (PREFETCH) {
+                    // next task of this tile (or the first task of the next tile)
+                    int p_tile = tile, p_row0 = row0 + G::kTaskRows;
+                    if (task + 1 == n_tasks) { p_tile = tile + 1; p_row0 = row_begin; }
+                    if (p_tile < n_tiles) {
+                        const int p_chunks = min(G::kTileChunks, n16 - p_tile * G::kTileChunks);
+                        const int p_rows = min(G::kTaskRows, row_end - p_row0);
+                        for (int r = lane; r < p_rows; r += 32)
+                            bulk_prefetch_l2(m + (size_t)(p_row0 + r) * row_bytes +
+                                                 (size_t)p_tile * G::kTileChunks * 16,
+                                             (uint32_t)p_chunks * 16u);
+                    }
+                }
+                for (int seg = 0; seg < n_seg; ++seg) {
+                    if (round > 0 && !mbar_wait(empty_bar(s), (round & 1u) ^ 1u, status)) {
+                        alive = false;
+                        break;
+                    }
+                    const int chunks = min(G::kSegChunks, tile_chunks - seg * G::kSegChunks);
+                    const uint32_t bytes = (uint32_t)chunks * 16u;
+                    if (lane == 0) mbar_arrive_expect_tx(full_bar(s), bytes * (uint32_t)valid_rows);
+                    const size_t col = ((size_t)tile * G::kTileChunks + (size_t)seg * G::kSegChunks) * 16;
+                    for (int r = lane; r < valid_rows; r += 32)
+                        bulk_load(ring_s + s * G::kStageBytes + r * G::kSegBytes,
+                                  m + (size_t)(row0 + r) * row_bytes + col, bytes, full_bar(s));
+                    if (++s == STAGES) { s = 0; ++round; }
+                }
+            }
+        }
+        if (!alive) {
+            // a wait gave up: give the copies already issued time to land
+            // before the CTA's shared memory is released
+            const unsigned long long t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < 1000000ull) {}
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------- consumers --
+    int s = 0;            // ring slot of the next stage
+    uint32_t phase = 0;   // its mbarrier parity
+    bool alive = true;
+    uint32_t tile_parity = 0;
+    const uint4* const ring_lane = reinterpret_cast<const uint4*>(ring) + (warp * RW) * G::kSegChunks + lane;
+    for (int tile = 0; tile < n_tiles && alive; ++tile) {
+        const int tile_chunks = min(G::kTileChunks, n16 - tile * G::kTileChunks);
+        const int n_seg = (tile_chunks + G::kSegChunks - 1) / G::kSegChunks;
+        const int n_full_seg = tile_chunks / G::kSegChunks;
+        // stage the vector tile: FP16 pairs, (group g, half k, lane l) is the
+        // uint4 at (g*2 + k)*32 + l and holds codes 16*(32g+l) + 8k .. +7.
+        if (tile > 0 && !mbar_sync(tile_bar, tile_parity, status)) break;  // previous tile consumed
+        {
+            const int w_begin = tile * (TILE / 4);
+            const int w_valid = tile_chunks * 4;
+            const int w_fill = n_seg * G::kSegChunks * 4;
+            uint2* vec2 = reinterpret_cast<uint2*>(vec);
+            constexpr int kBatch = 4;  // loads in flight per thread
+            for (int w0 = threadIdx.x; w0 < w_fill; w0 += kBatch * CW * 32) {
+                uint32_t raw[kBatch];
+#pragma unroll
+                for (int b = 0; b < kBatch; ++b) {
+                    const int wl = w0 + b * CW * 32;
+                    raw[b] = wl < w_valid ? __ldg(v + w_begin + wl) : 0u;  // beyond N: code 0 = +0.0
+                }
+#pragma unroll
+                for (int b = 0; b < kBatch; ++b) {
+                    const int wl = w0 + b * CW * 32;
+                    if (wl < w_fill) {
+                        uint32_t lo, hi;
+                        decode_word_h2<MODE>(raw[b], lo, hi);
+                        const int chunk = wl >> 2, k = wl & 3;
+                        vec2[(((chunk >> 5) * 2 + (k >> 1)) * 32 + (chunk & 31)) * 2 + (k & 1)] = make_uint2(lo, hi);
+                    }
+                }
+            }
+        }
+        if (!mbar_sync(tile_bar, tile_parity, status)) break;
+
+        for (int task = 0; task < n_tasks && alive; ++task) {
+            const int row0 = row_begin + task * G::kTaskRows + warp * RW;
+            const bool all_rows = row0 + RW <= row_end;  // warp-uniform
+            float acc[RW][4];
+#pragma unroll
+            for (int r = 0; r < RW; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+
+            for (int seg = 0; seg < n_seg; ++seg) {
+                if (!mbar_wait(full_bar(s), phase, status)) {
+                    alive = false;
+                    break;
+                }
+                const uint4* st = ring_lane + s * (G::kStageBytes / 16);
+                const uint4* vs = vec + (seg * CL * 2) * 32 + lane;
+                if (all_rows && seg < n_full_seg) {
+                    // whole segment, all rows: no predicates, fully unrolled
+#pragma unroll
+                    for (int c = 0; c < CL; ++c) {
+                        const uint4 va = vs[(c * 2) * 32], vb = vs[(c * 2 + 1) * 32];
+#pragma unroll
+                        for (int r = 0; r < RW; ++r)
+                            fma_chunk<MODE>(st[r * G::kSegChunks + c * 32], va, vb, acc[r]);
+                    }
+                } else {
+                    const int chunks = min(G::kSegChunks, tile_chunks - seg * G::kSegChunks);
+#pragma unroll 1
+                    for (int c = 0; c < CL; ++c) {
+                        if (c * 32 + lane < chunks) {
+                            const uint4 va = vs[(c * 2) * 32], vb = vs[(c * 2 + 1) * 32];
+#pragma unroll
+                            for (int r = 0; r < RW; ++r)
+                                if (row0 + r < row_end)
+                                    fma_chunk<MODE>(st[r * G::kSegChunks + c * 32], va, vb, acc[r]);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty_bar(s));  // this warp is done with the stage
+                if (++s == STAGES) { s = 0; phase ^= 1u; }
+            }
+            if (!alive) break;
+            // the warp owns its rows: one butterfly, then the row's lane writes
+            float sums[RW];
+#pragma unroll
+            for (int r = 0; r < RW; ++r) sums[r] = (acc[r][0] + acc[r][1]) + (acc[r][2] + acc[r][3]);
+            warp_reduce_rows<RW>(sums, lane);
+            if ((lane & (32 / RW - 1)) == 0) {
+                const int row = row0 + lane / (32 / RW);
+                if (row < row_end) {
+                    if (tile == 0) out[row] = sums[0];
+                    else out[row] += sums[0];  // the same lane owns the row in every tile
+                }
+            }
+        }
+    }
+}
+
+}  // namespace feather

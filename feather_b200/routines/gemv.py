@@ -1,0 +1,71 @@
+"""Packed-FP8 GEMV: the reference's ``feather.routines.gemv`` surface.
+
+``gemv_fp8_e5m2_acc_fp32_gpu`` / ``gemv_fp8_e4m3_acc_fp32_gpu`` keep the
+reference signatures (feather/routines/gemv.py:136, :187): packed matrix,
+packed vector, the UNPACKED matrix shape; result an FP32 ``(M,)`` CUDA tensor,
+enqueued on the current stream without synchronising.  Unlike the reference
+wrappers, operands are validated (the reference computes garbage silently for
+a short vector, a CPU tensor or N % 4 != 0) and the output is allocated on the
+device directly.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from ..packers.fp8 import as_words
+
+__all__ = ["gemv_fp8_acc_fp32_gpu", "gemv_fp8_e5m2_acc_fp32_gpu", "gemv_fp8_e4m3_acc_fp32_gpu"]
+
+
+def gemv_fp8_acc_fp32_gpu(m: torch.Tensor, v: torch.Tensor, m_shape, mode: str = "E5M2",
+                          out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r] = sum_j decode(m[r, j]) * decode(v[j]) with FP32 accumulation."""
+    # packed operands may be PackedFP8 (a Tensor subclass): skip the Python-level
+    # __torch_function__ dispatch for the metadata reads below
+    with torch._C.DisableTorchFunctionSubclass():
+        return _gemv(m, v, m_shape, mode, out)
+
+
+def _gemv(m, v, m_shape, mode, out):
+    mode_id = _lib.mode_id(mode)
+    m = as_words(m, "m")
+    v = as_words(v, "v")
+    if len(m_shape) != 2:
+        raise ValueError("m_shape must be the unpacked (M, N) of the matrix")
+    M, N = int(m_shape[0]), int(m_shape[1])
+    if M < 0 or N < 0 or N % 4:
+        raise ValueError("N must be a non-negative multiple of 4: rows are whole packed words")
+    if m.numel() < M * (N // 4):
+        raise ValueError(f"m holds {m.numel()} words, {M}x{N} needs {M * (N // 4)}")
+    if v.numel() < N // 4:
+        raise ValueError(f"v holds {v.numel()} words, N={N} needs {N // 4}")
+    if v.device != m.device:
+        raise ValueError("m and v must be on the same device")
+    if out is None:
+        out = torch.empty((M,), dtype=torch.float32, device=m.device)
+    elif (out.dtype != torch.float32 or out.numel() != M or out.device != m.device
+          or not out.is_contiguous()):
+        raise ValueError("out must be a contiguous float32 tensor of M elements on m's device")
+    if M:
+        fn = _lib.load().feather_gemv_fp8
+        idx = m.device.index
+        if torch.cuda.current_device() == idx:
+            _lib.check(fn(m.data_ptr(), v.data_ptr(), out.data_ptr(), M, N, mode_id,
+                          _lib.current_stream_ptr(idx)))
+        else:
+            with torch.cuda.device(idx):
+                _lib.check(fn(m.data_ptr(), v.data_ptr(), out.data_ptr(), M, N, mode_id,
+                              _lib.current_stream_ptr(idx)))
+    return out
+
+
+def gemv_fp8_e5m2_acc_fp32_gpu(m: torch.Tensor, v: torch.Tensor, m_shape) -> torch.Tensor:
+    """Drop-in for feather/routines/gemv.py:136-184."""
+    return gemv_fp8_acc_fp32_gpu(m, v, m_shape, "E5M2")
+
+
+def gemv_fp8_e4m3_acc_fp32_gpu(m: torch.Tensor, v: torch.Tensor, m_shape) -> torch.Tensor:
+    """Drop-in for feather/routines/gemv.py:187-235 (kernel decode of
+    gemv.py:83-88: exponent-0 codes are +-m * 2^-17, 0x7F/0xFF are +-480)."""
+    return gemv_fp8_acc_fp32_gpu(m, v, m_shape, "E4M3")

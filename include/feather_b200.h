@@ -1,0 +1,131 @@
+/*
+ * feather_b200 -- C ABI of the packed-FP8 matrix-vector path for NVIDIA B200
+ * (sm_100a).  One shared library, plain pointers and sizes, no C++ types.
+ *
+ * The reference project (SuriyaaMM/feather) is pure Python and has no FFI
+ * layer; each entry point below names the reference function whose work it
+ * replaces (paths inside the reference project).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer owned by the caller.  The library
+ *     never allocates or frees device memory and keeps no per-call state.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default
+ *     stream).  All work is enqueued on it; no call synchronises the host.
+ *   - A "word" is a little-endian uint32 holding four FP8 codes, element 4k in
+ *     the low byte (feather/packers/fp8.py:123-134).
+ *   - mode:   0 = E5M2, 1 = E4M3 (the "fn" flavour: no inf, 0x7F/0xFF NaN).
+ *   - Return: FEATHER_OK (0) or a negative feather_status; see
+ *     feather_strerror().  No exceptions, no prints, no exit().
+ */
+#ifndef FEATHER_B200_H
+#define FEATHER_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum feather_status {
+    FEATHER_OK = 0,
+    FEATHER_ERR_BAD_ARG = -1,     /* null pointer, negative size, N % 4 != 0 ... */
+    FEATHER_ERR_MISALIGNED = -2,  /* pointer not aligned as documented          */
+    FEATHER_ERR_MODE = -3,        /* unknown mode / dtype / semantics value     */
+    FEATHER_ERR_ARCH = -4,        /* current device is not compute capability 10.x */
+    FEATHER_ERR_LAUNCH = -5,      /* CUDA reported a launch error               */
+    FEATHER_ERR_WORKSPACE = -6,   /* workspace missing or too small             */
+    FEATHER_ERR_TIMEOUT = -7      /* a bounded device-side wait gave up         */
+} feather_status;
+
+#define FEATHER_MODE_E5M2 0
+#define FEATHER_MODE_E4M3 1
+#define FEATHER_SRC_F16 0
+#define FEATHER_SRC_F32 1
+#define FEATHER_DECODE_KERNEL 0 /* values the GEMV/dot kernels multiply with  */
+#define FEATHER_DECODE_IEEE 1   /* values the reference CPU unpacker returns   */
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+int feather_version(void);
+
+/* Static, NUL-terminated description of a feather_status value. */
+const char* feather_strerror(int status);
+
+/*
+ * Encode fp16/fp32 values to FP8 and pack four codes per word.
+ * Replaces feather/packers/fp8.py:260-281 (pack_fp8_tensor), :178-210
+ * (pack_fp8_ndarray: flatten, zero-pad the tail to a whole word) and :69-136
+ * (pack_fp8_into_fp32: one round-to-nearest-even cast, E4M3 overflow to the
+ * NaN code, E5M2 overflow to inf).  Bit-exact with the reference packer.
+ *   src      n_elems values of src_dtype (FEATHER_SRC_F16 / _F32), element
+ *            aligned
+ *   dst      ceil(n_elems / 4) words, 4-byte aligned; padding codes are 0
+ */
+int feather_encode_fp8(const void* src, int src_dtype, uint32_t* dst, int64_t n_elems,
+                       int mode, void* stream);
+
+/*
+ * Decode packed words to fp32, element order.
+ * FEATHER_DECODE_KERNEL reproduces the in-kernel decode of
+ * feather/routines/gemv.py:31-34 (E5M2: fp16 bits = code << 8) and
+ * gemv.py:83-88 (E4M3 re-bias: exponent-0 codes give +-m * 2^-17, 0x7F/0xFF
+ * give +-480).  FEATHER_DECODE_IEEE reproduces the CPU unpacker
+ * feather/packers/fp8.py:336-392 / :395-432.
+ *   src      ceil(n_elems / 4) words;  dst  n_elems floats
+ */
+int feather_decode_fp8(const uint32_t* src, float* dst, int64_t n_elems, int mode,
+                       int semantics, void* stream);
+
+/*
+ * out[r] = sum_j decode(m[r, j]) * decode(v[j]),  FP32 products and sums.
+ * Replaces feather/routines/gemv.py:136-184 (gemv_fp8_e5m2_acc_fp32_gpu) and
+ * :187-235 (gemv_fp8_e4m3_acc_fp32_gpu) with their kernels gemv.py:8-61 and
+ * :91-133.
+ *   m        M * N / 4 words, row-major, row stride N / 4 words (gemv.py:18)
+ *   v        N / 4 words
+ *   out      M floats (written, not accumulated)
+ *   M, N     UNPACKED matrix shape; N % 4 == 0 (rows are whole words,
+ *            gemv.py:182).  M == 0 or N == 0 is allowed (N == 0 writes zeros).
+ * m, v and out must be 4-byte aligned; the fast paths need m 16-byte aligned
+ * and N % 16 == 0, other shapes take a slower general kernel.
+ * The kernel is launched with programmatic stream serialisation: it orders
+ * itself after all earlier work of the stream before touching memory, and
+ * lets the next kernel of the stream start its launch early.
+ * The sum order differs from the reference's (which is itself unspecified);
+ * results agree to FP32 rounding.
+ */
+int feather_gemv_fp8(const uint32_t* m, const uint32_t* v, float* out, int64_t M, int64_t N,
+                     int mode, void* stream);
+
+/*
+ * Health check for the kernels that wait on shared-memory barriers (the large
+ * GEMV streams the matrix through a ring of asynchronous bulk copies).  Every
+ * such wait is bounded; a wait that gives up raises a sticky status word on
+ * the device instead of hanging.  This call SYNCHRONISES `stream`, returns
+ * FEATHER_ERR_TIMEOUT if the word was raised since the last check (and clears
+ * it), FEATHER_OK otherwise.  No counterpart in the reference (its Triton
+ * kernels have no waits); the GEMV results of a run that reports a timeout
+ * are undefined.
+ */
+int feather_device_status(void* stream);
+
+/*
+ * *out = sum_i decode(a[i]) * decode(b[i]) over 4 * n_words codes.
+ * Replaces feather/routines/dot.py:220-260 (dot_fp8_e5m2_acc_fp32_gpu) and its
+ * kernel dot.py:144-192.  The reference adds per-block sums with a float
+ * atomic (run-to-run different in the last bits); this one reduces in a fixed
+ * order through `workspace`, so it is deterministic.  mode E4M3 (kernel decode
+ * of gemv.py:83-88) is an extension: the reference has no E4M3 dot.
+ *   workspace   feather_dot_workspace_bytes(n_words) bytes, 16-byte aligned.
+ *               Its first 16 bytes must be zero before the FIRST use; the
+ *               kernel leaves them zero again, so the buffer can be reused by
+ *               later calls on the same stream without clearing.
+ *   out         one float (written)
+ */
+int feather_dot_fp8(const uint32_t* a, const uint32_t* b, float* out, void* workspace,
+                    int64_t n_words, int mode, void* stream);
+int64_t feather_dot_workspace_bytes(int64_t n_words);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FEATHER_B200_H */

@@ -1,0 +1,69 @@
+"""CPU-side checks of the boundary: the shared library loads, exports every
+symbol include/feather_b200.h declares, and rejects bad arguments before it
+touches a device.  No compute call is made here."""
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from feather_b200.csrc import build
+    build.build()  # nvcc cross-compiles for sm_100a without a GPU
+    from feather_b200 import _lib
+    return _lib.load()
+
+
+def test_every_declared_symbol_is_exported(lib):
+    header = open(os.path.join(ROOT, "include", "feather_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(feather_[a-z0-9_]+)\s*\(", header))
+    from feather_b200 import _lib
+    assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
+    for name in declared:
+        assert getattr(lib, name) is not None
+
+
+def test_version_and_strerror(lib):
+    assert lib.feather_version() >= 100
+    assert lib.feather_strerror(0) == b"success"
+    for code in range(-7, 0):
+        assert lib.feather_strerror(code) not in (b"", b"unknown feather status")
+    assert lib.feather_strerror(-99) == b"unknown feather status"
+    assert lib.feather_dot_workspace_bytes(1 << 24) >= 16 + 4
+
+
+def test_argument_rejection_needs_no_device(lib):
+    # these return before any CUDA call
+    assert lib.feather_gemv_fp8(None, None, None, 2, 6, 0, None) == -1   # N % 4
+    assert lib.feather_gemv_fp8(None, None, None, -1, 8, 0, None) == -1
+    assert lib.feather_gemv_fp8(None, None, None, 2, 8, 3, None) == -3   # mode
+    assert lib.feather_gemv_fp8(None, None, None, 0, 8, 0, None) == 0    # empty
+    assert lib.feather_encode_fp8(None, 0, None, -5, 0, None) == -1
+    assert lib.feather_encode_fp8(None, 2, None, 4, 0, None) == -3       # dtype
+    assert lib.feather_encode_fp8(None, 0, None, 0, 1, None) == 0
+    assert lib.feather_decode_fp8(None, None, 4, 0, 2, None) == -3       # semantics
+    assert lib.feather_dot_fp8(None, None, None, None, -1, 0, None) == -1
+    assert lib.feather_dot_fp8(None, None, None, None, 4, 0, None) == -1  # out is null
+
+
+def test_python_surface_without_gpu():
+    import torch
+
+    import feather
+    import feather_b200
+    assert feather.gemv is feather_b200.gemv and feather.dot is feather_b200.dot
+    from feather.packers.fp8 import pack_fp8_tensor
+    from feather.routines.dot import dot_fp8_e5m2_acc_fp32_gpu  # noqa: F401
+    from feather.routines.gemv import gemv_fp8_e4m3_acc_fp32_gpu, gemv_fp8_e5m2_acc_fp32_gpu  # noqa: F401
+    with pytest.raises(NotImplementedError):
+        pack_fp8_tensor(torch.zeros(4, dtype=torch.float16), mode="E3M4")
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):  # no CPU fallback
+            pack_fp8_tensor(torch.zeros(4, dtype=torch.float16))
+        with pytest.raises(ValueError):
+            feather.gemv(torch.zeros(4, dtype=torch.int32), torch.zeros(1, dtype=torch.int32),
+                         original_shape=(4, 4))

@@ -1,0 +1,426 @@
+"""GPU parity tests: the CUDA path, called through the C ABI (ctypes), against
+the oracle and the golden vectors produced by the reference.
+
+Bars: packed bytes and decoded values bit-exact; GEMV / dot within max relative
+error 1e-5, where "relative" is normalised by the largest reference output
+(GEMV) or by the sum of |products| (dot) -- FP32 accumulation is
+order-dependent and the reference's own order is unspecified.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import feather_oracle as O
+from tests.golden_inputs import DOT_CASES, GEMV_CASES, c3_matrix, dot_case, gemv_case, sample_f32
+
+pytestmark = pytest.mark.gpu
+MODES = ("E5M2", "E4M3")
+TOL = 1e-5  # max relative error stated by the north star
+
+
+@pytest.fixture(scope="module")
+def fb():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import feather_b200
+    feather_b200._lib.load()
+    return feather_b200
+
+
+def dev(a: np.ndarray) -> torch.Tensor:
+    if a.dtype == np.uint32:
+        return torch.from_numpy(a.view(np.int32)).cuda().view(torch.uint32)
+    return torch.from_numpy(a).cuda()
+
+
+def host_words(t: torch.Tensor) -> np.ndarray:
+    return t.view(torch.int32).cpu().numpy().view(np.uint32)
+
+
+def same_floats(a, b) -> bool:
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    nan = np.isnan(a)
+    return bool(np.array_equal(nan, np.isnan(b)) and
+                np.array_equal(a.view(np.uint32)[~nan], b.view(np.uint32)[~nan]))
+
+
+# ------------------------------------------------------------------ encode --
+@pytest.mark.parametrize("mode", MODES)
+def test_encode_every_fp16_pattern(fb, golden, mode):
+    h = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.float16).cuda()
+    got = host_words(fb.pack_fp8_tensor(h, mode)).view(np.uint8)
+    assert np.array_equal(got, golden("encode")[f"fp16_all_{mode}"])
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("kind,seed", [("bits", 11), ("lognormal", 12)])
+def test_encode_fp32_samples(fb, golden, mode, kind, seed):
+    x = dev(sample_f32(kind, 131072, seed))
+    got = host_words(fb.pack_fp8_tensor(x, mode)).view(np.uint8)
+    assert np.array_equal(got, golden("encode")[f"fp32_{kind}_{mode}"])
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_encode_fp32_edges(fb, golden, mode):
+    g = golden("encode")
+    x = dev(g["fp32_edge_input_bits"].view(np.float32).copy())
+    got = host_words(fb.pack_fp8_tensor(x, mode)).view(np.uint8)[: x.numel()]
+    assert np.array_equal(got, g[f"fp32_edge_{mode}"])
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_encode_layout_ragged_2d_and_cpu_input(fb, golden, mode):
+    g = golden("encode")
+    t = torch.from_numpy(sample_f32("lognormal", 31, 13).astype(np.float16))
+    w = fb.pack_fp8_tensor(t.cuda(), mode)
+    assert w.dtype == torch.uint32 and w.ndim == 1 and w.is_cuda
+    assert np.array_equal(host_words(w), g[f"ragged31_{mode}"])
+    assert np.array_equal(host_words(fb.pack_fp8_tensor(t[:28].reshape(7, 4).cuda(), mode)),
+                          g[f"matrix7x4_{mode}"])
+    w_cpu = fb.pack_fp8_tensor(t, mode)  # CPU in -> CPU out, as the reference returns
+    assert not w_cpu.is_cuda and np.array_equal(w_cpu.view(torch.int32).numpy().view(np.uint32),
+                                                g[f"ragged31_{mode}"])
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_encode_large_random_and_ragged_lengths_vs_oracle(fb, c_oracle, mode, dtype):
+    rng = np.random.default_rng(7)
+    bits = rng.integers(0, 2 ** 32, size=(1 << 22) + 77, dtype=np.uint64).astype(np.uint32)
+    x = bits.view(np.float32) if dtype == np.float32 else bits.view(np.float16)
+    xd = dev(x.copy())
+    assert np.array_equal(host_words(fb.pack_fp8_tensor(xd, mode)), c_oracle.pack(x, mode))
+    for n in (0, 1, 2, 3, 4, 5, 15, 16, 17, 63, 4099):
+        assert np.array_equal(host_words(fb.pack_fp8_tensor(xd[:n], mode)), c_oracle.pack(x[:n], mode))
+    # source not 16-byte aligned: takes the word-granular kernel
+    assert np.array_equal(host_words(fb.pack_fp8_tensor(xd[1:5001], mode)), c_oracle.pack(x[1:5001], mode))
+
+
+def test_encode_rejects(fb):
+    with pytest.raises(NotImplementedError):
+        fb.pack_fp8_tensor(torch.zeros(4, dtype=torch.float16, device="cuda"), "E3M4")
+    with pytest.raises(TypeError):
+        fb.pack_fp8_tensor(torch.zeros(4, dtype=torch.bfloat16, device="cuda"))
+
+
+# ------------------------------------------------------------------ decode --
+@pytest.mark.parametrize("mode", MODES)
+def test_decode_all_codes_all_lanes(fb, golden, mode):
+    g = golden("decode")
+    words = np.arange(256, dtype=np.uint8).view(np.uint32)  # every code, every byte lane
+    for sem in ("kernel", "ieee"):
+        got = fb.unpack_fp8_tensor(dev(words.copy()), mode, sem).cpu().numpy()
+        assert same_floats(got, O.decode_table(mode, sem))  # signed zeros included
+    assert same_floats(fb.unpack_fp8_tensor(dev(words.copy()), mode, "ieee").cpu().numpy(),
+                       g[f"ieee_{mode}"])
+    got = fb.unpack_fp8_tensor(dev(words.copy()), mode, "kernel").cpu().numpy()
+    with np.errstate(invalid="ignore"):
+        assert same_floats(got * np.float32(1) + np.float32(0), g[f"kernel_{mode}_lane0"])
+    # ragged element count and a large random buffer
+    rng = np.random.default_rng(8)
+    w = rng.integers(0, 2 ** 32, size=100003, dtype=np.uint64).astype(np.uint32)
+    for n in (1, 2, 3, 5, 400009):
+        got = fb.unpack_fp8_tensor(dev(w), mode, "kernel", n_elems=n).cpu().numpy()
+        assert same_floats(got, O.unpack(w, mode, "kernel", n))
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_gemv_uses_kernel_decode_for_every_code_and_lane(fb, golden, mode):
+    """The GEMV kernels themselves (fast and general path) multiply with the
+    reference kernel's decode: one code per row times 1.0, every byte lane."""
+    g = golden("decode")
+    one = {"E5M2": 0x3C, "E4M3": 0x38}[mode]
+    for lane in range(4):
+        ref = g[f"kernel_{mode}_lane{lane}"]
+        # general path: one word per row
+        mw = (np.arange(256, dtype=np.uint32) << (8 * lane))
+        vw = np.array([one << (8 * lane)], dtype=np.uint32)
+        got = fb.gemv_fp8_acc_fp32_gpu(dev(mw), dev(vw), (256, 4), mode).cpu().numpy()
+        assert same_floats(got, ref)
+        # streaming path: 256 rows x 1024 columns, the code at column 16*r + 4*j + lane
+        M, N = 256, 1024
+        m = np.zeros((M, N), dtype=np.uint8)
+        v = np.zeros(N, dtype=np.uint8)
+        cols = (np.arange(M) * 4 + lane) % N
+        m[np.arange(M), cols] = np.arange(256)
+        v[:] = one  # other columns hold code 0 -> +0 * 1.0
+        got = fb.gemv_fp8_acc_fp32_gpu(dev(m.reshape(-1).view(np.uint32)), dev(v.view(np.uint32)),
+                                       (M, N), mode).cpu().numpy()
+        assert same_floats(got, ref)
+
+
+# -------------------------------------------------------------------- gemv --
+@pytest.mark.parametrize("mode", MODES)
+def test_gemv_docstring_example(fb, golden, mode):
+    a = torch.tensor([[1, 1, -2, 0], [-3, -3, -2, -3], [0, 1, 1, -2], [2, 0, -1, 2]],
+                     dtype=torch.float16, device="cuda")
+    b = torch.tensor([2, 2, -1, 2], dtype=torch.float16, device="cuda")
+    fn = fb.gemv_fp8_e5m2_acc_fp32_gpu if mode == "E5M2" else fb.gemv_fp8_e4m3_acc_fp32_gpu
+    y = fn(fb.pack_fp8_tensor(a, mode), fb.pack_fp8_tensor(b, mode), a.shape)
+    assert y.dtype == torch.float32 and y.shape == (4,) and y.is_cuda
+    assert y.cpu().tolist() == [6.0, -16.0, -3.0, 9.0] == golden("gemv")[f"doc_{mode}"].tolist()
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("case", sorted(GEMV_CASES))
+def test_gemv_matches_reference_kernel_outputs(fb, golden, mode, case):
+    g = golden("gemv")
+    A, v = gemv_case(case)
+    mw, vw = fb.pack_fp8_tensor(dev(A), mode), fb.pack_fp8_tensor(dev(v), mode)
+    assert np.array_equal(host_words(mw), g[f"{case}_{mode}_m"])  # packed bytes bit-exact
+    assert np.array_equal(host_words(vw), g[f"{case}_{mode}_v"])
+    y = fb.gemv_fp8_acc_fp32_gpu(mw, vw, A.shape, mode).cpu().numpy()
+    ref = g[f"{case}_{mode}_out"]
+    if case.startswith("int"):
+        assert np.array_equal(y, ref)
+    else:
+        assert O.normalised_error(y, ref) < TOL
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_gemv_raw_bits_nonfinite_classes(fb, golden, mode):
+    g = golden("gemv")
+    y = fb.gemv_fp8_acc_fp32_gpu(dev(g["rawbits_m"]), dev(g["rawbits_v"]), (8, 2048), mode).cpu().numpy()
+    ref = g[f"rawbits_{mode}_out"]
+    assert np.array_equal(np.isnan(y), np.isnan(ref)) and np.array_equal(np.isinf(y), np.isinf(ref))
+    fin = np.isfinite(ref)
+    if fin.any():
+        assert O.normalised_error(y[fin], ref[fin]) < TOL
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("shape", [(1, 4), (3, 8), (17, 20), (5, 4100), (1, 16384), (2, 16),
+                                   (300, 2048), (1031, 4096), (40, 16400), (9, 32784), (64, 65536)])
+def test_gemv_edge_shapes_vs_oracle(fb, c_oracle, mode, shape):
+    rng = np.random.default_rng(shape[0] * 131 + shape[1])
+    A = rng.standard_normal(shape).astype(np.float16)
+    v = rng.standard_normal(shape[1]).astype(np.float16)
+    mw, vw = c_oracle.pack(A, mode), c_oracle.pack(v, mode)
+    y = fb.gemv_fp8_acc_fp32_gpu(dev(mw), dev(vw), shape, mode).cpu().numpy()
+    ref = c_oracle.gemv(mw, vw, shape, mode, acc="f64")
+    assert O.normalised_error(y, ref) < TOL
+    # matrix base not 16-byte aligned (a view one word into a larger buffer)
+    buf = dev(np.concatenate([np.zeros(1, np.uint32), mw]))
+    y2 = fb.gemv_fp8_acc_fp32_gpu(buf[1:], dev(vw), shape, mode).cpu().numpy()
+    assert O.normalised_error(y2, ref) < TOL
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("shape", [(4737, 4096), (5000, 16400), (4800, 32784), (4736, 65536),
+                                   (6001, 4112), (9999, 8192)])
+def test_gemv_ring_path_ragged_shapes_vs_oracle(fb, c_oracle, mode, shape):
+    """Shapes that take the bulk-copy ring kernel: row counts that leave partial
+    row blocks, rows that end inside a 4 KiB segment, several column tiles."""
+    M, N = shape
+    gen = torch.Generator(device="cuda").manual_seed(M + N)
+    A = torch.randn(M, N, device="cuda", generator=gen, dtype=torch.float16)
+    v = torch.randn(N, device="cuda", generator=gen, dtype=torch.float16)
+    mw, vw = fb.pack_fp8_tensor(A, mode), fb.pack_fp8_tensor(v, mode)
+    y = fb.gemv_fp8_acc_fp32_gpu(mw, vw, shape, mode).cpu().numpy()
+    ref = c_oracle.gemv(host_words(mw), host_words(vw), shape, mode, acc="f64")
+    assert O.normalised_error(y, ref) < TOL
+    fb.device_status()  # no bounded wait gave up
+
+
+def test_gemv_empty_and_rejects(fb):
+    z = torch.zeros(8, dtype=torch.int32, device="cuda")
+    assert fb.gemv_fp8_acc_fp32_gpu(z, z, (0, 8)).shape == (0,)
+    assert fb.gemv_fp8_acc_fp32_gpu(z, z, (5, 0)).tolist() == [0.0] * 5
+    with pytest.raises(ValueError):
+        fb.gemv_fp8_acc_fp32_gpu(z, z, (2, 6))          # N % 4 != 0
+    with pytest.raises(ValueError):
+        fb.gemv_fp8_acc_fp32_gpu(z, z[:1], (2, 16))     # vector too short
+    with pytest.raises(ValueError):
+        fb.gemv_fp8_acc_fp32_gpu(z.cpu(), z, (2, 16))   # no CPU path
+    with pytest.raises(NotImplementedError):
+        fb.gemv_fp8_acc_fp32_gpu(z, z, (2, 16), "E3M4")
+    with pytest.raises(TypeError):
+        fb.gemv(z, z)                                   # original_shape is required
+
+
+def test_readme_surface_and_mode_tag(fb):
+    import feather
+    torch.manual_seed(3)
+    a = torch.randn(64, 256, dtype=torch.float16, device="cuda")
+    b = torch.randn(256, dtype=torch.float16, device="cuda")
+    for mode in MODES:
+        mp = feather.pack_fp8_tensor(a, mode=mode).cuda()
+        vp = feather.pack_fp8_tensor(b, mode=mode).cuda()
+        assert mp.feather_mode == mode and mp.view(torch.uint32).feather_mode == mode
+        y = feather.gemv(mp, vp, original_shape=a.shape)  # mode comes from the packed operand
+        y2 = fb.gemv_fp8_acc_fp32_gpu(mp, vp, a.shape, mode)
+        assert torch.equal(y, y2)
+        d = feather.dot(vp, vp)
+        assert torch.equal(d, fb.dot_fp8_acc_fp32_gpu(vp, vp, mode))
+    from feather.packers.fp8 import pack_fp8_tensor
+    from feather.routines.dot import dot_fp8_e5m2_acc_fp32_gpu
+    from feather.routines.gemv import gemv_fp8_e4m3_acc_fp32_gpu, gemv_fp8_e5m2_acc_fp32_gpu
+    mp = pack_fp8_tensor(a, mode="E5M2").view(torch.uint32).to("cuda")  # as bench_gemv.py does
+    vp = pack_fp8_tensor(b, mode="E5M2").view(torch.uint32).to("cuda")
+    assert gemv_fp8_e5m2_acc_fp32_gpu(mp, vp, a.shape).shape == (64,)
+    assert gemv_fp8_e4m3_acc_fp32_gpu(mp.view(torch.int32), vp.view(torch.float32), a.shape).shape == (64,)
+    assert dot_fp8_e5m2_acc_fp32_gpu(vp, vp).ndim == 0
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_gemv_bench_gemv_integer_inputs_exact(fb, mode):
+    """feather/benchmark/bench_gemv.py:48-93: integer-valued inputs in [-3, 2]
+    are exact in both formats, so the result equals torch.mv exactly."""
+    torch.manual_seed(4)
+    for M, N in ((4096, 4096), (8192, 4096), (4096, 16384)):
+        a = torch.randint(-3, 3, (M, N), device="cuda").to(torch.float16)
+        b = torch.randint(-3, 3, (N,), device="cuda").to(torch.float16)
+        y = fb.gemv_fp8_acc_fp32_gpu(fb.pack_fp8_tensor(a, mode), fb.pack_fp8_tensor(b, mode),
+                                     a.shape, mode)
+        assert torch.equal(y, torch.mv(a.float(), b.float()))
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_gemv_config1_4096(fb, c_oracle, mode):
+    """seed 0, 4096 x 4096 fp16 N(0,1): packed bytes, decode round trip, GEMV."""
+    torch.manual_seed(0)
+    A = torch.randn(4096, 4096).half()
+    v = torch.randn(4096).half()
+    mw, vw = fb.pack_fp8_tensor(A.cuda(), mode), fb.pack_fp8_tensor(v.cuda(), mode)
+    mw_ref = c_oracle.pack(A.numpy(), mode)
+    assert np.array_equal(host_words(mw), mw_ref)
+    assert same_floats(fb.unpack_fp8_tensor(mw, mode).cpu().numpy(), c_oracle.unpack(mw_ref, mode))
+    y = fb.gemv_fp8_acc_fp32_gpu(mw, vw, A.shape, mode).cpu().numpy()
+    assert O.normalised_error(y, c_oracle.gemv(mw_ref, host_words(vw), A.shape, mode, acc="f64")) < TOL
+    assert O.normalised_error(y, c_oracle.gemv(mw_ref, host_words(vw), A.shape, mode)) < TOL
+
+
+def test_gemv_config2_e5m2_16384_full_size(fb, c_oracle):
+    torch.manual_seed(1)
+    M = N = 16384
+    A = torch.randn(M, N, dtype=torch.float16, device="cuda")
+    v = torch.randn(N, dtype=torch.float16, device="cuda")
+    mw, vw = fb.pack_fp8_tensor(A, "E5M2"), fb.pack_fp8_tensor(v, "E5M2")
+    mh, vh = host_words(mw), host_words(vw)
+    assert np.array_equal(mh[: 1 << 20], c_oracle.pack(A[:256].cpu().numpy(), "E5M2"))
+    y = fb.gemv_fp8_acc_fp32_gpu(mw, vw, (M, N), "E5M2").cpu().numpy()
+    assert O.normalised_error(y, c_oracle.gemv(mh, vh, (M, N), "E5M2", acc="f64")) < TOL
+    # linearity in the vector: scaling v by 2 (exact in FP8) doubles the result exactly
+    y2 = fb.gemv_fp8_acc_fp32_gpu(mw, fb.pack_fp8_tensor(v * 2, "E5M2"), (M, N), "E5M2").cpu().numpy()
+    assert np.array_equal(y2, 2 * y)
+
+
+@pytest.mark.parametrize("shape,seed", [((8192, 8192), 2), ((16384, 8192), 3), ((16384, 16384), 4)])
+def test_gemv_config3_e4m3_shape_sweep(fb, c_oracle, shape, seed):
+    """fp32 matrices: 90 % 4*N(0,1), 5 % E4M3-subnormal magnitudes, 5 % beyond
+    saturation; E4M3 packed.  Generated on the device (same recipe as
+    c3_matrix) because the full-size host generator is slow."""
+    M, N = shape
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    x = 4.0 * torch.randn(M, N, device="cuda", generator=gen)
+    u = torch.rand(M, N, device="cuda", generator=gen)
+    sign = torch.where(torch.rand(M, N, device="cuda", generator=gen) < 0.5, -1.0, 1.0)
+    r = torch.rand(M, N, device="cuda", generator=gen)
+    small = sign * (2.0 ** -9 + r * (2.0 ** -6 - 2.0 ** -9))
+    big = sign * (448.0 + r * (1000.0 - 448.0))
+    x = torch.where(u < 0.05, small, torch.where(u < 0.10, big, x))
+    del u, sign, r, small, big
+    v = torch.randn(N, device="cuda", generator=gen)
+    mw, vw = fb.pack_fp8_tensor(x, "E4M3"), fb.pack_fp8_tensor(v, "E4M3")
+    mh, vh = host_words(mw), host_words(vw)
+    assert np.array_equal(mh[: 1 << 18], c_oracle.pack(x.reshape(-1)[: 1 << 20].cpu().numpy(), "E4M3"))
+    codes = mh[: 1 << 20].view(np.uint8)
+    assert ((codes & 0x7F) == 0x7F).mean() > 0.02 and ((codes & 0x78) == 0).mean() > 0.03
+    y = fb.gemv_fp8_acc_fp32_gpu(mw, vw, shape, "E4M3").cpu().numpy()
+    assert O.normalised_error(y, c_oracle.gemv(mh, vh, shape, "E4M3", acc="f64")) < TOL
+
+
+def test_gemv_65536_sampled_rows(fb, c_oracle):
+    """4 GiB packed matrix (the row-sharded configuration on one GPU): rows are
+    generated and packed block by block on the device; 2048 sampled rows are
+    checked against the oracle."""
+    M = N = 65536
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    v = torch.randn(N, device="cuda", generator=gen).half()
+    vw = fb.pack_fp8_tensor(v, "E5M2")
+    mw = torch.empty(M * (N // 4), dtype=torch.int32, device="cuda").view(torch.uint32)
+    blk = 4096
+    for r0 in range(0, M, blk):
+        a = torch.randn(blk, N, device="cuda", generator=gen, dtype=torch.float16)
+        mw[r0 * (N // 4):(r0 + blk) * (N // 4)] = fb.pack_fp8_tensor(a, "E5M2")
+    del a
+    y = fb.gemv_fp8_acc_fp32_gpu(mw, vw, (M, N), "E5M2")
+    rows = torch.from_numpy(np.random.default_rng(5).choice(M, 2048, replace=False)).cuda()
+    sub = mw.view(torch.int32).view(M, N // 4)[rows].contiguous()
+    ref = c_oracle.gemv(sub.cpu().numpy().view(np.uint32), host_words(vw), (2048, N), "E5M2", acc="f64")
+    assert O.normalised_error(y[rows].cpu().numpy(), ref) < TOL
+    # a contiguous row block computed alone (what one rank of a sharded run does)
+    # gives bit-identical values: rows never interact
+    y_blk = fb.gemv_fp8_acc_fp32_gpu(mw[8192 * (N // 4): 2 * 8192 * (N // 4)], vw, (8192, N), "E5M2")
+    assert torch.equal(y_blk, y[8192:16384])
+
+
+# --------------------------------------------------------------------- dot --
+def test_dot_golden_and_docstring(fb, golden):
+    g = golden("dot")
+    a = fb.pack_fp8_tensor(torch.tensor([2, 0, -3, 1], dtype=torch.float16, device="cuda"))
+    b = fb.pack_fp8_tensor(torch.tensor([-1, 0, -3, 1], dtype=torch.float16, device="cuda"))
+    d = fb.dot_fp8_e5m2_acc_fp32_gpu(a, b)
+    assert d.ndim == 0 and d.dtype == torch.float32 and d.item() == 8.0 == float(g["doc"])
+    for n, seed in DOT_CASES:
+        x1, x2 = dot_case(n, seed)
+        aw, bw = fb.pack_fp8_tensor(dev(x1)), fb.pack_fp8_tensor(dev(x2))
+        ah, bh = host_words(aw), host_words(bw)
+        sums = np.array([ah.astype(np.uint64).sum(), bh.astype(np.uint64).sum()], dtype=np.uint64)
+        assert np.array_equal(sums, g[f"n{n}_wordsum"])
+        scale = float(np.abs(O.unpack(ah) * O.unpack(bh)).sum())
+        assert abs(fb.dot_fp8_e5m2_acc_fp32_gpu(aw, bw).item() - float(g[f"n{n}_out"])) / scale < TOL
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_dot_sizes_alignment_determinism(fb, c_oracle, mode):
+    rng = np.random.default_rng(9)
+    for n_words in (0, 1, 3, 4, 5, 1023, 1024, 4097, (1 << 20) + 3):
+        a = rng.integers(0, 2 ** 32, size=n_words + 1, dtype=np.uint64).astype(np.uint32)
+        b = rng.integers(0, 2 ** 32, size=n_words + 1, dtype=np.uint64).astype(np.uint32)
+        # keep values finite: clear the top exponent bit of every code
+        a &= 0xBFBFBFBF
+        b &= 0xBFBFBFBF
+        ad, bd = dev(a), dev(b)
+        for off in (0, 1):  # off=1: operands are not 16-byte aligned
+            aw, bw = ad[off:off + n_words], bd[off:off + n_words]
+            got = fb.dot_fp8_acc_fp32_gpu(aw, bw, mode).item()
+            ref = float(c_oracle.dot(a[off:off + n_words], b[off:off + n_words], mode, acc="f64"))
+            scale = float(np.abs(O.unpack(a[off:off + n_words], mode).astype(np.float64) *
+                                 O.unpack(b[off:off + n_words], mode)).sum()) or 1.0
+            assert abs(got - ref) / scale < TOL
+            assert fb.dot_fp8_acc_fp32_gpu(aw, bw, mode).item() == got  # same bits every run
+
+
+def test_dot_config2_two_pow_26(fb, c_oracle):
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    n = 1 << 26
+    x1 = torch.randn(n, device="cuda", generator=gen).half()
+    x2 = torch.randn(n, device="cuda", generator=gen).half()
+    aw, bw = fb.pack_fp8_tensor(x1), fb.pack_fp8_tensor(x2)
+    ah, bh = host_words(aw), host_words(bw)
+    got = fb.dot_fp8_e5m2_acc_fp32_gpu(aw, bw).item()
+    ref = float(c_oracle.dot(ah, bh, "E5M2", acc="f64"))
+    scale = float((x1.float().abs() * x2.float().abs()).sum().item())
+    assert abs(got - ref) / scale < TOL
+    assert fb.dot_fp8_e5m2_acc_fp32_gpu(aw, bw).item() == got
+
+
+# ------------------------------------------------------------------- C ABI --
+def test_c_abi_status_codes_on_device(fb):
+    lib = fb._lib.load()
+    z = torch.zeros(64, dtype=torch.int32, device="cuda")
+    o = torch.zeros(8, dtype=torch.float32, device="cuda")
+    p, po = z.data_ptr(), o.data_ptr()
+    assert lib.feather_gemv_fp8(p, p, po, 2, 16, 0, None) == 0
+    assert lib.feather_gemv_fp8(p, p, po, 2, 18, 0, None) == -1
+    assert lib.feather_gemv_fp8(p, p, po, 2, 16, 7, None) == -3
+    assert lib.feather_gemv_fp8(p + 2, p, po, 2, 16, 0, None) == -2
+    assert lib.feather_gemv_fp8(None, p, po, 2, 16, 0, None) == -1
+    assert lib.feather_dot_fp8(p, p, po, None, 4, 0, None) == -6
+    assert lib.feather_encode_fp8(po, 5, p, 4, 0, None) == -3
+    assert lib.feather_decode_fp8(p, po, 4, 0, 9, None) == -3
+    assert lib.feather_device_status(None) == 0
+    torch.cuda.synchronize()

@@ -1,0 +1,104 @@
+"""Row-sharded GEMV plumbing on CPU ranks (gloo, world size 2).
+
+The CUDA kernel cannot run here, so the oracle GEMV is injected as the local
+compute; what is tested is the partition, the agreement check, the in-place
+gather and the error paths.
+"""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _oracle_local_gemv(m_local, v_packed, shape, mode, out):
+    from oracle import feather_oracle as O
+    y = O.gemv(m_local.numpy().view(np.uint32), v_packed.numpy().view(np.uint32), shape, mode)
+    out.copy_(torch.from_numpy(y))
+    return out
+
+
+def _worker(rank: int, world: int, port: int, case: str, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from feather_b200.sharded import RowShardedGemv, local_words
+        from oracle import feather_oracle as O
+        rng = np.random.default_rng(42)  # same data on every rank
+        M, N, mode = 24, 520, "E4M3"
+        A = rng.standard_normal((M, N)).astype(np.float16)
+        v = rng.standard_normal(N).astype(np.float16)
+        mw = torch.from_numpy(O.pack_fp8_ndarray(A, mode).view(np.int32))
+        vw = torch.from_numpy(O.pack_fp8_ndarray(v, mode).view(np.int32))
+        if case == "ok":
+            op = RowShardedGemv(local_words(mw, (M, N), world, rank), (M, N), mode,
+                                local_gemv=_oracle_local_gemv)
+            y = op(vw)
+            ref = O.gemv(mw.numpy().view(np.uint32), vw.numpy().view(np.uint32), (M, N), mode)
+            q.put((rank, bool(np.array_equal(y.numpy(), ref)), op.row_begin, op.row_end))
+        elif case == "disagree":
+            shape = (M, N) if rank == 0 else (M, N)
+            mode_r = mode if rank == 0 else "E5M2"
+            try:
+                RowShardedGemv(local_words(mw, shape, world, rank), shape, mode_r,
+                               local_gemv=_oracle_local_gemv)
+                q.put((rank, "no error"))
+            except ValueError as e:
+                q.put((rank, "ValueError" if "disagree" in str(e) else str(e)))
+        elif case == "wrong_block":
+            try:
+                RowShardedGemv(mw[:17], (M, N), mode, local_gemv=_oracle_local_gemv)
+                q.put((rank, "no error"))
+            except ValueError:
+                q.put((rank, "ValueError"))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(case: str, world: int = 2):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, case, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    return sorted(out)
+
+
+def test_row_sharded_gemv_matches_single_rank():
+    res = _run("ok")
+    assert res == [(0, True, 0, 12), (1, True, 12, 24)]
+
+
+def test_ranks_that_disagree_raise():
+    assert _run("disagree") == [(0, "ValueError"), (1, "ValueError")]
+
+
+def test_wrong_local_block_raises():
+    assert _run("wrong_block") == [(0, "ValueError"), (1, "ValueError")]
+
+
+def test_row_block_partition():
+    from feather_b200.sharded import row_block
+    assert [row_block(65536, 8, r) for r in (0, 7)] == [(0, 8192), (57344, 65536)]
+    with pytest.raises(ValueError):
+        row_block(10, 4, 0)      # not divisible
+    with pytest.raises(ValueError):
+        row_block(8, 4, 4)       # rank out of range
