@@ -26,6 +26,8 @@ SYMBOLS = {
     "feather_device_status": (_i32, [_vp]),
     "feather_dot_fp8": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _vp]),
     "feather_dot_workspace_bytes": (_i64, [_i64]),
+    "feather_dot_fp8_static": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
+    "feather_dot_fp8_static_max_words": (_i64, []),
 }
 
 _lib = None
@@ -78,7 +80,7 @@ def check(status: int) -> None:
     if status == 0:
         return
     msg = load().feather_strerror(status).decode()
-    if status in (-1, -2, -6):
+    if status in (-1, -2, -6, -8):
         raise ValueError(f"libfeather_b200: {msg} (status {status})")
     if status == -7:
         raise FeatherError(status, msg + " (a device-side wait timed out; results are undefined)")

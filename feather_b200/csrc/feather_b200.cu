@@ -273,6 +273,58 @@ static int dot_launch(const uint32_t* a, const uint32_t* b, float* out, void* wo
     return launch_status();
 }
 
+// ---------------------------------------------------- dot without allocation --
+// Scratch of feather_dot_fp8_static: the ticket counter (first 16 bytes) and one
+// partial sum per CTA.  It lives in the library image, so every GPU that loads
+// the library holds these few KiB until the process exits, and every call on a
+// device shares it.
+constexpr int kStaticDotSlots = 1024;                 // CTAs (= partial sums) at most
+constexpr long long kStaticDotMaxWords = 1ll << 28;   // 1 GiB of codes per operand
+constexpr int kStaticDotPartialOffset = 256;
+static __device__ __align__(256) unsigned char g_dot_scratch[kStaticDotPartialOffset + 4 * kStaticDotSlots];
+
+// Device address of g_dot_scratch on the current device.  In host code the
+// array's name is only a handle for the runtime, not a pointer a kernel could
+// use, so the address is asked for once per device (with that device current)
+// and remembered.
+static int static_dot_scratch(unsigned char** ptr) {
+    static std::atomic<unsigned char*> cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FEATHER_ERR_LAUNCH;
+    unsigned char* p = cached[dev].load(std::memory_order_acquire);
+    if (!p) {
+        if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_dot_scratch) != cudaSuccess || !p)
+            return FEATHER_ERR_LAUNCH;
+        cached[dev].store(p, std::memory_order_release);
+    }
+    *ptr = p;
+    return FEATHER_OK;
+}
+
+template <int MODE>
+static int dot_static_launch(const uint32_t* a, const uint32_t* b, float* out, long long n_words,
+                             const DeviceInfo& dev, cudaStream_t s) {
+    unsigned char* scratch = nullptr;
+    if (int st = static_dot_scratch(&scratch)) return st;
+    // The array keeps whatever the previous call left.  The partial sums are
+    // all rewritten before they are read; the ticket must start at zero.
+    if (cudaMemsetAsync(scratch, 0, 16, s) != cudaSuccess) return FEATHER_ERR_LAUNCH;
+    unsigned int* ticket = reinterpret_cast<unsigned int*>(scratch);
+    float* partial = reinterpret_cast<float*>(scratch + kStaticDotPartialOffset);
+    long long grid = (long long)dev.sm_count * 4;
+    const long long need = (n_words / 4 + kDotThreads - 1) / kDotThreads;
+    if (grid > need) grid = need;
+    if (grid < 1) grid = 1;
+    if (grid > kStaticDotSlots) grid = kStaticDotSlots;
+    if (aligned(a, 16) && aligned(b, 16))
+        dot_kernel<MODE, true, 4><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket, partial,
+                                                                          n_words);
+    else
+        dot_kernel<MODE, false, 1><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket,
+                                                                           partial, n_words);
+    return launch_status();
+}
+
 }  // namespace feather
 
 using namespace feather;
@@ -291,6 +343,7 @@ const char* feather_strerror(int status) {
         case FEATHER_ERR_LAUNCH: return "CUDA reported an error at launch";
         case FEATHER_ERR_WORKSPACE: return "workspace is missing or too small";
         case FEATHER_ERR_TIMEOUT: return "a bounded device-side wait gave up";
+        case FEATHER_ERR_TOO_LARGE: return "size exceeds what the built-in scratch of the no-allocation entry point covers";
         default: return "unknown feather status";
     }
 }
@@ -386,6 +439,22 @@ int feather_dot_fp8(const uint32_t* a, const uint32_t* b, float* out, void* work
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return mode == FEATHER_MODE_E5M2 ? dot_launch<kE5M2>(a, b, out, workspace, n_words, *dev, s)
                                      : dot_launch<kE4M3>(a, b, out, workspace, n_words, *dev, s);
+}
+
+int64_t feather_dot_fp8_static_max_words(void) { return kStaticDotMaxWords; }
+
+int feather_dot_fp8_static(const uint32_t* a, const uint32_t* b, float* out, int64_t n_words,
+                           int mode, void* stream) {
+    if (n_words < 0) return FEATHER_ERR_BAD_ARG;
+    if (mode != FEATHER_MODE_E5M2 && mode != FEATHER_MODE_E4M3) return FEATHER_ERR_MODE;
+    if (n_words > kStaticDotMaxWords) return FEATHER_ERR_TOO_LARGE;
+    if (!out || (n_words > 0 && (!a || !b))) return FEATHER_ERR_BAD_ARG;
+    if (!aligned(a, 4) || !aligned(b, 4) || !aligned(out, 4)) return FEATHER_ERR_MISALIGNED;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return mode == FEATHER_MODE_E5M2 ? dot_static_launch<kE5M2>(a, b, out, n_words, *dev, s)
+                                     : dot_static_launch<kE4M3>(a, b, out, n_words, *dev, s);
 }
 
 }  // extern "C"

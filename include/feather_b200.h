@@ -34,7 +34,8 @@ typedef enum feather_status {
     FEATHER_ERR_ARCH = -4,        /* current device is not compute capability 10.x */
     FEATHER_ERR_LAUNCH = -5,      /* CUDA reported a launch error               */
     FEATHER_ERR_WORKSPACE = -6,   /* workspace missing or too small             */
-    FEATHER_ERR_TIMEOUT = -7      /* a bounded device-side wait gave up         */
+    FEATHER_ERR_TIMEOUT = -7,     /* a bounded device-side wait gave up         */
+    FEATHER_ERR_TOO_LARGE = -8    /* beyond the built-in scratch of a *_static call */
 } feather_status;
 
 #define FEATHER_MODE_E5M2 0
@@ -124,6 +125,36 @@ int feather_device_status(void* stream);
 int feather_dot_fp8(const uint32_t* a, const uint32_t* b, float* out, void* workspace,
                     int64_t n_words, int mode, void* stream);
 int64_t feather_dot_workspace_bytes(int64_t n_words);
+
+/*
+ * feather_dot_fp8 for callers that cannot hand over a workspace because they
+ * cannot allocate device memory at all.  It has no counterpart in the
+ * reference.  Such callers exist: code that runs from a host callback queued
+ * on a stream (the CUDA runtime forbids allocation calls there), a plug-in
+ * inside a serving process whose device memory was given whole to another
+ * allocator at start-up, or a latency-critical loop that must not take
+ * cudaMalloc's device-wide synchronisation.  For them the scratch the kernel
+ * needs (a ticket counter and one partial sum per CTA, about 4 KiB) is a fixed
+ * array inside the library image instead of an argument; this call performs no
+ * cudaMalloc, cudaFree or any other allocating routine.
+ *
+ *   a, b, out, n_words, mode, stream   as feather_dot_fp8
+ *   limit    n_words <= feather_dot_fp8_static_max_words() (2^28 words, i.e.
+ *            1 GiB of codes per operand); larger sizes return
+ *            FEATHER_ERR_TOO_LARGE and launch nothing
+ *
+ * The array costs every GPU that loads the library those few KiB until the
+ * process exits.  The first call on a device looks up the array's device
+ * address (once per device); make that first call outside any stream capture.
+ * All calls on a device share the one array: it still holds what the previous
+ * call left (the call clears the part that must start at zero itself), and two
+ * calls that can overlap on the GPU (different streams, no ordering between
+ * them) race on it.  Serialise them, or use feather_dot_fp8 with one
+ * workspace per stream.
+ */
+int feather_dot_fp8_static(const uint32_t* a, const uint32_t* b, float* out, int64_t n_words,
+                           int mode, void* stream);
+int64_t feather_dot_fp8_static_max_words(void);
 
 #ifdef __cplusplus
 }
