@@ -135,7 +135,7 @@ def cpu_gemv_gbps(M: int, N: int, mode: str, budget_s: float, seed: int = 1):
 
     from oracle import c_oracle as C
     C.build()
-    threads = C.num_threads()
+    threads = C.use_all_cores()
     rng = np.random.default_rng(seed)
     rows = min(M, 2048)
     A = rng.standard_normal((rows, N)).astype(np.float16)
@@ -171,7 +171,7 @@ def run_reference(args) -> None:
 
     from oracle import c_oracle as C
     C.build()
-    threads = C.num_threads()
+    threads = C.use_all_cores()
     rng = np.random.default_rng(1)
     # bounded sample: rows chosen so that warmup + steps end within ~2 minutes
     rows = min(M, 4096)
@@ -314,11 +314,11 @@ def run_ours(args) -> None:
     if world == 1:
         kern_ms = ms_per_step
         kern_bytes = step_bytes
-        kern_name = "gemv_stream_kernel<E5M2>"
+        kern_name = "gemv_ring_kernel<E5M2>"
     else:
         kern_ms = time_calls(torch, lambda: op.local(vw), max(20, K), 5)
         kern_bytes = gemv_bytes(M // world, N)
-        kern_name = "gemv_stream_kernel<E5M2> (per-rank block)"
+        kern_name = "gemv_ring_kernel<E5M2> (per-rank block)"
     achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": kern_name, "achieved": round(achieved, 1),
                 "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",

@@ -37,6 +37,7 @@ def load():
         lib = ctypes.CDLL(_LIB)
         vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
         lib.fo_num_threads.restype = i32
+        lib.fo_set_num_threads.argtypes = [i32]
         lib.fo_encode.argtypes = [vp, i32, vp, i64, i32]
         lib.fo_pack.argtypes = [vp, i32, vp, i64, i32]
         lib.fo_decode_table.argtypes = [vp, i32, i32]
@@ -61,6 +62,16 @@ def _ptr(a: np.ndarray) -> ctypes.c_void_p:
 
 def num_threads() -> int:
     return int(load().fo_num_threads())
+
+
+def use_all_cores() -> int:
+    """Run on every core this process may use, whatever OMP_NUM_THREADS says."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    load().fo_set_num_threads(n)
+    return num_threads()
 
 
 def pack(x: np.ndarray, mode: str = "E5M2") -> np.ndarray:

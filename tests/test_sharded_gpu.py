@@ -1,0 +1,83 @@
+"""Row-sharded GEMV on real GPUs (NCCL).  World size 1 always runs; world size
+2 runs when the box has two GPUs."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    try:
+        dist.init_process_group("nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", rank))
+    except Exception as e:  # e.g. the rendezvous port was taken: report, do not stall the parent
+        q.put((rank, "init failed", repr(e)))
+        return
+    try:
+        import feather_b200 as fb
+        from feather_b200.sharded import RowShardedGemv, local_words
+        from oracle import c_oracle as C
+        from oracle import feather_oracle as O
+        M, N, mode = 9472, 8192, "E4M3"   # 4736 rows per rank at world 2: the ring kernel
+        gen = torch.Generator(device="cuda").manual_seed(77)  # same data on every rank
+        A = torch.randn(M, N, device="cuda", generator=gen, dtype=torch.float16)
+        v = torch.randn(N, device="cuda", generator=gen, dtype=torch.float16)
+        mw, vw = fb.pack_fp8_tensor(A, mode), fb.pack_fp8_tensor(v, mode)
+        op = RowShardedGemv(local_words(mw, (M, N), world, rank), (M, N), mode)
+        y = op(vw)
+        y_single = fb.gemv_fp8_acc_fp32_gpu(mw, vw, (M, N), mode)
+        host = lambda t: t.view(torch.int32).cpu().numpy().view(np.uint32)
+        ref = C.gemv(host(mw), host(vw), (M, N), mode, acc="f64")
+        err = O.normalised_error(y.cpu().numpy(), ref)
+        # rows never interact, so the sharded result has the single-GPU bits
+        q.put((rank, bool(torch.equal(y, y_single)), err < 1e-5))
+        fb.device_status()
+    except Exception as e:
+        q.put((rank, "failed", repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(world: int):
+    ctx = mp.get_context("spawn")
+    for attempt in range(3):  # a rendezvous port can be taken between probing and binding
+        q = ctx.Queue()
+        port = _free_port()
+        procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+        for p in procs:
+            p.start()
+        out = [q.get(timeout=180) for _ in range(world)]
+        for p in procs:
+            p.join(timeout=60)
+        if any(o[1] == "init failed" for o in out) and attempt < 2:
+            continue
+        return sorted(out)
+
+
+def test_row_sharded_world_1():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    assert _run(1) == [(0, True, True)]
+
+
+def test_row_sharded_world_2():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    assert _run(2) == [(0, True, True), (1, True, True)]
