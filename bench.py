@@ -36,10 +36,10 @@ METRIC = "packed_fp8_gemv_hbm_gbps"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes per launch of gemv_stream_kernel at 16384 x 16384 from an ncu
-# capture (dram__bytes_read.sum + dram__bytes_write.sum, profiles/); None until
-# a capture exists.
-NCU_TRAFFIC_BYTES_16384 = None
+# DRAM bytes per launch of gemv_ring_kernel<E5M2> at 16384 x 16384 from an ncu
+# capture: dram__bytes_read.sum 268 475 136 + dram__bytes_write.sum 3 669 248
+# (profiles/gemv_ring_e5m2_16384x16384.md).
+NCU_TRAFFIC_BYTES_16384 = 272144384
 
 
 def gemv_bytes(M: int, N: int) -> int:
@@ -280,12 +280,14 @@ def run_ours(args) -> None:
         m_local = make_packed(rows, N, 5 + rank, mode)
         gen.manual_seed(5)
         vw = fb.pack_fp8_tensor(torch.randn(N, device=dev, generator=gen, dtype=torch.float16), mode)
-        op = RowShardedGemv(m_local, (M, N), mode)
+        op = RowShardedGemv(m_local, (M, N), mode)  # fused peer-store exchange when available
         step_bytes = gemv_bytes(M, N)
 
         def step():
             op(vw)
         l2_note = f"per-rank block {rows * N >> 20} MiB, larger than L2"
+        extra["exchange"] = ("fused into the GEMV kernel (peer stores over NVLink)" if op.fused
+                             else "NCCL all-gather after the local GEMV")
 
     # ---- the timed region: W warm-up steps, then exactly K steps -----------
     for _ in range(W):
@@ -318,6 +320,13 @@ def run_ours(args) -> None:
     else:
         kern_ms = time_calls(torch, lambda: op.local(vw), max(20, K), 5)
         kern_bytes = gemv_bytes(M // world, N)
+        if op.fused:  # the same step with the separate NCCL all-gather, for comparison
+            op_nccl = RowShardedGemv(m_local, (M, N), mode, fused=False)
+            ms_nccl = time_calls(torch, lambda: op_nccl(vw), max(20, K), 5)
+            t = torch.tensor([ms_nccl], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            extra["same_step_with_nccl_all_gather_us"] = round(float(t.item()) * 1e3, 3)
+        extra["local_gemv_kernel_us"] = round(kern_ms * 1e3, 3)
         kern_name = "gemv_ring_kernel<E5M2> (per-rank block)"
     achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": kern_name, "achieved": round(achieved, 1),

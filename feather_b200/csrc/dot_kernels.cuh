@@ -10,6 +10,7 @@
 #pragma once
 #include "fp8_codec.cuh"
 #include "gemv_kernels.cuh"  // ldg_stream, warp_sum
+#include "gemv_ring.cuh"     // decode_word_h2, fma_h2
 
 namespace feather {
 
@@ -17,13 +18,16 @@ constexpr int kDotThreads = 256;
 constexpr int kDotMaxCtas = 2048;  // partial slots in the workspace
 constexpr int kDotWorkspaceBytes = 16 + 4 * kDotMaxCtas;
 
+// Four code pairs: both words decoded to FP16 pairs, multiplied with the
+// mixed-precision FMA (FP16 operands, FP32 accumulate; the product of two FP16
+// values is exact in FP32).
 template <int MODE>
-__device__ __forceinline__ void dot_words(uint32_t wa, uint32_t wb, float2& a0, float2& a1) {
-    float2 alo, ahi, blo, bhi;
-    decode_word<MODE>(wa, alo, ahi);
-    decode_word<MODE>(wb, blo, bhi);
-    a0 = __ffma2_rn(alo, blo, a0);
-    a1 = __ffma2_rn(ahi, bhi, a1);
+__device__ __forceinline__ void dot_words(uint32_t wa, uint32_t wb, float (&acc)[4]) {
+    uint32_t alo, ahi, blo, bhi;
+    decode_word_h2<MODE>(wa, alo, ahi);
+    decode_word_h2<MODE>(wb, blo, bhi);
+    fma_h2(alo, blo, acc[0], acc[1]);
+    fma_h2(ahi, bhi, acc[2], acc[3]);
 }
 
 // a, b: n_words words.  VEC: both pointers are 16-byte aligned, so whole
@@ -34,46 +38,46 @@ dot_kernel(const uint32_t* __restrict__ a, const uint32_t* __restrict__ b, float
            unsigned int* __restrict__ ticket, float* __restrict__ partial, long long n_words) {
     __shared__ float warp_part[kDotThreads / 32];
     __shared__ bool is_last;
-    float2 acc0 = make_float2(0.f, 0.f), acc1 = acc0;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
     const long long tid = (long long)blockIdx.x * kDotThreads + threadIdx.x;
     const long long n_threads = (long long)gridDim.x * kDotThreads;
 
     long long done_words = 0;
     if (VEC) {
+        // Grid-stride over 16-byte chunks; a thread keeps UNROLL chunks of each
+        // operand in flight.  Chunks past the end are replaced by zero words
+        // (code 0 decodes to +0.0), so there is no remainder loop.
         const long long n_chunks = n_words >> 2;
         const uint4* a4 = reinterpret_cast<const uint4*>(a);
         const uint4* b4 = reinterpret_cast<const uint4*>(b);
-        long long c = tid;
-        // UNROLL chunks of each operand in flight per thread
-        for (; c + (UNROLL - 1) * n_threads < n_chunks; c += UNROLL * n_threads) {
+        for (long long c = tid; c < n_chunks; c += UNROLL * n_threads) {
             uint4 xa[UNROLL], xb[UNROLL];
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
-                xa[u] = ldg_stream(a4 + c + u * n_threads);
-                xb[u] = ldg_stream(b4 + c + u * n_threads);
+                const long long cu = c + u * n_threads;
+                if (cu < n_chunks) {
+                    xa[u] = ldg_stream(a4 + cu);
+                    xb[u] = ldg_stream(b4 + cu);
+                } else {
+                    xa[u] = make_uint4(0, 0, 0, 0);
+                    xb[u] = make_uint4(0, 0, 0, 0);
+                }
             }
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
-                dot_words<MODE>(xa[u].x, xb[u].x, acc0, acc1);
-                dot_words<MODE>(xa[u].y, xb[u].y, acc0, acc1);
-                dot_words<MODE>(xa[u].z, xb[u].z, acc0, acc1);
-                dot_words<MODE>(xa[u].w, xb[u].w, acc0, acc1);
+                dot_words<MODE>(xa[u].x, xb[u].x, acc);
+                dot_words<MODE>(xa[u].y, xb[u].y, acc);
+                dot_words<MODE>(xa[u].z, xb[u].z, acc);
+                dot_words<MODE>(xa[u].w, xb[u].w, acc);
             }
-        }
-        for (; c < n_chunks; c += n_threads) {
-            const uint4 xa = ldg_stream(a4 + c), xb = ldg_stream(b4 + c);
-            dot_words<MODE>(xa.x, xb.x, acc0, acc1);
-            dot_words<MODE>(xa.y, xb.y, acc0, acc1);
-            dot_words<MODE>(xa.z, xb.z, acc0, acc1);
-            dot_words<MODE>(xa.w, xb.w, acc0, acc1);
         }
         done_words = n_chunks << 2;
     }
     for (long long w = done_words + tid; w < n_words; w += n_threads)
-        dot_words<MODE>(__ldg(a + w), __ldg(b + w), acc0, acc1);
+        dot_words<MODE>(__ldg(a + w), __ldg(b + w), acc);
 
     // CTA partial: lanes -> warp (shuffles) -> CTA (fixed order over warps)
-    const float s = warp_sum((acc0.x + acc0.y) + (acc1.x + acc1.y));
+    const float s = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) warp_part[warp] = s;
     __syncthreads();

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstring>
 
 #include "../../include/feather_b200.h"
 #include "dot_kernels.cuh"
@@ -200,11 +201,12 @@ static int ensure_smem(K kernel, int smem, std::atomic<unsigned long long>& conf
     return FEATHER_OK;
 }
 
-template <int MODE>
+template <int MODE, bool FUSED>
 static int gemv_ring_launch(const uint32_t* m, const uint32_t* v, float* out, long long M,
-                            long long N, const DeviceInfo& dev, cudaStream_t s) {
+                            long long N, const DeviceInfo& dev, cudaStream_t s,
+                            const ShardArgs& shard) {
     using G = RingGeometry<kRingCW, kRingRW, kRingCL, kRingStages, kRingTile>;
-    auto kernel = gemv_ring_kernel<MODE, kRingCW, kRingRW, kRingCL, kRingStages, kRingTile, 1, false>;
+    auto kernel = gemv_ring_kernel<MODE, kRingCW, kRingRW, kRingCL, kRingStages, kRingTile, 1, false, FUSED>;
     static std::atomic<unsigned long long> configured{0};
     if (int st = ensure_smem(kernel, G::kSmemBytes, configured)) return st;
     unsigned int* status = nullptr;
@@ -223,17 +225,23 @@ static int gemv_ring_launch(const uint32_t* m, const uint32_t* v, float* out, lo
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const unsigned char*>(m),
-                                             v, out, (int)M, (int)(N / 16), status);
+                                             v, out, (int)M, (int)(N / 16), status, shard);
     return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
+}
+
+// Shapes the bulk-copy ring kernel takes: 16-byte aligned rows, rows long
+// enough for 4 KiB copies, and at least two full tasks for every SM.
+static bool ring_eligible(const void* m, long long M, long long N, const DeviceInfo& dev) {
+    return (N % 16 == 0) && aligned(m, 16) && N >= 4096 &&
+           M >= 2ll * dev.sm_count * kRingCW * kRingRW;
 }
 
 template <int MODE>
 static int gemv_launch(const uint32_t* m, const uint32_t* v, float* out, long long M, long long N,
                        const DeviceInfo& dev, cudaStream_t s) {
     const bool vec_ok = (N % 16 == 0) && aligned(m, 16);
-    // ring: every SM gets at least two full tasks and rows are long enough for 4 KiB copies
-    if (vec_ok && N >= 4096 && M >= 2ll * dev.sm_count * kRingCW * kRingRW)
-        return gemv_ring_launch<MODE>(m, v, out, M, N, dev, s);
+    if (ring_eligible(m, M, N, dev))
+        return gemv_ring_launch<MODE, false>(m, v, out, M, N, dev, s, ShardArgs{});
     const bool fast = vec_ok && M * (N / 16) >= 4096;
     if (!fast) {
         const long long blocks = (M + 7) / 8;  // 8 warps per CTA, one row per warp
@@ -259,13 +267,13 @@ static int dot_launch(const uint32_t* a, const uint32_t* b, float* out, void* wo
                       long long n_words, const DeviceInfo& dev, cudaStream_t s) {
     unsigned int* ticket = reinterpret_cast<unsigned int*>(workspace);
     float* partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 16);
-    long long grid = (long long)dev.sm_count * 4;
+    long long grid = (long long)dev.sm_count * 6;  // measured best on B200 (sweep 2..12 per SM)
     const long long need = (n_words / 4 + kDotThreads - 1) / kDotThreads;
     if (grid > need) grid = need;
     if (grid < 1) grid = 1;
     if (grid > kDotMaxCtas) grid = kDotMaxCtas;
     if (aligned(a, 16) && aligned(b, 16))
-        dot_kernel<MODE, true, 4><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket, partial,
+        dot_kernel<MODE, true, 1><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket, partial,
                                                                           n_words);
     else
         dot_kernel<MODE, false, 1><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket,
@@ -311,13 +319,13 @@ static int dot_static_launch(const uint32_t* a, const uint32_t* b, float* out, l
     if (cudaMemsetAsync(scratch, 0, 16, s) != cudaSuccess) return FEATHER_ERR_LAUNCH;
     unsigned int* ticket = reinterpret_cast<unsigned int*>(scratch);
     float* partial = reinterpret_cast<float*>(scratch + kStaticDotPartialOffset);
-    long long grid = (long long)dev.sm_count * 4;
+    long long grid = (long long)dev.sm_count * 6;
     const long long need = (n_words / 4 + kDotThreads - 1) / kDotThreads;
     if (grid > need) grid = need;
     if (grid < 1) grid = 1;
     if (grid > kStaticDotSlots) grid = kStaticDotSlots;
     if (aligned(a, 16) && aligned(b, 16))
-        dot_kernel<MODE, true, 4><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket, partial,
+        dot_kernel<MODE, true, 1><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket, partial,
                                                                           n_words);
     else
         dot_kernel<MODE, false, 1><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket,
@@ -406,6 +414,124 @@ int feather_gemv_fp8(const uint32_t* m, const uint32_t* v, float* out, int64_t M
                    ? FEATHER_OK : FEATHER_ERR_LAUNCH;
     return mode == FEATHER_MODE_E5M2 ? gemv_launch<kE5M2>(m, v, out, M, N, *dev, s)
                                      : gemv_launch<kE4M3>(m, v, out, M, N, *dev, s);
+}
+
+// Base address of the cudaMalloc allocation that contains `ptr` (the driver's
+// cuMemGetAddressRange, reached through the runtime so libcuda is not linked).
+static int allocation_base(const void* ptr, const void** base) {
+    typedef int (*get_range_fn)(unsigned long long*, size_t*, unsigned long long);
+    static std::atomic<get_range_fn> cached{nullptr};
+    get_range_fn fn = cached.load(std::memory_order_acquire);
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess || !sym)
+            return FEATHER_ERR_LAUNCH;
+        fn = reinterpret_cast<get_range_fn>(sym);
+        cached.store(fn, std::memory_order_release);
+    }
+    unsigned long long b = 0;
+    size_t size = 0;
+    if (fn(&b, &size, (unsigned long long)(uintptr_t)ptr) != 0) return FEATHER_ERR_BAD_ARG;
+    *base = reinterpret_cast<const void*>((uintptr_t)b);
+    return FEATHER_OK;
+}
+
+int feather_ipc_export(const void* ptr, void* handle64, int64_t* offset) {
+    if (!ptr || !handle64 || !offset) return FEATHER_ERR_BAD_ARG;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the ABI");
+    const void* base = nullptr;
+    if (int st = allocation_base(ptr, &base)) return st;
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, const_cast<void*>(base)) != cudaSuccess) {
+        cudaGetLastError();
+        return FEATHER_ERR_LAUNCH;
+    }
+    memcpy(handle64, &h, 64);
+    *offset = (int64_t)((const char*)ptr - (const char*)base);
+    return FEATHER_OK;
+}
+
+int feather_ipc_open(const void* handle64, int64_t offset, void** mapped) {
+    if (!handle64 || !mapped || offset < 0) return FEATHER_ERR_BAD_ARG;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void* base = nullptr;
+    // opened with the CONSUMER's device current: the runtime maps the peer's
+    // allocation for this device and turns peer access on
+    if (cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess || !base) {
+        cudaGetLastError();
+        return FEATHER_ERR_LAUNCH;
+    }
+    // the mapping must resolve to device memory from this device's point of view
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, base) != cudaSuccess || attr.type != cudaMemoryTypeDevice) {
+        cudaGetLastError();
+        cudaIpcCloseMemHandle(base);
+        return FEATHER_ERR_LAUNCH;
+    }
+    *mapped = (char*)base + offset;
+    return FEATHER_OK;
+}
+
+int feather_ipc_close(void* mapped, int64_t offset) {
+    if (!mapped || offset < 0) return FEATHER_ERR_BAD_ARG;
+    if (cudaIpcCloseMemHandle((char*)mapped - offset) != cudaSuccess) {
+        cudaGetLastError();
+        return FEATHER_ERR_LAUNCH;
+    }
+    return FEATHER_OK;
+}
+
+int feather_enable_peer_access(int peer_device) {
+    int dev = 0, can = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return FEATHER_ERR_LAUNCH;
+    if (peer_device == dev) return FEATHER_OK;
+    if (cudaDeviceCanAccessPeer(&can, dev, peer_device) != cudaSuccess || !can) return FEATHER_ERR_BAD_ARG;
+    const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        cudaGetLastError();  // not an error for us: clear the sticky code
+        return FEATHER_OK;
+    }
+    return e == cudaSuccess ? FEATHER_OK : FEATHER_ERR_LAUNCH;
+}
+
+int feather_gemv_fp8_sharded_supported(int64_t rows_local, int64_t N) {
+    const DeviceInfo* dev;
+    if (device_info(&dev)) return 0;
+    return rows_local > 0 && rows_local <= 0x7FFFFFFF && N > 0 && N <= 0x7FFFFFFFll * 4 &&
+           ring_eligible(nullptr, rows_local, N, *dev) ? 1 : 0;
+}
+
+int feather_gemv_fp8_sharded(const uint32_t* m_local, const uint32_t* v, int64_t rows_local,
+                             int64_t N, int mode, float* const* peer_out,
+                             uint32_t* const* peer_flags, int rank, int world, uint32_t epoch,
+                             void* stream) {
+    if (rows_local <= 0 || N <= 0 || (N & 3) || rows_local > 0x7FFFFFFF || !peer_out || !peer_flags ||
+        world < 1 || world > kMaxShardRanks || rank < 0 || rank >= world || epoch == 0 || !m_local || !v)
+        return FEATHER_ERR_BAD_ARG;
+    if (mode != FEATHER_MODE_E5M2 && mode != FEATHER_MODE_E4M3) return FEATHER_ERR_MODE;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    if (!aligned(v, 4)) return FEATHER_ERR_MISALIGNED;
+    if (!ring_eligible(m_local, rows_local, N, *dev)) return FEATHER_ERR_BAD_ARG;
+    ShardArgs sh = {};
+    for (int p = 0; p < world; ++p) {
+        if (!peer_out[p] || !peer_flags[p]) return FEATHER_ERR_BAD_ARG;
+        if (!aligned(peer_out[p], 4) || !aligned(peer_flags[p], 4)) return FEATHER_ERR_MISALIGNED;
+        sh.out[p] = peer_out[p];
+        sh.flags[p] = peer_flags[p];
+    }
+    sh.row_offset = (long long)rank * rows_local;
+    sh.rank = rank;
+    sh.world = world;
+    sh.epoch = epoch;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float* mine = peer_out[rank] + sh.row_offset;
+    return mode == FEATHER_MODE_E5M2
+               ? gemv_ring_launch<kE5M2, true>(m_local, v, mine, rows_local, N, *dev, s, sh)
+               : gemv_ring_launch<kE4M3, true>(m_local, v, mine, rows_local, N, *dev, s, sh);
 }
 
 int feather_device_status(void* stream) {

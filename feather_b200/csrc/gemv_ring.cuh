@@ -94,6 +94,26 @@ __device__ __forceinline__ bool mbar_sync(uint32_t bar, uint32_t& parity, unsign
     return ok;
 }
 
+// Row-sharded multi-GPU launch (FUSED = true): where every rank's output
+// buffer and flag block live.  Pointers are valid on THIS device (peer-mapped).
+constexpr int kMaxShardRanks = 16;
+constexpr int kShardTicketWord = kMaxShardRanks;  // flag-block word used as this rank's CTA ticket
+struct ShardArgs {
+    float* out[kMaxShardRanks];          // rank p's full output buffer
+    unsigned int* flags[kMaxShardRanks]; // rank p's flag block: word q = last epoch rank q delivered
+    long long row_offset;                // first global row of this rank's block
+    int rank, world;
+    unsigned int epoch;                  // this call's number, increasing by one per call
+};
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // acc += a.lo * b.lo ; acc2 += a.hi * b.hi   (FP16 operands, FP32 accumulate)
 __device__ __forceinline__ void fma_h2(uint32_t a, uint32_t b, float& acc_lo, float& acc_hi) {
     asm("{ .reg .b16 a0, a1, b0, b1;\n"
@@ -162,7 +182,7 @@ struct RingGeometry {
     static constexpr int kStageBytes = kTaskRows * kSegBytes;
     static constexpr int kTileChunks = TILE / 16;
     static constexpr int kVecBytes = TILE * 2;         // FP16 vector tile
-    static constexpr int kSmemBytes = kVecBytes + STAGES * kStageBytes + (2 * STAGES + 1) * 8;
+    static constexpr int kSmemBytes = kVecBytes + STAGES * kStageBytes + (2 * STAGES + 2) * 8;
     static constexpr int kThreads = (CW + 1) * 32;
     static_assert(kTileChunks % kSegChunks == 0, "a tile holds whole segments");
 };
@@ -170,10 +190,19 @@ struct RingGeometry {
 // CTAS: CTAs resident per SM the launch is sized for.  PREFETCH: the producer
 // also asks L2 for the next task's rows (cp.async.bulk.prefetch.L2) when it
 // starts a task, so HBM reads run a whole task ahead of the ring.
-template <int MODE, int CW, int RW, int CL, int STAGES, int TILE, int CTAS, bool PREFETCH>
+// FUSED: the kernel is one rank of a row-sharded GEMV.  Each finished row is
+// stored straight into EVERY rank's output buffer (plain stores to peer-mapped
+// memory over NVLink), so the gather of the output slices happens inside the
+// GEMV instead of in a separate collective.  When the last CTA of the rank is
+// done it publishes the call's epoch in every rank's flag block and then waits
+// (bounded) until all ranks have published theirs here: when the kernel ends,
+// this rank's buffer holds the full result.
+template <int MODE, int CW, int RW, int CL, int STAGES, int TILE, int CTAS, bool PREFETCH,
+          bool FUSED = false>
 __global__ void __launch_bounds__((CW + 1) * 32, CTAS)
 gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict__ v,
-                 float* __restrict__ out, int M, int n16, unsigned int* __restrict__ status) {
+                 float* __restrict__ out, int M, int n16, unsigned int* __restrict__ status,
+                 const __grid_constant__ ShardArgs sh = ShardArgs{}) {
     using G = RingGeometry<CW, RW, CL, STAGES, TILE>;
     // Programmatic dependent launch: let the next kernel of the stream be
     // scheduled onto SMs as they free up, and wait for everything before this
@@ -189,6 +218,8 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
     const uint32_t tile_bar = bars + 8u * (2 * STAGES);  // all consumer threads
+    unsigned int* warps_done = reinterpret_cast<unsigned int*>(ring + STAGES * G::kStageBytes +
+                                                               8 * (2 * STAGES + 1));
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row_begin = (int)(((long long)M * blockIdx.x) / gridDim.x);
@@ -203,10 +234,11 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
             mbar_init(empty_bar(s), CW);   // one arrive per consumer warp
         }
         mbar_init(tile_bar, CW * 32);
+        *warps_done = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (n_tasks == 0) return;
+    if (n_tasks == 0 && !FUSED) return;  // a fused rank needs every CTA at the final ticket
 
     if (warp == CW) {
         // ------------------------------------------------------- producer --
@@ -346,8 +378,45 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
             if ((lane & (32 / RW - 1)) == 0) {
                 const int row = row0 + lane / (32 / RW);
                 if (row < row_end) {
-                    if (tile == 0) out[row] = sums[0];
-                    else out[row] += sums[0];  // the same lane owns the row in every tile
+                    if (!FUSED) {
+                        if (tile == 0) out[row] = sums[0];
+                        else out[row] += sums[0];  // the same lane owns the row in every tile
+                    } else {
+                        // partial sums of earlier column tiles sit in this rank's own buffer
+                        float* mine = sh.out[sh.rank] + sh.row_offset;
+                        const float total = tile == 0 ? sums[0] : mine[row] + sums[0];
+                        if (tile + 1 < n_tiles) {
+                            mine[row] = total;
+                        } else {
+                            for (int p = 0; p < sh.world; ++p) sh.out[p][sh.row_offset + row] = total;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (FUSED) {
+        // This warp's rows are delivered.  Order its peer stores before the
+        // counters; the last warp of the last CTA of the rank signals and waits.
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0 && atomicAdd(warps_done, 1u) == CW - 1) {
+            __threadfence();
+            unsigned int* my_flags = sh.flags[sh.rank];
+            if (atomicAdd(my_flags + kShardTicketWord, 1u) == gridDim.x - 1) {
+                my_flags[kShardTicketWord] = 0u;  // every CTA has arrived: ready for the next call
+                __threadfence_system();
+                for (int p = 0; p < sh.world; ++p) st_release_sys(sh.flags[p] + sh.rank, sh.epoch);
+                const unsigned long long t0 = global_timer_ns();
+                for (int q = 0; q < sh.world; ++q) {
+                    // wrap-safe "flag has reached this epoch"
+                    while ((int)(ld_acquire_sys(my_flags + q) - sh.epoch) < 0) {
+                        if (global_timer_ns() - t0 > kWaitLimitNs) {
+                            atomicOr(status, 2u);  // a peer's slice did not arrive in time
+                            q = sh.world;
+                            break;
+                        }
+                    }
                 }
             }
         }

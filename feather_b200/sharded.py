@@ -7,13 +7,25 @@ N/4 words), so rank r of W holds the contiguous packed rows
 packed vector is replicated, every rank runs the single-GPU kernel on its
 block, and the FP32 output slices are exchanged with one all-gather.
 
+Two exchange paths:
+
+* ``fused=False``: local GEMV into the rank's slice, then one in-place NCCL
+  all-gather.
+* ``fused=True`` (default on GPUs when the shape allows it): the GEMV kernel
+  itself stores every finished row into all ranks' output buffers through
+  peer-mapped memory (``feather_gemv_fp8_sharded``), so the exchange overlaps
+  the streaming of the matrix and costs one NVLink round trip at the end
+  instead of a collective launch.  The buffers are shared between the ranks'
+  processes with CUDA IPC (torch's own tensor sharing).
+
 One process per GPU over ``torch.distributed`` (NCCL on GPUs).  The local
 compute is injectable so that the partition / gather plumbing can be tested
 with the gloo backend on CPU ranks.
 """
 from __future__ import annotations
 
-from typing import Callable, Optional, Tuple
+import ctypes
+from typing import Callable, List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -52,11 +64,17 @@ class RowShardedGemv:
     group   : process group (default: the world group).
     local_gemv : callable ``(m_local, v_packed, (rows, N), mode, out) -> out``;
         defaults to the CUDA kernel.  Tests on CPU ranks inject the oracle.
+    fused   : True = exchange inside the kernel (raises if impossible), False =
+        NCCL all-gather, None = fused when the operands are on GPUs, the world
+        has more than one rank and the kernel supports the shape.
+
+    The result of ``op(v)`` is the object's own buffer.  In fused mode two
+    buffers alternate, so a result stays valid until the call after the next.
     """
 
     def __init__(self, m_local: torch.Tensor, m_shape, mode: str = "E5M2",
                  group: Optional[dist.ProcessGroup] = None,
-                 local_gemv: Optional[Callable] = None):
+                 local_gemv: Optional[Callable] = None, fused: Optional[bool] = None):
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed is not initialised")
         self.group = group
@@ -73,12 +91,110 @@ class RowShardedGemv:
                              f"{self.rows}x{self.N} needs {need}")
         self.m_local = m_local
         self.mode = mode
+        custom_compute = local_gemv is not None
         if local_gemv is None:
             from .routines.gemv import gemv_fp8_acc_fp32_gpu
             local_gemv = gemv_fp8_acc_fp32_gpu
         self._local_gemv = local_gemv
         self._check_agreement()
         self.out = torch.empty(self.M, dtype=torch.float32, device=m_local.device)
+        self.fused = False
+        self._epoch = 0
+        want = fused
+        if want is None:
+            want = (not custom_compute) and m_local.is_cuda and self.world_size > 1
+        error = None
+        if want:
+            # Every rank runs the same sequence of collectives whatever fails locally.
+            error = self._setup_fused()
+        # all ranks must take the same path, or they would wait on each other
+        agree = torch.tensor([int(want and error is None)], dtype=torch.int32, device=m_local.device)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN, group=self.group)
+        self.fused = bool(int(agree.item()))
+        if fused and not self.fused:
+            raise RuntimeError(f"fused exchange requested but not available: {error or 'a peer rank failed'}")
+
+    # ------------------------------------------------------------ fused path --
+    def _setup_fused(self):
+        """Allocate the shared buffers and map every peer's.  Returns None on
+        success or the exception that makes the fused path unusable here."""
+        from . import _lib
+        from .packers.fp8 import as_words
+        dev = self.m_local.device
+        error, payload = None, None
+        try:
+            lib = _lib.load()
+            if self.world_size > 16:
+                raise ValueError("fused exchange supports at most 16 ranks")
+            as_words(self.m_local, "m_local")
+            with torch.cuda.device(dev):
+                if not lib.feather_gemv_fp8_sharded_supported(self.rows, self.N):
+                    raise ValueError(f"{self.rows}x{self.N} per rank is outside the fused kernel's range")
+                # [two output buffers | flag block]: one allocation per rank, exported by CUDA IPC
+                self._shared = torch.zeros(2 * self.M + 32, dtype=torch.float32, device=dev)
+                torch.cuda.synchronize(dev)
+                handle = ctypes.create_string_buffer(64)
+                offset = ctypes.c_int64(0)
+                _lib.check(lib.feather_ipc_export(self._shared.data_ptr(), handle, ctypes.byref(offset)))
+            payload = (handle.raw, int(offset.value), dev.index)
+        except Exception as e:  # noqa: BLE001 - reported through the agreement step
+            error = e
+        gathered: List = [None] * self.world_size
+        dist.all_gather_object(gathered, payload, group=self.group)
+        if error is not None:
+            return error
+        try:
+            if any(g is None for g in gathered):
+                raise RuntimeError("a peer rank could not share its buffer")
+            base, self._mapped = [], []
+            with torch.cuda.device(dev):  # map with the device that runs the kernel current
+                for r, (raw, off, peer_dev) in enumerate(gathered):
+                    if r == self.rank:
+                        base.append(self._shared.data_ptr())
+                        continue
+                    if not torch.cuda.can_device_access_peer(dev.index, peer_dev):
+                        raise RuntimeError(f"GPU {dev.index} cannot access GPU {peer_dev} directly")
+                    _lib.check(lib.feather_enable_peer_access(peer_dev))
+                    mapped = ctypes.c_void_p(0)
+                    _lib.check(lib.feather_ipc_open(raw, off, ctypes.byref(mapped)))
+                    self._mapped.append((mapped.value, off))
+                    base.append(mapped.value)
+            arr = ctypes.c_void_p * self.world_size
+            self._out_ptrs = [arr(*[b + 4 * self.M * k for b in base]) for k in (0, 1)]
+            self._flag_ptrs = arr(*[b + 4 * 2 * self.M for b in base])
+            self._views = [self._shared[: self.M], self._shared[self.M: 2 * self.M]]
+            self._lib, self._check = lib, _lib.check
+            self._mode_id = _lib.mode_id(self.mode)
+            self._stream_ptr = _lib.current_stream_ptr
+            torch.cuda.synchronize(dev)
+        except Exception as e:  # noqa: BLE001
+            return e
+        return None
+
+    def close(self) -> None:
+        """Unmap the peers' buffers (fused mode).  Call on every rank, after the
+        last result has been consumed and before the process group goes away."""
+        if getattr(self, "_mapped", None):
+            torch.cuda.synchronize(self.m_local.device)
+            dist.barrier(group=self.group)  # nobody is still writing into a buffer being unmapped
+            with torch.cuda.device(self.m_local.device):
+                for ptr, off in self._mapped:
+                    self._lib.feather_ipc_close(ptr, off)
+            self._mapped = []
+            self.fused = False
+
+    def _call_fused(self, v_packed: torch.Tensor) -> torch.Tensor:
+        self._epoch += 1
+        k = self._epoch & 1
+        dev = self.m_local.device
+        if v_packed.numel() < self.N // 4 or v_packed.device != dev:
+            raise ValueError("v must hold N/4 packed words on this rank's device")
+        with torch.cuda.device(dev):
+            self._check(self._lib.feather_gemv_fp8_sharded(
+                self.m_local.data_ptr(), v_packed.data_ptr(), self.rows, self.N, self._mode_id,
+                self._out_ptrs[k], self._flag_ptrs, self.rank, self.world_size,
+                self._epoch & 0xFFFFFFFF or 1, self._stream_ptr(dev.index)))
+        return self._views[k]
 
     def _check_agreement(self) -> None:
         """Every rank must describe the same global problem."""
@@ -100,6 +216,8 @@ class RowShardedGemv:
     def __call__(self, v_packed: torch.Tensor) -> torch.Tensor:
         """Full ``(M,)`` FP32 result on every rank.  The returned tensor is the
         object's own buffer and is overwritten by the next call."""
+        if self.fused:
+            return self._call_fused(v_packed)
         mine = self.local(v_packed)
         if self.world_size > 1:
             # in place: rank r's slice already sits at offset r * rows

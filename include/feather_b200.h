@@ -98,6 +98,68 @@ int feather_gemv_fp8(const uint32_t* m, const uint32_t* v, float* out, int64_t M
                      int mode, void* stream);
 
 /*
+ * One rank of a row-sharded GEMV with the gather of the output slices fused
+ * into the kernel.  The reference is single-GPU (feather/routines/gemv.py:136,
+ * :187 hard-code one device); rows are independent, so rank r of `world` holds
+ * the packed rows [r * rows_local, (r + 1) * rows_local) and the whole packed
+ * vector.  Instead of a separate all-gather, every finished row is stored into
+ * ALL ranks' output buffers through peer-mapped pointers (NVLink), the rank
+ * then publishes `epoch` in every rank's flag block and waits, for at most two
+ * seconds, until every rank has published the same epoch in its own block.
+ * When the kernel ends, peer_out[rank] holds all world * rows_local results.
+ *   m_local     rows_local * N / 4 words, 16-byte aligned; N % 16 == 0,
+ *               N >= 4096, rows_local >= 32 * SM count (use
+ *               feather_gemv_fp8_sharded_supported(); other shapes return
+ *               FEATHER_ERR_BAD_ARG: run feather_gemv_fp8 and gather instead)
+ *   peer_out    HOST array of `world` device pointers: rank p's output buffer
+ *               (world * rows_local floats), as mapped into THIS process
+ *   peer_flags  HOST array of `world` device pointers: rank p's flag block,
+ *               32 words, zero before the first call
+ *   epoch       1 for the first call, +1 for every later call, equal on all
+ *               ranks.  Use two output buffers alternately (even / odd epoch):
+ *               a fast rank may start writing call k+1 while a slow rank's
+ *               consumer still reads call k.
+ * One call per rank must be in flight at the same time on every rank, each on
+ * its own GPU.  A rank that never arrives makes the others raise the status
+ * word after the bounded wait (see feather_device_status) instead of hanging.
+ */
+int feather_gemv_fp8_sharded(const uint32_t* m_local, const uint32_t* v, int64_t rows_local,
+                             int64_t N, int mode, float* const* peer_out,
+                             uint32_t* const* peer_flags, int rank, int world, uint32_t epoch,
+                             void* stream);
+int feather_gemv_fp8_sharded_supported(int64_t rows_local, int64_t N);
+
+/*
+ * Let kernels on the CURRENT device load and store memory that lives on
+ * `peer_device` (cudaDeviceEnablePeerAccess; already-enabled is success).  The
+ * fused sharded GEMV stores into its peers' buffers, so each rank calls this
+ * once per peer before its first feather_gemv_fp8_sharded.  Mapping a peer's
+ * buffer into the process (CUDA IPC) does not by itself grant that access.
+ * FEATHER_ERR_BAD_ARG if the two GPUs have no direct path.
+ */
+int feather_enable_peer_access(int peer_device);
+
+/*
+ * Sharing a buffer between the one-process-per-GPU ranks of a node (CUDA IPC),
+ * for the peer_out / peer_flags arguments above.  The library allocates
+ * nothing: the owner exports a buffer it already holds, the peers map it.
+ *   feather_ipc_export  owner side, owner's device current.  `ptr` lies in a
+ *                       cudaMalloc allocation (a PyTorch tensor of the default
+ *                       allocator does); writes the 64-byte handle of that
+ *                       allocation and ptr's offset inside it.
+ *   feather_ipc_open    peer side, with the device that will RUN THE KERNEL
+ *                       current: maps the allocation for that device (peer
+ *                       access is enabled by the runtime) and returns the
+ *                       address that corresponds to the owner's `ptr`.
+ *   feather_ipc_close   unmaps; pass what feather_ipc_open returned and the
+ *                       same offset.  The owner must keep the buffer alive
+ *                       until every peer has closed it.
+ */
+int feather_ipc_export(const void* ptr, void* handle64, int64_t* offset);
+int feather_ipc_open(const void* handle64, int64_t offset, void** mapped);
+int feather_ipc_close(void* mapped, int64_t offset);
+
+/*
  * Health check for the kernels that wait on shared-memory barriers (the large
  * GEMV streams the matrix through a ring of asynchronous bulk copies).  Every
  * such wait is bounded; a wait that gives up raises a sticky status word on

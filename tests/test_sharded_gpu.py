@@ -40,15 +40,21 @@ def _worker(rank: int, world: int, port: int, q):
         A = torch.randn(M, N, device="cuda", generator=gen, dtype=torch.float16)
         v = torch.randn(N, device="cuda", generator=gen, dtype=torch.float16)
         mw, vw = fb.pack_fp8_tensor(A, mode), fb.pack_fp8_tensor(v, mode)
-        op = RowShardedGemv(local_words(mw, (M, N), world, rank), (M, N), mode)
-        y = op(vw)
         y_single = fb.gemv_fp8_acc_fp32_gpu(mw, vw, (M, N), mode)
         host = lambda t: t.view(torch.int32).cpu().numpy().view(np.uint32)
         ref = C.gemv(host(mw), host(vw), (M, N), mode, acc="f64")
-        err = O.normalised_error(y.cpu().numpy(), ref)
-        # rows never interact, so the sharded result has the single-GPU bits
-        q.put((rank, bool(torch.equal(y, y_single)), err < 1e-5))
-        fb.device_status()
+        ok_bits, ok_err, modes = True, True, []
+        for fused in ((False, True) if world > 1 else (False,)):
+            op = RowShardedGemv(local_words(mw, (M, N), world, rank), (M, N), mode, fused=fused)
+            modes.append(op.fused)
+            for it in range(3):  # several calls: the fused path alternates buffers and counts epochs
+                y = op(vw).clone()
+                torch.cuda.synchronize()
+                # rows never interact, so the sharded result has the single-GPU bits
+                ok_bits &= bool(torch.equal(y, y_single))
+                ok_err &= O.normalised_error(y.cpu().numpy(), ref) < 1e-5
+            fb.device_status()
+        q.put((rank, ok_bits and modes == ([False, True] if world > 1 else [False]), ok_err))
     except Exception as e:
         q.put((rank, "failed", repr(e)))
     finally:
