@@ -65,6 +65,8 @@ class ClockSampler:
         self._stop = threading.Event()
         self._thread = None
         try:
+            if index < 0:
+                raise ValueError("sampling disabled on this rank")
             import pynvml
             pynvml.nvmlInit()
             self._nv = pynvml
@@ -90,7 +92,7 @@ class ClockSampler:
                 self._once()
             except Exception:
                 break
-            self._stop.wait(0.002)
+            self._stop.wait(0.005)
 
     def __enter__(self):
         if self._nv is not None:
@@ -296,7 +298,8 @@ def run_ours(args) -> None:
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    with ClockSampler(physical_gpu_index(local_rank)) as clocks:
+    # only rank 0 polls NVML: concurrent queries from every rank serialise in the driver
+    with ClockSampler(physical_gpu_index(local_rank) if rank == 0 else -1) as clocks:
         start.record()
         for _ in range(K):
             step()

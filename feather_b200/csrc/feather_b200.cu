@@ -41,6 +41,19 @@ __device__ __forceinline__ uint32_t pack4_h(uint2 h) {  // four fp16 values
            (encode_h<MODE>(h.y & 0xFFFFu) << 16) | (encode_h<MODE>(h.y >> 16) << 24);
 }
 
+// fp16 -> E5M2 on two values at once.  For a non-NaN fp16 bit pattern h the
+// code is RNE of the low byte:  (h + 0x7F + ((h >> 8) & 1)) >> 8  (a mantissa
+// carry walks into the exponent, 0x7BFF.. rounds to inf 0x7C).  Both halves of
+// a 32-bit word are rounded with one add; no carry can cross from the low half
+// to the high half unless the low half is a negative NaN, and words that hold
+// a NaN take the scalar path.  The two codes end up in bytes 1 and 3.
+__device__ __forceinline__ uint32_t round_e5m2_pair(uint32_t w) {
+    return w + 0x007F007Fu + ((w >> 8) & 0x00010001u);
+}
+__device__ __forceinline__ uint32_t has_nan_pair(uint32_t w) {  // bit 15 / 31 set for a NaN half
+    return ((w & 0x7FFF7FFFu) + 0x03FF03FFu) & 0x80008000u;
+}
+
 template <int MODE, bool F32>
 __global__ void __launch_bounds__(256)
 encode_vec_kernel(const void* __restrict__ src, uint4* __restrict__ dst, long long n_groups) {
@@ -57,6 +70,19 @@ encode_vec_kernel(const void* __restrict__ src, uint4* __restrict__ dst, long lo
     } else {
         const uint4* s = reinterpret_cast<const uint4*>(src) + g * 2;
         const uint4 a = __ldcs(s), b = __ldcs(s + 1);
+        if (MODE == kE5M2) {
+            const uint32_t nan = has_nan_pair(a.x) | has_nan_pair(a.y) | has_nan_pair(a.z) |
+                                 has_nan_pair(a.w) | has_nan_pair(b.x) | has_nan_pair(b.y) |
+                                 has_nan_pair(b.z) | has_nan_pair(b.w);
+            if (nan == 0u) {  // the usual case: sixteen values, two per integer add
+                o.x = prmt(round_e5m2_pair(a.x), round_e5m2_pair(a.y), 0x7531u);
+                o.y = prmt(round_e5m2_pair(a.z), round_e5m2_pair(a.w), 0x7531u);
+                o.z = prmt(round_e5m2_pair(b.x), round_e5m2_pair(b.y), 0x7531u);
+                o.w = prmt(round_e5m2_pair(b.z), round_e5m2_pair(b.w), 0x7531u);
+                dst[g] = o;
+                return;
+            }
+        }
         o.x = pack4_h<MODE>(make_uint2(a.x, a.y));
         o.y = pack4_h<MODE>(make_uint2(a.z, a.w));
         o.z = pack4_h<MODE>(make_uint2(b.x, b.y));
@@ -527,11 +553,24 @@ int feather_gemv_fp8_sharded(const uint32_t* m_local, const uint32_t* v, int64_t
     sh.rank = rank;
     sh.world = world;
     sh.epoch = epoch;
+    {   // rows per CTA as the kernel will split them (grid = min(SMs, tasks))
+        long long grid = dev->sm_count;
+        const long long tasks = (rows_local + kRingCW * kRingRW - 1) / (kRingCW * kRingRW);
+        if (grid > tasks) grid = tasks;
+        sh.staged = (rows_local + grid - 1) / grid <= kShardStageRows ? 1 : 0;
+    }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     float* mine = peer_out[rank] + sh.row_offset;
     return mode == FEATHER_MODE_E5M2
                ? gemv_ring_launch<kE5M2, true>(m_local, v, mine, rows_local, N, *dev, s, sh)
                : gemv_ring_launch<kE4M3, true>(m_local, v, mine, rows_local, N, *dev, s, sh);
+}
+
+int feather_set_wait_limit_ms(int milliseconds) {
+    if (milliseconds < 1 || milliseconds > 600000) return FEATHER_ERR_BAD_ARG;
+    const unsigned long long ns = (unsigned long long)milliseconds * 1000000ull;
+    return cudaMemcpyToSymbol(g_wait_limit_ns, &ns, sizeof(ns)) == cudaSuccess ? FEATHER_OK
+                                                                                : FEATHER_ERR_LAUNCH;
 }
 
 int feather_device_status(void* stream) {

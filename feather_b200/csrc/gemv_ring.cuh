@@ -35,7 +35,11 @@
 
 namespace feather {
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+// How long a bounded wait may go without progress before it gives up: 2 s
+// unless the host changed it (feather_set_wait_limit_ms).  One copy per kernel
+// image that includes this header; the library has one.
+__device__ unsigned long long g_wait_limit_ns = 2000000000ull;
+#define kWaitLimitNs g_wait_limit_ns
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -97,6 +101,7 @@ __device__ __forceinline__ bool mbar_sync(uint32_t bar, uint32_t& parity, unsign
 // Row-sharded multi-GPU launch (FUSED = true): where every rank's output
 // buffer and flag block live.  Pointers are valid on THIS device (peer-mapped).
 constexpr int kMaxShardRanks = 16;
+constexpr int kShardStageRows = 512;  // results a CTA can stage in shared memory before pushing
 constexpr int kShardTicketWord = kMaxShardRanks;  // flag-block word used as this rank's CTA ticket
 struct ShardArgs {
     float* out[kMaxShardRanks];          // rank p's full output buffer
@@ -104,6 +109,9 @@ struct ShardArgs {
     long long row_offset;                // first global row of this rank's block
     int rank, world;
     unsigned int epoch;                  // this call's number, increasing by one per call
+    int staged;                          // 1: every CTA owns <= kShardStageRows rows and pushes them
+                                         //    to the peers as ONE coalesced block when it is done;
+                                         // 0: each row is stored to the peers as it finishes
 };
 __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -182,7 +190,8 @@ struct RingGeometry {
     static constexpr int kStageBytes = kTaskRows * kSegBytes;
     static constexpr int kTileChunks = TILE / 16;
     static constexpr int kVecBytes = TILE * 2;         // FP16 vector tile
-    static constexpr int kSmemBytes = kVecBytes + STAGES * kStageBytes + (2 * STAGES + 2) * 8;
+    static constexpr int kSmemBytes = kVecBytes + STAGES * kStageBytes + (2 * STAGES + 2) * 8 +
+                                      kShardStageRows * 4;
     static constexpr int kThreads = (CW + 1) * 32;
     static_assert(kTileChunks % kSegChunks == 0, "a tile holds whole segments");
 };
@@ -220,6 +229,7 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
     const uint32_t tile_bar = bars + 8u * (2 * STAGES);  // all consumer threads
     unsigned int* warps_done = reinterpret_cast<unsigned int*>(ring + STAGES * G::kStageBytes +
                                                                8 * (2 * STAGES + 1));
+    float* staged_rows = reinterpret_cast<float*>(ring + STAGES * G::kStageBytes + 8 * (2 * STAGES + 2));
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row_begin = (int)(((long long)M * blockIdx.x) / gridDim.x);
@@ -381,6 +391,11 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
                     if (!FUSED) {
                         if (tile == 0) out[row] = sums[0];
                         else out[row] += sums[0];  // the same lane owns the row in every tile
+                    } else if (sh.staged) {
+                        // the CTA's rows are collected in shared memory (partial sums of
+                        // earlier column tiles too) and pushed once, coalesced, at the end
+                        const int i = row - row_begin;
+                        staged_rows[i] = tile == 0 ? sums[0] : staged_rows[i] + sums[0];
                     } else {
                         // partial sums of earlier column tiles sit in this rank's own buffer
                         float* mine = sh.out[sh.rank] + sh.row_offset;
@@ -389,6 +404,7 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
                             mine[row] = total;
                         } else {
                             for (int p = 0; p < sh.world; ++p) sh.out[p][sh.row_offset + row] = total;
+                            __threadfence_system();  // before this warp reports itself finished
                         }
                     }
                 }
@@ -396,25 +412,44 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
         }
     }
     if (FUSED) {
-        // This warp's rows are delivered.  Order its peer stores before the
-        // counters; the last warp of the last CTA of the rank signals and waits.
-        __threadfence_system();
+        // This warp's rows are finished.  The last consumer warp of the CTA
+        // delivers the CTA's block to every rank, then the last CTA of the rank
+        // signals the peers and waits for their signals.
+        __threadfence_block();
         __syncwarp();
-        if (lane == 0 && atomicAdd(warps_done, 1u) == CW - 1) {
-            __threadfence();
-            unsigned int* my_flags = sh.flags[sh.rank];
-            if (atomicAdd(my_flags + kShardTicketWord, 1u) == gridDim.x - 1) {
-                my_flags[kShardTicketWord] = 0u;  // every CTA has arrived: ready for the next call
-                __threadfence_system();
-                for (int p = 0; p < sh.world; ++p) st_release_sys(sh.flags[p] + sh.rank, sh.epoch);
-                const unsigned long long t0 = global_timer_ns();
-                for (int q = 0; q < sh.world; ++q) {
-                    // wrap-safe "flag has reached this epoch"
-                    while ((int)(ld_acquire_sys(my_flags + q) - sh.epoch) < 0) {
-                        if (global_timer_ns() - t0 > kWaitLimitNs) {
-                            atomicOr(status, 2u);  // a peer's slice did not arrive in time
-                            q = sh.world;
-                            break;
+        unsigned int arrived = 0;
+        if (lane == 0) arrived = atomicAdd(warps_done, 1u);
+        arrived = __shfl_sync(0xFFFFFFFFu, arrived, 0);
+        if (arrived == CW - 1) {
+            __threadfence_block();
+            if (sh.staged) {
+                const int n_rows = row_end - row_begin;
+                for (int k = 0; k < sh.world; ++k) {
+                    const int p = (sh.rank + k) % sh.world;  // own buffer first, then round the ring
+                    float* dst = sh.out[p] + sh.row_offset + row_begin;
+                    for (int i = lane; i < n_rows; i += 32) dst[i] = staged_rows[i];
+                }
+            }
+            __threadfence_system();  // the pushed rows are visible everywhere before the ticket
+            __syncwarp();
+            if (lane == 0) {
+                unsigned int* my_flags = sh.flags[sh.rank];
+                if (atomicAdd(my_flags + kShardTicketWord, 1u) == gridDim.x - 1) {
+                    my_flags[kShardTicketWord] = 0u;  // every CTA has arrived: ready for the next call
+                    __threadfence_system();
+                    for (int k = 1; k <= sh.world; ++k) {
+                        const int p = (sh.rank + k) % sh.world;
+                        st_release_sys(sh.flags[p] + sh.rank, sh.epoch);
+                    }
+                    const unsigned long long t0 = global_timer_ns();
+                    for (int q = 0; q < sh.world; ++q) {
+                        // wrap-safe "flag has reached this epoch"
+                        while ((int)(ld_acquire_sys(my_flags + q) - sh.epoch) < 0) {
+                            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                                atomicOr(status, 2u);  // a peer's slice did not arrive in time
+                                q = sh.world;
+                                break;
+                            }
                         }
                     }
                 }

@@ -164,6 +164,10 @@ class RowShardedGemv:
             self._flag_ptrs = arr(*[b + 4 * 2 * self.M for b in base])
             self._views = [self._shared[: self.M], self._shared[self.M: 2 * self.M]]
             self._lib, self._check = lib, _lib.check
+            self._fn = lib.feather_gemv_fp8_sharded
+            self._m_ptr = self.m_local.data_ptr()
+            self._n_words = self.N // 4
+            self._dev, self._dev_index = dev, dev.index
             self._mode_id = _lib.mode_id(self.mode)
             self._stream_ptr = _lib.current_stream_ptr
             torch.cuda.synchronize(dev)
@@ -184,16 +188,25 @@ class RowShardedGemv:
             self.fused = False
 
     def _call_fused(self, v_packed: torch.Tensor) -> torch.Tensor:
+        # hot path: everything that does not change between calls was prepared in
+        # _setup_fused; operands may be PackedFP8 subclasses, so metadata reads
+        # skip the Python-level __torch_function__ dispatch
+        with torch._C.DisableTorchFunctionSubclass():
+            if v_packed.numel() < self._n_words or v_packed.device != self._dev:
+                raise ValueError("v must hold N/4 packed words on this rank's device")
+            v_ptr = v_packed.data_ptr()
         self._epoch += 1
         k = self._epoch & 1
-        dev = self.m_local.device
-        if v_packed.numel() < self.N // 4 or v_packed.device != dev:
-            raise ValueError("v must hold N/4 packed words on this rank's device")
-        with torch.cuda.device(dev):
-            self._check(self._lib.feather_gemv_fp8_sharded(
-                self.m_local.data_ptr(), v_packed.data_ptr(), self.rows, self.N, self._mode_id,
-                self._out_ptrs[k], self._flag_ptrs, self.rank, self.world_size,
-                self._epoch & 0xFFFFFFFF or 1, self._stream_ptr(dev.index)))
+        idx = self._dev_index
+        if torch.cuda.current_device() != idx:
+            with torch.cuda.device(idx):
+                return self._launch_fused(v_ptr, k, idx)
+        return self._launch_fused(v_ptr, k, idx)
+
+    def _launch_fused(self, v_ptr: int, k: int, idx: int) -> torch.Tensor:
+        self._check(self._fn(self._m_ptr, v_ptr, self.rows, self.N, self._mode_id,
+                             self._out_ptrs[k], self._flag_ptrs, self.rank, self.world_size,
+                             (self._epoch & 0xFFFFFFFF) or 1, self._stream_ptr(idx)))
         return self._views[k]
 
     def _check_agreement(self) -> None:

@@ -172,6 +172,13 @@ int feather_ipc_close(void* mapped, int64_t offset);
 int feather_device_status(void* stream);
 
 /*
+ * Change, on the current device, how long a bounded device-side wait may go
+ * without progress before it gives up (default 2000 ms; 1 .. 600000).  Takes
+ * effect for kernels launched afterwards; synchronises the device.
+ */
+int feather_set_wait_limit_ms(int milliseconds);
+
+/*
  * *out = sum_i decode(a[i]) * decode(b[i]) over 4 * n_words codes.
  * Replaces feather/routines/dot.py:220-260 (dot_fp8_e5m2_acc_fp32_gpu) and its
  * kernel dot.py:144-192.  The reference adds per-block sums with a float

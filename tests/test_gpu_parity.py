@@ -424,3 +424,43 @@ def test_c_abi_status_codes_on_device(fb):
     assert lib.feather_decode_fp8(p, po, 4, 0, 9, None) == -3
     assert lib.feather_device_status(None) == 0
     torch.cuda.synchronize()
+
+
+# ------------------------------------------------------- bounded device waits --
+def test_sharded_wait_gives_up_and_reports_instead_of_hanging(fb):
+    """A rank whose peer never delivers must not hang: the fused sharded kernel
+    waits a bounded time for the peer's epoch flag, raises the device status
+    word and returns; the host reads FEATHER_ERR_TIMEOUT and the context stays
+    usable.  The "peer" here is a second flag block on the same GPU that nothing
+    ever writes (no second process, no fault)."""
+    lib = fb._lib.load()
+    rows, N = 4736, 4096
+    assert lib.feather_gemv_fp8_sharded_supported(rows, N) == 1
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    A = torch.randn(rows, N, device="cuda", generator=gen, dtype=torch.float16)
+    v = torch.randn(N, device="cuda", generator=gen, dtype=torch.float16)
+    mw, vw = fb.pack_fp8_tensor(A, "E5M2"), fb.pack_fp8_tensor(v, "E5M2")
+    out = [torch.zeros(2 * rows, dtype=torch.float32, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(32, dtype=torch.int32, device="cuda") for _ in range(2)]
+    arr = ctypes.c_void_p * 2
+    outs, flgs = arr(*[t.data_ptr() for t in out]), arr(*[t.data_ptr() for t in flags])
+    assert lib.feather_device_status(None) == 0
+    assert lib.feather_set_wait_limit_ms(100) == 0
+    try:
+        st = lib.feather_gemv_fp8_sharded(mw.data_ptr(), vw.data_ptr(), rows, N, 0, outs, flgs,
+                                          0, 2, 1, None)
+        assert st == 0
+        assert lib.feather_device_status(None) == -7          # the wait gave up, no hang
+        assert lib.feather_device_status(None) == 0           # sticky word was cleared
+        with pytest.raises(fb._lib.FeatherError):
+            fb._lib.check(-7)
+        # rank 0's own rows were still computed and delivered to both buffers
+        ref = fb.gemv_fp8_acc_fp32_gpu(mw, vw, (rows, N), "E5M2")
+        assert torch.equal(out[0][:rows], ref) and torch.equal(out[1][:rows], ref)
+        # with the missing flag supplied by hand the next call completes cleanly
+        flags[0][1] = 2
+        st = lib.feather_gemv_fp8_sharded(mw.data_ptr(), vw.data_ptr(), rows, N, 0, outs, flgs,
+                                          0, 2, 2, None)
+        assert st == 0 and lib.feather_device_status(None) == 0
+    finally:
+        assert lib.feather_set_wait_limit_ms(2000) == 0
