@@ -417,6 +417,17 @@ def run_ours(args) -> None:
                                              "GB/s": round(b / ms_s / 1e6, 1),
                                              "frac_of_peak": round(b / ms_s / 1e6 / peak, 4)}
         del m4
+        # the headline workload with FEATHER_GEMV_STATIC_MATRIX (weights promised static)
+        st5 = {"i": 0}
+
+        def step_static():
+            fb.gemv_fp8_acc_fp32_gpu(mats[st5["i"] % n_buf], vw, (M, N), mode, out=out, static_matrix=True)
+            st5["i"] += 1
+        torch.cuda.synchronize()
+        ms_st = time_calls(torch, step_static, max(n_it, 200), 10)
+        extra["gemv_e5m2_16384x16384_static_matrix_flag"] = {
+            "us_per_call": round(ms_st * 1e3, 3), "GB/s": round(step_bytes / ms_st / 1e6, 1),
+            "frac_of_peak": round(step_bytes / ms_st / 1e6 / peak, 4)}
         # dot on two 2^26-element E5M2 vectors: reuse the packed matrices as operands
         n_words = 1 << 24
         ops = [(mats[i][:n_words], mats[i][n_words:2 * n_words]) for i in range(n_buf)]

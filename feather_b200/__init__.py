@@ -48,12 +48,13 @@ def device_status() -> None:
     _lib.check(_lib.load().feather_device_status(torch.cuda.current_stream().cuda_stream))
 
 
-def gemv(m_packed, v_packed, original_shape=None, mode=None, out=None):
+def gemv(m_packed, v_packed, original_shape=None, mode=None, out=None, static_matrix=False):
     """``feather.gemv(m_packed, v_packed, original_shape=matrix.shape)``."""
     if original_shape is None:
         raise TypeError("gemv() needs original_shape=(M, N), the matrix shape before packing")
     return gemv_fp8_acc_fp32_gpu(m_packed, v_packed, tuple(original_shape),
-                                 _mode_of(mode, m_packed, v_packed), out=out)
+                                 _mode_of(mode, m_packed, v_packed), out=out,
+                                 static_matrix=static_matrix)
 
 
 def dot(a_packed, b_packed, mode=None):

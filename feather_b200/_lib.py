@@ -32,6 +32,7 @@ SYMBOLS = {
     "feather_ipc_close": (_i32, [_vp, _i64]),
     "feather_device_status": (_i32, [_vp]),
     "feather_set_wait_limit_ms": (_i32, [_i32]),
+    "feather_gemv_fp8_ex": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, ctypes.c_uint32, _vp]),
     "feather_dot_fp8": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _vp]),
     "feather_dot_workspace_bytes": (_i64, [_i64]),
     "feather_dot_fp8_static": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),

@@ -227,12 +227,13 @@ static int ensure_smem(K kernel, int smem, std::atomic<unsigned long long>& conf
     return FEATHER_OK;
 }
 
-template <int MODE, bool FUSED>
+template <int MODE, bool FUSED, bool EARLY = false>
 static int gemv_ring_launch(const uint32_t* m, const uint32_t* v, float* out, long long M,
                             long long N, const DeviceInfo& dev, cudaStream_t s,
                             const ShardArgs& shard) {
     using G = RingGeometry<kRingCW, kRingRW, kRingCL, kRingStages, kRingTile>;
-    auto kernel = gemv_ring_kernel<MODE, kRingCW, kRingRW, kRingCL, kRingStages, kRingTile, 1, false, FUSED>;
+    auto kernel = gemv_ring_kernel<MODE, kRingCW, kRingRW, kRingCL, kRingStages, kRingTile, 1, false,
+                                   FUSED, EARLY>;
     static std::atomic<unsigned long long> configured{0};
     if (int st = ensure_smem(kernel, G::kSmemBytes, configured)) return st;
     unsigned int* status = nullptr;
@@ -264,10 +265,12 @@ static bool ring_eligible(const void* m, long long M, long long N, const DeviceI
 
 template <int MODE>
 static int gemv_launch(const uint32_t* m, const uint32_t* v, float* out, long long M, long long N,
-                       const DeviceInfo& dev, cudaStream_t s) {
+                       const DeviceInfo& dev, cudaStream_t s, bool static_matrix = false) {
     const bool vec_ok = (N % 16 == 0) && aligned(m, 16);
     if (ring_eligible(m, M, N, dev))
-        return gemv_ring_launch<MODE, false>(m, v, out, M, N, dev, s, ShardArgs{});
+        return static_matrix
+                   ? gemv_ring_launch<MODE, false, true>(m, v, out, M, N, dev, s, ShardArgs{})
+                   : gemv_ring_launch<MODE, false>(m, v, out, M, N, dev, s, ShardArgs{});
     const bool fast = vec_ok && M * (N / 16) >= 4096;
     if (!fast) {
         const long long blocks = (M + 7) / 8;  // 8 warps per CTA, one row per warp
@@ -427,6 +430,12 @@ int feather_decode_fp8(const uint32_t* src, float* dst, int64_t n_elems, int mod
 
 int feather_gemv_fp8(const uint32_t* m, const uint32_t* v, float* out, int64_t M, int64_t N,
                      int mode, void* stream) {
+    return feather_gemv_fp8_ex(m, v, out, M, N, mode, 0u, stream);
+}
+
+int feather_gemv_fp8_ex(const uint32_t* m, const uint32_t* v, float* out, int64_t M, int64_t N,
+                        int mode, uint32_t flags, void* stream) {
+    if (flags & ~(uint32_t)FEATHER_GEMV_STATIC_MATRIX) return FEATHER_ERR_BAD_ARG;
     if (M < 0 || N < 0 || (N & 3) || M > 0x7FFFFFFF || N > 0x7FFFFFFFll * 4) return FEATHER_ERR_BAD_ARG;
     if (mode != FEATHER_MODE_E5M2 && mode != FEATHER_MODE_E4M3) return FEATHER_ERR_MODE;
     if (M == 0) return FEATHER_OK;
@@ -438,8 +447,9 @@ int feather_gemv_fp8(const uint32_t* m, const uint32_t* v, float* out, int64_t M
     if (N == 0)
         return cudaMemsetAsync(out, 0, sizeof(float) * (size_t)M, s) == cudaSuccess
                    ? FEATHER_OK : FEATHER_ERR_LAUNCH;
-    return mode == FEATHER_MODE_E5M2 ? gemv_launch<kE5M2>(m, v, out, M, N, *dev, s)
-                                     : gemv_launch<kE4M3>(m, v, out, M, N, *dev, s);
+    const bool static_matrix = (flags & FEATHER_GEMV_STATIC_MATRIX) != 0;
+    return mode == FEATHER_MODE_E5M2 ? gemv_launch<kE5M2>(m, v, out, M, N, *dev, s, static_matrix)
+                                     : gemv_launch<kE4M3>(m, v, out, M, N, *dev, s, static_matrix);
 }
 
 // Base address of the cudaMalloc allocation that contains `ptr` (the driver's

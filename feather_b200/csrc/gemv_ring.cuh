@@ -206,8 +206,13 @@ struct RingGeometry {
 // done it publishes the call's epoch in every rank's flag block and then waits
 // (bounded) until all ranks have published theirs here: when the kernel ends,
 // this rank's buffer holds the full result.
+// EARLY: the caller promises that nothing earlier in the stream writes the
+// MATRIX (static weights).  The producer warp then starts streaming matrix
+// bytes before the stream-order wait, so a kernel that was launched early
+// (programmatic dependent launch) fills its ring while its predecessor still
+// drains; the vector is read and the output written only after the wait.
 template <int MODE, int CW, int RW, int CL, int STAGES, int TILE, int CTAS, bool PREFETCH,
-          bool FUSED = false>
+          bool FUSED = false, bool EARLY = false>
 __global__ void __launch_bounds__((CW + 1) * 32, CTAS)
 gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict__ v,
                  float* __restrict__ out, int M, int n16, unsigned int* __restrict__ status,
@@ -218,7 +223,7 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
     // kernel (in stream order) to have completed and become visible before any
     // global memory is touched.  Without the launch attribute both are no-ops.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");
     extern __shared__ __align__(128) unsigned char smem[];
     uint4* vec = reinterpret_cast<uint4*>(smem);
     unsigned char* ring = smem + G::kVecBytes;
@@ -300,6 +305,7 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
     }
 
     // ---------------------------------------------------------- consumers --
+    if (EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");  // before the vector and the output
     int s = 0;            // ring slot of the next stage
     uint32_t phase = 0;   // its mbarrier parity
     bool alive = true;

@@ -19,15 +19,22 @@ __all__ = ["gemv_fp8_acc_fp32_gpu", "gemv_fp8_e5m2_acc_fp32_gpu", "gemv_fp8_e4m3
 
 
 def gemv_fp8_acc_fp32_gpu(m: torch.Tensor, v: torch.Tensor, m_shape, mode: str = "E5M2",
-                          out: torch.Tensor | None = None) -> torch.Tensor:
-    """out[r] = sum_j decode(m[r, j]) * decode(v[j]) with FP32 accumulation."""
+                          out: torch.Tensor | None = None,
+                          static_matrix: bool = False) -> torch.Tensor:
+    """out[r] = sum_j decode(m[r, j]) * decode(v[j]) with FP32 accumulation.
+
+    ``static_matrix=True`` promises that no work still in flight on the stream
+    writes ``m`` (weights packed earlier and synchronised): the kernel may then
+    start streaming the matrix before it has waited for the previous kernel
+    (``FEATHER_GEMV_STATIC_MATRIX``).  Leave it False when ``m`` was produced by
+    the call right before."""
     # packed operands may be PackedFP8 (a Tensor subclass): skip the Python-level
     # __torch_function__ dispatch for the metadata reads below
     with torch._C.DisableTorchFunctionSubclass():
-        return _gemv(m, v, m_shape, mode, out)
+        return _gemv(m, v, m_shape, mode, out, 1 if static_matrix else 0)
 
 
-def _gemv(m, v, m_shape, mode, out):
+def _gemv(m, v, m_shape, mode, out, flags):
     mode_id = _lib.mode_id(mode)
     m = as_words(m, "m")
     v = as_words(v, "v")
@@ -48,14 +55,14 @@ def _gemv(m, v, m_shape, mode, out):
           or not out.is_contiguous()):
         raise ValueError("out must be a contiguous float32 tensor of M elements on m's device")
     if M:
-        fn = _lib.load().feather_gemv_fp8
+        fn = _lib.load().feather_gemv_fp8_ex
         idx = m.device.index
         if torch.cuda.current_device() == idx:
-            _lib.check(fn(m.data_ptr(), v.data_ptr(), out.data_ptr(), M, N, mode_id,
+            _lib.check(fn(m.data_ptr(), v.data_ptr(), out.data_ptr(), M, N, mode_id, flags,
                           _lib.current_stream_ptr(idx)))
         else:
             with torch.cuda.device(idx):
-                _lib.check(fn(m.data_ptr(), v.data_ptr(), out.data_ptr(), M, N, mode_id,
+                _lib.check(fn(m.data_ptr(), v.data_ptr(), out.data_ptr(), M, N, mode_id, flags,
                               _lib.current_stream_ptr(idx)))
     return out
 

@@ -98,6 +98,24 @@ int feather_gemv_fp8(const uint32_t* m, const uint32_t* v, float* out, int64_t M
                      int mode, void* stream);
 
 /*
+ * feather_gemv_fp8 with option flags.
+ *   FEATHER_GEMV_STATIC_MATRIX  the caller promises that no earlier work of the
+ *       stream that may still be running WRITES THE MATRIX (weights that were
+ *       packed once and synchronised, the usual case for repeated GEMVs).
+ *       The kernel then begins streaming matrix bytes as soon as it is
+ *       scheduled, before it has waited for the previous kernel of the stream;
+ *       the vector is still read, and the output written, only after that
+ *       wait.  Back-to-back GEMVs overlap one kernel's tail with the next
+ *       one's start.  If the promise is broken (for example the matrix is
+ *       packed by the kernel right before), the result is undefined; use flags
+ *       = 0 there.  The reference has no counterpart (one Triton launch per
+ *       call, gemv.py:181).
+ */
+#define FEATHER_GEMV_STATIC_MATRIX 1u
+int feather_gemv_fp8_ex(const uint32_t* m, const uint32_t* v, float* out, int64_t M, int64_t N,
+                        int mode, uint32_t flags, void* stream);
+
+/*
  * One rank of a row-sharded GEMV with the gather of the output slices fused
  * into the kernel.  The reference is single-GPU (feather/routines/gemv.py:136,
  * :187 hard-code one device); rows are independent, so rank r of `world` holds

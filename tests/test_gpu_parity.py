@@ -224,6 +224,29 @@ def test_gemv_ring_path_ragged_shapes_vs_oracle(fb, c_oracle, mode, shape):
     fb.device_status()  # no bounded wait gave up
 
 
+@pytest.mark.parametrize("mode", MODES)
+def test_gemv_static_matrix_option_same_bits(fb, mode):
+    """FEATHER_GEMV_STATIC_MATRIX only changes when the matrix bytes start to
+    stream; repeated back-to-back calls give the bits of the default path."""
+    M, N = 6000, 8192
+    gen = torch.Generator(device="cuda").manual_seed(21)
+    mats = [fb.pack_fp8_tensor(torch.randn(M, N, device="cuda", generator=gen, dtype=torch.float16), mode)
+            for _ in range(2)]
+    vs = [fb.pack_fp8_tensor(torch.randn(N, device="cuda", generator=gen, dtype=torch.float16), mode)
+          for _ in range(3)]
+    torch.cuda.synchronize()  # the promise: nothing in flight writes the matrices
+    ref = [fb.gemv_fp8_acc_fp32_gpu(mats[i % 2], vs[i % 3], (M, N), mode) for i in range(6)]
+    torch.cuda.synchronize()
+    outs = [torch.empty(M, dtype=torch.float32, device="cuda") for _ in range(6)]
+    for i in range(6):  # back to back: each kernel starts streaming under its predecessor's tail
+        fb.gemv(mats[i % 2], vs[i % 3], original_shape=(M, N), mode=mode, out=outs[i], static_matrix=True)
+    torch.cuda.synchronize()
+    for i in range(6):
+        assert torch.equal(outs[i], ref[i])
+    lib = fb._lib.load()
+    assert lib.feather_gemv_fp8_ex(mats[0].data_ptr(), vs[0].data_ptr(), outs[0].data_ptr(), M, N, 0, 8, None) == -1
+
+
 def test_gemv_empty_and_rejects(fb):
     z = torch.zeros(8, dtype=torch.int32, device="cuda")
     assert fb.gemv_fp8_acc_fp32_gpu(z, z, (0, 8)).shape == (0,)
