@@ -428,6 +428,14 @@ def run_ours(args) -> None:
         extra["gemv_e5m2_16384x16384_static_matrix_flag"] = {
             "us_per_call": round(ms_st * 1e3, 3), "GB/s": round(step_bytes / ms_st / 1e6, 1),
             "frac_of_peak": round(step_bytes / ms_st / 1e6 / peak, 4)}
+        # TinyLlama-shaped GEMV chain (155 GEMVs per token, E4M3 weights), CUDA graph replay
+        try:
+            from feather_b200 import chain
+            extra["tinyllama_gemv_chain_1gpu"] = chain.measure(tokens=20, use_graph=True)
+            extra["tinyllama_gemv_chain_1gpu_merged_qkv_gateup"] = chain.measure(
+                tokens=20, use_graph=True, merge_projections=True)
+        except Exception as e:  # noqa: BLE001 - the extra section must not sink the headline
+            extra["tinyllama_gemv_chain_1gpu"] = {"error": repr(e)}
         # dot on two 2^26-element E5M2 vectors: reuse the packed matrices as operands
         n_words = 1 << 24
         ops = [(mats[i][:n_words], mats[i][n_words:2 * n_words]) for i in range(n_buf)]

@@ -1,0 +1,114 @@
+"""TinyLlama-1.1B-shaped batch-1 decode GEMV chain on packed-FP8 weights.
+
+The architecture's matrix shapes only (22 layers, hidden 2048, intermediate
+5632 with SwiGLU, 32 query heads / 4 KV heads of dimension 64, vocabulary
+32000); weights are random N(0, 0.02) packed E4M3, activations random N(0, 1)
+packed E4M3.  One "token" runs, per layer, the q/k/v/o and gate/up/down GEMVs
+and finally the lm_head GEMV through ``feather_b200.gemv`` -- 155 GEMVs that
+read 1.03 GB of weights.  There is no attention, normalisation or sampling:
+this measures the GEMV path only.  The reference has no such driver; it is the
+batch-1 use its README motivates (feather README.md:5-21).
+
+    python -m feather_b200.chain [--tokens 50] [--no-graph]
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+import feather_b200 as fb
+
+HIDDEN, INTER, VOCAB, LAYERS = 2048, 5632, 32000, 22
+KV_DIM = 4 * 64
+#: (name, rows M, cols N) of the GEMVs of one layer
+LAYER_SHAPES = (("q", HIDDEN, HIDDEN), ("k", KV_DIM, HIDDEN), ("v", KV_DIM, HIDDEN),
+                ("o", HIDDEN, HIDDEN), ("gate", INTER, HIDDEN), ("up", INTER, HIDDEN),
+                ("down", HIDDEN, INTER))
+
+
+def weight_bytes() -> int:
+    per_layer = sum(m * n for _, m, n in LAYER_SHAPES)
+    return LAYERS * per_layer + VOCAB * HIDDEN
+
+
+class GemvChain:
+    """Weights, activations and output buffers of the chain; ``token()`` enqueues
+    the 155 GEMVs of one token on the current stream."""
+
+    def __init__(self, mode: str = "E4M3", seed: int = 6, device: str = "cuda",
+                 layers: int = LAYERS, static_matrix: bool = True, merge_projections: bool = False):
+        gen = torch.Generator(device=device).manual_seed(seed)
+        self.mode = mode
+        self.static_matrix = static_matrix
+        self.ops = []  # (packed weights, packed activation, (M, N), out)
+        acts = {}
+        for n in (HIDDEN, INTER):
+            a = torch.randn(n, device=device, generator=gen, dtype=torch.float16)
+            acts[n] = fb.pack_fp8_tensor(a, mode)
+
+        def add(m: int, n: int) -> None:
+            w = (0.02 * torch.randn(m, n, device=device, generator=gen)).to(torch.float16)
+            self.ops.append((fb.pack_fp8_tensor(w, mode), acts[n], (m, n),
+                             torch.empty(m, dtype=torch.float32, device=device)))
+        # merge_projections: q/k/v share their input vector, and so do gate/up, so
+        # each group is ONE GEMV over the row-concatenated weights (same results,
+        # 89 instead of 155 launches per token)
+        shapes = LAYER_SHAPES if not merge_projections else (
+            ("qkv", HIDDEN + 2 * KV_DIM, HIDDEN), ("o", HIDDEN, HIDDEN),
+            ("gate_up", 2 * INTER, HIDDEN), ("down", HIDDEN, INTER))
+        for _ in range(layers):
+            for _, m, n in shapes:
+                add(m, n)
+        add(VOCAB, HIDDEN)
+        torch.cuda.synchronize()  # weights are final before any static_matrix GEMV runs
+
+    def token(self) -> None:
+        for w, a, shape, out in self.ops:
+            fb.gemv_fp8_acc_fp32_gpu(w, a, shape, self.mode, out=out,
+                                     static_matrix=self.static_matrix)
+
+    def bytes_per_token(self) -> int:
+        return sum(m * n + n + 4 * m for _, _, (m, n), _ in self.ops)
+
+
+def measure(tokens: int = 50, use_graph: bool = True, mode: str = "E4M3",
+            merge_projections: bool = False) -> dict:
+    chain = GemvChain(mode, merge_projections=merge_projections)
+    for _ in range(3):
+        chain.token()
+    torch.cuda.synchronize()
+    run = chain.token
+    if use_graph:
+        stream = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            chain.token()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=stream):
+                chain.token()
+        run = graph.replay
+        run()
+        torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(tokens):
+        run()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / tokens
+    nbytes = chain.bytes_per_token()
+    return {"tokens_per_s": round(1e3 / ms, 1), "us_per_token": round(ms * 1e3, 1),
+            "gemvs_per_token": len(chain.ops), "GB/s": round(nbytes / ms / 1e6, 1),
+            "bytes_per_token": nbytes, "cuda_graph": use_graph, "mode": mode,
+            "merged_projections": merge_projections}
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=50)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--mode", default="E4M3")
+    ap.add_argument("--merge-projections", action="store_true")
+    a = ap.parse_args()
+    print(measure(a.tokens, not a.no_graph, a.mode, a.merge_projections))

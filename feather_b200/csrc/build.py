@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 LIB = os.path.join(PKG, "libfeather_b200.so")
 SOURCES = ["feather_b200.cu"]
-HEADERS = ["fp8_codec.cuh", "gemv_kernels.cuh", "dot_kernels.cuh",
+HEADERS = ["fp8_codec.cuh", "gemv_common.cuh", "gemv_kernels.cuh", "gemv_ring.cuh", "dot_kernels.cuh",
            os.path.join("..", "..", "include", "feather_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math=false", "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared"]

@@ -8,9 +8,7 @@
 // workspace) adds the partials in index order: a single launch, and the same
 // bits every run.
 #pragma once
-#include "fp8_codec.cuh"
-#include "gemv_kernels.cuh"  // ldg_stream, warp_sum
-#include "gemv_ring.cuh"     // decode_word_h2, fma_h2
+#include "gemv_common.cuh"  // ldg_stream, warp_sum, decode_word_h2, fma_h2
 
 namespace feather {
 

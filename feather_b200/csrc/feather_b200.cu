@@ -207,12 +207,8 @@ static int status_word(unsigned int** ptr) {
 // Launch geometry.
 //   ring kernel (large matrices): 16 consumer warps x 1 row, 4 KiB of a row per
 //   bulk copy, 3 stages of 64 KiB, FP16 vector tile of 16384 codes, 1 CTA/SM.
-//   stream kernel (mid-size): 8 warps, 4 rows per group, 2 CTAs/SM.
+//   rows kernel (small and mid-size): 8 warps per CTA, each warp owns 1, 2 or 4 rows.
 constexpr int kRingCW = 16, kRingRW = 1, kRingCL = 8, kRingStages = 3, kRingTile = 16384;
-constexpr int kGemvWarps = 8;
-constexpr int kGemvRows = 4;
-constexpr int kGemvCtasPerSm = 2;
-constexpr int kGemvTileCodes = 16384;
 
 template <typename K>
 static int ensure_smem(K kernel, int smem, std::atomic<unsigned long long>& configured) {
@@ -263,6 +259,28 @@ static bool ring_eligible(const void* m, long long M, long long N, const DeviceI
            M >= 2ll * dev.sm_count * kRingCW * kRingRW;
 }
 
+template <int MODE, int RW, int U, bool EARLY>
+static int gemv_rows_launch(const uint32_t* m, const uint32_t* v, float* out, long long M,
+                            long long N, cudaStream_t s) {
+    auto kernel = gemv_rows_kernel<MODE, RW, U, EARLY>;
+    static std::atomic<unsigned long long> configured{0};
+    if (int st = ensure_smem(kernel, gemv_rows_smem_bytes(kRowsTileCodes), configured)) return st;
+    const long long rows_per_cta = (kRowsThreads / 32) * RW;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((M + rows_per_cta - 1) / rows_per_cta));
+    cfg.blockDim = dim3(kRowsThreads);
+    cfg.dynamicSmemBytes = gemv_rows_smem_bytes((int)(N > kRowsTileCodes ? kRowsTileCodes : N));
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const uint4*>(m), v, out,
+                                             (int)M, (int)(N / 16));
+    return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
+}
+
 template <int MODE>
 static int gemv_launch(const uint32_t* m, const uint32_t* v, float* out, long long M, long long N,
                        const DeviceInfo& dev, cudaStream_t s, bool static_matrix = false) {
@@ -271,24 +289,23 @@ static int gemv_launch(const uint32_t* m, const uint32_t* v, float* out, long lo
         return static_matrix
                    ? gemv_ring_launch<MODE, false, true>(m, v, out, M, N, dev, s, ShardArgs{})
                    : gemv_ring_launch<MODE, false>(m, v, out, M, N, dev, s, ShardArgs{});
-    const bool fast = vec_ok && M * (N / 16) >= 4096;
-    if (!fast) {
+    if (!vec_ok) {
         const long long blocks = (M + 7) / 8;  // 8 warps per CTA, one row per warp
         const long long cap = (long long)dev.sm_count * 8;
         gemv_general_kernel<MODE><<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(
             m, v, out, (int)M, (int)(N / 4));
         return launch_status();
     }
-    auto kernel = gemv_stream_kernel<MODE, kGemvWarps, kGemvRows, kGemvCtasPerSm, kGemvTileCodes>;
-    constexpr int smem = gemv_stream_smem_bytes(kGemvTileCodes, kGemvWarps, kGemvRows);
-    static std::atomic<unsigned long long> configured{0};
-    if (int st = ensure_smem(kernel, smem, configured)) return st;
-    long long grid = (long long)dev.sm_count * kGemvCtasPerSm;
-    const long long max_useful = (M + kGemvRows - 1) / kGemvRows;
-    if (grid > max_useful) grid = max_useful;
-    kernel<<<(unsigned)grid, kGemvWarps * 32, smem, s>>>(reinterpret_cast<const uint4*>(m), v, out,
-                                                         (int)M, (int)(N / 16));
-    return launch_status();
+    // warp-owned rows: as many rows per warp as still leaves ~16 warps per SM
+    const long long warps_wanted = (long long)dev.sm_count * 16;
+    if (M >= 4 * warps_wanted)
+        return static_matrix ? gemv_rows_launch<MODE, 4, 2, true>(m, v, out, M, N, s)
+                             : gemv_rows_launch<MODE, 4, 2, false>(m, v, out, M, N, s);
+    if (M >= 2 * warps_wanted)
+        return static_matrix ? gemv_rows_launch<MODE, 2, 4, true>(m, v, out, M, N, s)
+                             : gemv_rows_launch<MODE, 2, 4, false>(m, v, out, M, N, s);
+    return static_matrix ? gemv_rows_launch<MODE, 1, 4, true>(m, v, out, M, N, s)
+                         : gemv_rows_launch<MODE, 1, 4, false>(m, v, out, M, N, s);
 }
 
 template <int MODE>

@@ -1,194 +1,116 @@
-// Packed-FP8 GEMV kernels for sm_100a.
+// Packed-FP8 GEMV kernels for sm_100a, small and mid-size matrices.
 //
 //   out[r] = sum_j decode(m[r, j]) * decode(v[j])      (FP32 products, FP32 sums)
 //
 // replaces the reference kernels feather/routines/gemv.py:8-61 (E5M2) and
-// gemv.py:91-133 (E4M3).  The work is HBM-bound integer/byte streaming: one
-// byte of matrix per multiply-add, no reuse, so there are no tensor cores here.
+// gemv.py:91-133 (E4M3).  Large matrices take gemv_ring_kernel (gemv_ring.cuh).
 //
-// gemv_stream_kernel (fast path, N % 16 == 0, 16-byte aligned rows)
-//   * persistent grid: a multiple of the SM count; each CTA owns a contiguous
-//     block of rows and walks it in groups of R rows;
-//   * the vector is decoded to FP32 ONCE per CTA per column tile into shared
-//     memory, laid out so that every lane's float4 reads are conflict-free;
-//   * all warps of a CTA split the columns of the same R rows, each lane
-//     streams 16-byte (128-bit) chunks with non-allocating loads, R of them
-//     per step plus the next step's R prefetched, so the matrix bytes in
-//     flight do not depend on the reduction at the end of a row group;
-//   * codes are decoded in registers (prmt / shifts / masks, fp8_codec.cuh),
-//     multiplied with packed FP32 FMAs (fma.rn.f32x2), reduced with warp
-//     shuffles and one shared-memory step across the warps.
-//   Products of two decoded values are exact in FP32, so only the summation
-//   order differs from the reference (whose order is unspecified as well).
+// gemv_rows_kernel (N % 16 == 0, 16-byte aligned rows)
+//   * each WARP owns RW rows for all columns, so a row's sum never leaves the
+//     warp: one shuffle butterfly per warp, no CTA-wide reduction;
+//   * lanes stream 16-byte (128-bit) chunks with non-allocating loads, RW * U
+//     of them in flight per lane;
+//   * the vector is decoded once per CTA to FP16 pairs in shared memory (the
+//     decoded values of both formats are FP16 numbers), conflict-free layout;
+//   * codes are decoded in registers and multiplied with fma.rn.f32.f16 (FP16
+//     operands, FP32 accumulator; the product is exact in FP32);
+//   * launched with programmatic stream serialisation; with the static-matrix
+//     promise the first matrix loads are issued before the stream-order wait.
 //
 // gemv_general_kernel: any N % 4 == 0, 4-byte aligned; one warp per row, word
-//   loads.  Used for ragged shapes and tiny matrices.
+//   loads.  Used for ragged shapes.
 #pragma once
-#include "fp8_codec.cuh"
+#include "gemv_common.cuh"
 
 namespace feather {
 
-// Shared memory of gemv_stream_kernel: the FP32 vector tile, then two
-// buffers of WARPS x R partial sums.
-constexpr int gemv_stream_smem_bytes(int tile_codes, int warps, int rows) {
-    return tile_codes * 4 + 2 * warps * rows * 4;
+// Shared memory of gemv_rows_kernel: the FP16 vector tile.
+constexpr int kRowsTileCodes = 32768;                 // codes of the vector resident at a time
+constexpr int kRowsThreads = 256;                     // 8 warps
+constexpr int gemv_rows_smem_bytes(int n_codes) {
+    return (n_codes < kRowsTileCodes ? ((n_codes + 511) / 512) * 512 : kRowsTileCodes) * 2;
 }
 
-__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
-    uint4 r;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                 : "l"(p));
-    return r;
-}
-
-__device__ __forceinline__ float warp_sum(float x) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xFFFFFFFFu, x, o);
-    return x;
-}
-
-// Position of one step of a warp's walk: column tile, row group inside the
-// CTA's row block, column step inside the tile.
-struct Cursor {
-    int tile, task, step;
-};
-template <int V>
-struct IntTag {
-    static constexpr int value = V;
-};
-
-// TILE_CODES: codes of the vector resident (as FP32) at a time; a multiple of 512.
-template <int MODE, int WARPS, int R, int MIN_CTAS, int TILE_CODES>
-__global__ void __launch_bounds__(WARPS * 32, MIN_CTAS)
-gemv_stream_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
-                   float* __restrict__ out, int M, int n16) {
-    constexpr int kTileCodes = TILE_CODES;
-    constexpr int kTileChunks = kTileCodes / 16;   // 16-byte chunks per tile
-    constexpr int kTileGroups = kTileChunks / 32;  // warp-wide groups per tile
-    constexpr int kVecSmemBytes = kTileCodes * 4;
-    static_assert(TILE_CODES % 512 == 0, "tile must hold whole warp-wide groups");
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    float4* vec = reinterpret_cast<float4*>(smem_raw);  // kTileCodes floats
-    float* red = reinterpret_cast<float*>(smem_raw + kVecSmemBytes);  // [2][WARPS][R]
-
+template <int MODE, int RW, int U, bool EARLY>
+__global__ void __launch_bounds__(kRowsThreads)
+gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
+                 float* __restrict__ out, int M, int n16) {
+    extern __shared__ __align__(16) unsigned char rows_smem[];
+    uint4* vec = reinterpret_cast<uint4*>(rows_smem);
+    constexpr int kWarps = kRowsThreads / 32;
+    constexpr int kTileChunks = kRowsTileCodes / 16;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int row0 = (blockIdx.x * kWarps + warp) * RW;
+    const bool active = row0 < M;                     // warp-uniform
+    const uint4* rows[RW];
+#pragma unroll
+    for (int r = 0; r < RW; ++r) rows[r] = m + (size_t)min(row0 + r, M - 1) * n16;
 
-    // contiguous row block of this CTA
-    const int row_begin = (int)(((long long)M * blockIdx.x) / gridDim.x);
-    const int row_end = (int)(((long long)M * (blockIdx.x + 1)) / gridDim.x);
-    const int n_tasks = (row_end - row_begin + R - 1) / R;
-    if (n_tasks == 0) return;
-    const int n_tiles = (n16 + kTileChunks - 1) / kTileChunks;
-    // column steps per (tile, task): the widest tile decides; narrower tiles
-    // mask the excess.  Every warp executes the same number of steps.
-    const int tile_groups = min(kTileGroups, (n16 + 31) / 32);
-    const int steps = (tile_groups + WARPS - 1) / WARPS;
-
-    auto advance = [&](Cursor& c) {
-        if (++c.step == steps) {
-            c.step = 0;
-            if (++c.task == n_tasks) { c.task = 0; ++c.tile; }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // first batch of matrix chunks; with the static-matrix promise they are
+    // requested before the stream-order wait
+    uint4 buf[U][RW];
+    auto issue = [&](int c0) {  // chunks c0 + u*32 + lane, u < U
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = c0 + u * 32 + lane;
+#pragma unroll
+            for (int r = 0; r < RW; ++r)
+                buf[u][r] = (active && c < n16) ? ldg_stream(rows[r] + c) : make_uint4(0, 0, 0, 0);
         }
     };
-    auto issue = [&](const Cursor& c, uint4 (&buf)[R]) {
-        const int q_local = (warp + c.step * WARPS) * 32 + lane;
-        const int q = c.tile * kTileChunks + q_local;
-        const bool ok = (c.tile < n_tiles) && (q_local < kTileChunks) && (q < n16);
-        const int row0 = row_begin + c.task * R;
+    if (EARLY) issue(0);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!EARLY) issue(0);
+
+    float acc[RW][4];
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int row = min(row0 + r, row_end - 1);
-            buf[r] = ok ? ldg_stream(m + (size_t)row * n16 + q) : make_uint4(0, 0, 0, 0);
-        }
-    };
+    for (int r = 0; r < RW; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
 
-    Cursor pre = {0, 0, 0}, cur = {0, 0, 0};
-    uint4 buf[2][R];
-    issue(pre, buf[0]);  // matrix bytes are on their way before the vector is staged
-    advance(pre);
-
-    float2 acc[R][2];
-#pragma unroll
-    for (int r = 0; r < R; ++r) acc[r][0] = acc[r][1] = make_float2(0.f, 0.f);
-
-    int red_buf = 0;
-    // One step of the walk; PAR selects which half of `buf` is consumed (the
-    // other half receives the prefetch), so register indices stay static.
-    auto step_fn = [&](auto par_tag) {
-        constexpr int PAR = decltype(par_tag)::value;
-        if (cur.task == 0 && cur.step == 0) {
-            // stage this column tile of the vector: decode to FP32, permuted so
-            // that (group g, quarter k, lane l) is one float4 at (g*4 + k)*32 + l
-            // and holds the values in decode_word's pair order.
-            __syncthreads();  // everyone is done reading the previous tile
-            const int w_begin = cur.tile * (kTileCodes / 4);
-            const int w_end = min(n16 * 4, w_begin + kTileCodes / 4);
-            const int w_fill = w_begin + min(steps * WARPS * 128, kTileCodes / 4);
-            for (int w = w_begin + threadIdx.x; w < w_fill; w += WARPS * 32) {
-                float2 lo = make_float2(0.f, 0.f), hi = lo;  // beyond N: zeros
-                if (w < w_end) decode_word<MODE>(__ldg(v + w), lo, hi);
-                const int wl = w - w_begin, chunk = wl >> 2, k = wl & 3;
-                vec[((chunk >> 5) * 4 + k) * 32 + (chunk & 31)] = make_float4(lo.x, lo.y, hi.x, hi.y);
+    for (int t0 = 0; t0 < n16; t0 += kTileChunks) {
+        // stage the vector tile as FP16 pairs: (group g, half k, lane l) is the
+        // uint4 at (g*2 + k)*32 + l and holds codes 16*(32g+l) + 8k .. +7
+        const int tile_chunks = min(kTileChunks, n16 - t0);
+        if (t0 > 0) __syncthreads();
+        {
+            uint2* vec2 = reinterpret_cast<uint2*>(vec);
+            const int w_valid = tile_chunks * 4, w_fill = ((tile_chunks + 31) / 32) * 128;
+            for (int wl = threadIdx.x; wl < w_fill; wl += kRowsThreads) {
+                uint32_t lo, hi;
+                decode_word_h2<MODE>(wl < w_valid ? __ldg(v + t0 * 4 + wl) : 0u, lo, hi);
+                const int chunk = wl >> 2, k = wl & 3;
+                vec2[(((chunk >> 5) * 2 + (k >> 1)) * 32 + (chunk & 31)) * 2 + (k & 1)] = make_uint2(lo, hi);
             }
-            __syncthreads();
         }
-        // prefetch the next step, then consume the current one
-        issue(pre, buf[PAR ^ 1]);
-        advance(pre);
-
-        const int g = warp + cur.step * WARPS;
-        if (g < kTileGroups) {
-            const float4* vs = vec + (g * 4) * 32 + lane;
+        __syncthreads();
+        const int c_end = t0 + tile_chunks;
+        for (int c0 = t0; c0 < c_end; c0 += U * 32) {
+            uint4 cur[U][RW];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const float4 vv = vs[k * 32];
-                const float2 v_lo = make_float2(vv.x, vv.y), v_hi = make_float2(vv.z, vv.w);
+            for (int u = 0; u < U; ++u)
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const uint4 mw = buf[PAR][r];
-                    const uint32_t word = k == 0 ? mw.x : k == 1 ? mw.y : k == 2 ? mw.z : mw.w;
-                    float2 lo, hi;
-                    decode_word<MODE>(word, lo, hi);
-                    acc[r][0] = __ffma2_rn(lo, v_lo, acc[r][0]);
-                    acc[r][1] = __ffma2_rn(hi, v_hi, acc[r][1]);
+                for (int r = 0; r < RW; ++r) cur[u][r] = buf[u][r];
+            issue(c0 + U * 32);  // next batch (zeros past the end of the rows)
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int cl = c0 - t0 + u * 32;  // group offset inside the tile
+                if (cl < tile_chunks) {           // warp-uniform; lanes past N hold zero codes
+                    const uint4 va = vec[((cl >> 5) * 2) * 32 + lane];
+                    const uint4 vb = vec[((cl >> 5) * 2 + 1) * 32 + lane];
+#pragma unroll
+                    for (int r = 0; r < RW; ++r) fma_chunk<MODE>(cur[u][r], va, vb, acc[r]);
                 }
             }
         }
-
-        if (cur.step == steps - 1) {
-            // end of a row group: reduce R sums over the CTA
-            float s[R];
+    }
+    if (!active) return;
+    float sums[RW];
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                s[r] = warp_sum((acc[r][0].x + acc[r][0].y) + (acc[r][1].x + acc[r][1].y));
-                acc[r][0] = acc[r][1] = make_float2(0.f, 0.f);
-            }
-            float* rb = red + red_buf * (WARPS * R);
-            if (lane == 0) {
-#pragma unroll
-                for (int r = 0; r < R; ++r) rb[warp * R + r] = s[r];
-            }
-            __syncthreads();
-            if (threadIdx.x < R) {
-                const int row = row_begin + cur.task * R + threadIdx.x;
-                if (row < row_end) {
-                    float t = 0.f;
-#pragma unroll
-                    for (int w = 0; w < WARPS; ++w) t += rb[w * R + threadIdx.x];
-                    if (cur.tile == 0) out[row] = t;
-                    else out[row] += t;  // same thread owns the row in every tile
-                }
-            }
-            red_buf ^= 1;
-        }
-        advance(cur);
-    };
-    while (true) {
-        step_fn(IntTag<0>{});
-        if (cur.tile >= n_tiles) break;
-        step_fn(IntTag<1>{});
-        if (cur.tile >= n_tiles) break;
+    for (int r = 0; r < RW; ++r) sums[r] = (acc[r][0] + acc[r][1]) + (acc[r][2] + acc[r][3]);
+    warp_reduce_rows<RW>(sums, lane);
+    if ((lane & (32 / RW - 1)) == 0) {
+        const int row = row0 + lane / (32 / RW);
+        if (row < M) out[row] = sums[0];
     }
 }
 

@@ -31,7 +31,7 @@
 // the status word and stops waiting; the host reads the word with
 // feather_device_status().  No multicast copies are used anywhere.
 #pragma once
-#include "fp8_codec.cuh"
+#include "gemv_common.cuh"
 
 namespace feather {
 
@@ -120,66 +120,6 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
     unsigned int v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
-}
-
-// acc += a.lo * b.lo ; acc2 += a.hi * b.hi   (FP16 operands, FP32 accumulate)
-__device__ __forceinline__ void fma_h2(uint32_t a, uint32_t b, float& acc_lo, float& acc_hi) {
-    asm("{ .reg .b16 a0, a1, b0, b1;\n"
-        "  mov.b32 {a0, a1}, %2; mov.b32 {b0, b1}, %3;\n"
-        "  fma.rn.f32.f16 %0, a0, b0, %0;\n"
-        "  fma.rn.f32.f16 %1, a1, b1, %1; }"
-        : "+f"(acc_lo), "+f"(acc_hi) : "r"(a), "r"(b));
-}
-
-// Decode the four codes of a word to two FP16 pairs (same pairing for the
-// matrix and the vector): E5M2 lo=(c0,c1) hi=(c2,c3); E4M3 lo=(c0,c2) hi=(c1,c3).
-template <int MODE>
-__device__ __forceinline__ void decode_word_h2(uint32_t w, uint32_t& lo, uint32_t& hi) {
-    if (MODE == kE5M2) {
-        lo = prmt(w, 0u, 0x1404u);
-        hi = prmt(w, 0u, 0x3424u);
-    } else {
-        lo = e4m3_pair_to_h2(w << 8);
-        hi = e4m3_pair_to_h2(w);
-    }
-}
-
-// One 16-byte chunk of a row (16 codes) times the matching 16 vector values
-// (va, vb: eight FP16 pairs in decode_word_h2's pairing) into four accumulators.
-template <int MODE>
-__device__ __forceinline__ void fma_chunk(const uint4 mw, const uint4 va, const uint4 vb,
-                                          float (&acc)[4]) {
-    uint32_t lo, hi;
-    decode_word_h2<MODE>(mw.x, lo, hi);
-    fma_h2(lo, va.x, acc[0], acc[1]);
-    fma_h2(hi, va.y, acc[2], acc[3]);
-    decode_word_h2<MODE>(mw.y, lo, hi);
-    fma_h2(lo, va.z, acc[0], acc[1]);
-    fma_h2(hi, va.w, acc[2], acc[3]);
-    decode_word_h2<MODE>(mw.z, lo, hi);
-    fma_h2(lo, vb.x, acc[0], acc[1]);
-    fma_h2(hi, vb.y, acc[2], acc[3]);
-    decode_word_h2<MODE>(mw.w, lo, hi);
-    fma_h2(lo, vb.z, acc[0], acc[1]);
-    fma_h2(hi, vb.w, acc[2], acc[3]);
-}
-
-// Sum RW per-lane values over the warp with a halving butterfly: after it, the
-// lanes with lane % (32/RW) == 0 hold the total of row lane / (32/RW) in v[0].
-template <int RW>
-__device__ __forceinline__ void warp_reduce_rows(float (&v)[RW], int lane) {
-    int o = 16;
-#pragma unroll
-    for (int n = RW; n > 1; n >>= 1, o >>= 1) {
-        const bool upper = (lane & o) != 0;
-#pragma unroll
-        for (int i = 0; i < n / 2; ++i) {
-            const float send = upper ? v[i] : v[i + n / 2];
-            const float keep = upper ? v[i + n / 2] : v[i];
-            v[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, o);
-        }
-    }
-    for (; o > 0; o >>= 1) v[0] += __shfl_xor_sync(0xFFFFFFFFu, v[0], o);
 }
 
 template <int CW, int RW, int CL, int STAGES, int TILE>

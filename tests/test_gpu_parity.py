@@ -380,6 +380,39 @@ def test_gemv_65536_sampled_rows(fb, c_oracle):
     assert torch.equal(y_blk, y[8192:16384])
 
 
+@pytest.mark.parametrize("shape", [(2048, 2048), (256, 2048), (5632, 2048), (2048, 5632), (32000, 2048)])
+def test_gemv_config5_tinyllama_shapes_e4m3_small_weights(fb, c_oracle, shape):
+    """The GEMV shapes of a TinyLlama-1.1B layer and its lm_head with N(0, 0.02)
+    weights in E4M3: more than half of the codes have exponent field 0, which
+    the reference kernel decodes as m * 2^-17 (not the IEEE m * 2^-9).  Parity
+    means reproducing that."""
+    M, N = shape
+    gen = torch.Generator(device="cuda").manual_seed(6)
+    W = (0.02 * torch.randn(M, N, device="cuda", generator=gen)).half()
+    x = torch.randn(N, device="cuda", generator=gen).half()
+    mw, vw = fb.pack_fp8_tensor(W, "E4M3"), fb.pack_fp8_tensor(x, "E4M3")
+    mh, vh = host_words(mw), host_words(vw)
+    codes = mh.view(np.uint8)
+    assert ((codes & 0x78) == 0).mean() > 0.5
+    assert np.array_equal(mh, c_oracle.pack(W.cpu().numpy(), "E4M3"))
+    y = fb.gemv_fp8_acc_fp32_gpu(mw, vw, shape, "E4M3").cpu().numpy()
+    ref = c_oracle.gemv(mh, vh, shape, "E4M3", acc="f64")
+    assert O.normalised_error(y, ref) < TOL
+    # the IEEE reading of the same codes gives a visibly different answer
+    ieee = O.decode_table("E4M3", "ieee")[codes].reshape(M, N).astype(np.float64) @ \
+        np.nan_to_num(O.decode_table("E4M3", "ieee")[vh.view(np.uint8)].astype(np.float64))
+    assert O.normalised_error(ieee, ref) > 1e-3
+
+
+def test_gemv_chain_driver_runs(fb):
+    from feather_b200 import chain
+    assert chain.weight_bytes() == 1034420224  # 22 layers + lm_head, one byte per weight
+    c = chain.GemvChain(layers=1)
+    c.token()
+    torch.cuda.synchronize()
+    assert len(c.ops) == 8 and all(torch.isfinite(o).all() for _, _, _, o in c.ops)
+
+
 # --------------------------------------------------------------------- dot --
 def test_dot_golden_and_docstring(fb, golden):
     g = golden("dot")
