@@ -25,7 +25,6 @@ import argparse
 import json
 import os
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -56,66 +55,85 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
+_POLLER = r"""
+import sys, time
+import pynvml as nv
+nv.nvmlInit()
+h = nv.nvmlDeviceGetHandleByIndex(int(sys.argv[1]))
+print("max", nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM), flush=True)
+while True:
+    t = time.time()
+    print(t, nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM),
+          nv.nvmlDeviceGetCurrentClocksEventReasons(h), flush=True)
+    time.sleep(0.002)
+"""
+
+
 class ClockSampler:
-    """Poll SM clock and throttle reasons through NVML while the timed region
-    runs (read-only queries)."""
+    """SM clock and throttle reasons while the timed region runs.
+
+    NVML is polled (read-only queries, every 2 ms) by a CHILD process: polling
+    from a thread of the benchmark process contends with its kernel launches for
+    the driver's locks, which at 8 GPUs slowed the timed region by 25 %.  The
+    child is started before the warm-up; samples are kept if their wall-clock
+    time falls inside the timed region."""
+
+    REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40,
+               "sw_thermal_slowdown": 0x20, "hw_power_brake_slowdown": 0x80,
+               "applications_clocks_setting": 0x2}
 
     def __init__(self, index: int):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
-        self._stop = threading.Event()
-        self._thread = None
+        self.proc, self.t0, self.t1 = None, None, None
+        if index < 0:
+            return
         try:
-            if index < 0:
-                raise ValueError("sampling disabled on this rank")
-            import pynvml
-            pynvml.nvmlInit()
-            self._nv = pynvml
-            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+            import subprocess
+            self.proc = subprocess.Popen([sys.executable, "-c", _POLLER, str(index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.first = self.proc.stdout.readline()  # "max <MHz>": the poller is up and polling
         except Exception:
-            self._nv = None
-
-    def _once(self):
-        nv = self._nv
-        self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
-        r = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
-        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40,
-                 "sw_thermal_slowdown": 0x20, "hw_power_brake_slowdown": 0x80,
-                 "applications_clocks_setting": 0x2}
-        for k, bit in names.items():
-            if r & bit:
-                self.reasons.add(k)
-
-    def _run(self):
-        while not self._stop.is_set():
-            try:
-                self._once()
-            except Exception:
-                break
-            self._stop.wait(0.005)
+            self.proc = None
 
     def __enter__(self):
-        if self._nv is not None:
-            self._thread = threading.Thread(target=self._run, daemon=True)
-            self._thread.start()
+        self.t0 = time.time()
         return self
 
     def __exit__(self, *exc):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join()
-        if self._nv is not None and not self.samples:
-            try:
-                self._once()
-            except Exception:
-                pass
+        self.t1 = time.time()
+        if self.proc is not None:
+            time.sleep(0.005)  # one more sample after the region, for very short regions
+            self.proc.terminate()
 
     def summary(self):
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
-        s = sorted(self.samples)
-        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(s)}
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        try:
+            text, _ = self.proc.communicate(timeout=10)
+        except Exception:
+            self.proc.kill()
+            return out
+        inside, nearest, reasons = [], None, 0
+        for line in [self.first] + text.splitlines():
+            f = line.split()
+            if len(f) == 2 and f[0] == "max":
+                out["sm_max_mhz"] = int(f[1])
+            elif len(f) == 3:
+                t, mhz, r = float(f[0]), int(f[1]), int(f[2])
+                if self.t0 <= t <= self.t1:
+                    inside.append(mhz)
+                    reasons |= r
+                elif t > self.t1 and nearest is None:
+                    nearest = (mhz, r)
+        if not inside and nearest is not None:  # region shorter than one polling period
+            inside, reasons = [nearest[0]], nearest[1]
+            out["note"] = "timed region shorter than the polling period: first sample after it"
+        if inside:
+            inside.sort()
+            out["sm_mhz"] = inside[len(inside) // 2]
+            out["samples"] = len(inside)
+            out["reasons"] = sorted(k for k, bit in self.REASONS.items() if reasons & bit)
+        return out
 
 
 def physical_gpu_index(local: int) -> int:
@@ -292,14 +310,15 @@ def run_ours(args) -> None:
                              else "NCCL all-gather after the local GEMV")
 
     # ---- the timed region: W warm-up steps, then exactly K steps -----------
+    # only rank 0 samples clocks; the poller process is up before the warm-up ends
+    clocks = ClockSampler(physical_gpu_index(local_rank) if rank == 0 else -1)
     for _ in range(W):
         step()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    # only rank 0 polls NVML: concurrent queries from every rank serialise in the driver
-    with ClockSampler(physical_gpu_index(local_rank) if rank == 0 else -1) as clocks:
+    with clocks:
         start.record()
         for _ in range(K):
             step()
@@ -459,6 +478,8 @@ def run_ours(args) -> None:
             "frac_of_peak": round(3 * M * N / ms_e / 1e6 / peak, 4)}
         del src
 
+    if world > 1:
+        op.close()  # unmap the peers' buffers (a collective: every rank calls it)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()

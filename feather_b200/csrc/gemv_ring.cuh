@@ -113,12 +113,16 @@ struct ShardArgs {
                                          //    to the peers as ONE coalesced block when it is done;
                                          // 0: each row is stored to the peers as it finishes
 };
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// System-scope relaxed accesses for the epoch flags.  Ordering comes from ONE
+// system-scope fence before the flag stores (release pattern) and one after the
+// flag loads (acquire pattern): a release store per peer would pay a full
+// system fence per peer, which at eight ranks cost more than the whole exchange.
+__device__ __forceinline__ void st_relaxed_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+__device__ __forceinline__ unsigned int ld_relaxed_sys(const unsigned int* p) {
     unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
 
@@ -385,12 +389,12 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
                     __threadfence_system();
                     for (int k = 1; k <= sh.world; ++k) {
                         const int p = (sh.rank + k) % sh.world;
-                        st_release_sys(sh.flags[p] + sh.rank, sh.epoch);
+                        st_relaxed_sys(sh.flags[p] + sh.rank, sh.epoch);
                     }
                     const unsigned long long t0 = global_timer_ns();
                     for (int q = 0; q < sh.world; ++q) {
                         // wrap-safe "flag has reached this epoch"
-                        while ((int)(ld_acquire_sys(my_flags + q) - sh.epoch) < 0) {
+                        while ((int)(ld_relaxed_sys(my_flags + q) - sh.epoch) < 0) {
                             if (global_timer_ns() - t0 > kWaitLimitNs) {
                                 atomicOr(status, 2u);  // a peer's slice did not arrive in time
                                 q = sh.world;
@@ -398,6 +402,7 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
                             }
                         }
                     }
+                    __threadfence_system();  // the peers' rows are visible to whatever runs next
                 }
             }
         }
