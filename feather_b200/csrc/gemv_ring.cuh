@@ -382,28 +382,28 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
             }
             __threadfence_system();  // the pushed rows are visible everywhere before the ticket
             __syncwarp();
-            if (lane == 0) {
-                unsigned int* my_flags = sh.flags[sh.rank];
-                if (atomicAdd(my_flags + kShardTicketWord, 1u) == gridDim.x - 1) {
-                    my_flags[kShardTicketWord] = 0u;  // every CTA has arrived: ready for the next call
-                    __threadfence_system();
-                    for (int k = 1; k <= sh.world; ++k) {
-                        const int p = (sh.rank + k) % sh.world;
-                        st_relaxed_sys(sh.flags[p] + sh.rank, sh.epoch);
-                    }
+            unsigned int* my_flags = sh.flags[sh.rank];
+            unsigned int ticket = 0;
+            if (lane == 0) ticket = atomicAdd(my_flags + kShardTicketWord, 1u);
+            ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
+            if (ticket == gridDim.x - 1) {
+                // last CTA of this rank: lane q tells rank q "my slice is with you"
+                // and waits for rank q's slice here -- all peers in parallel
+                if (lane == 0) my_flags[kShardTicketWord] = 0u;  // ready for the next call
+                __threadfence_system();
+                if (lane < sh.world) {
+                    st_relaxed_sys(sh.flags[lane] + sh.rank, sh.epoch);
                     const unsigned long long t0 = global_timer_ns();
-                    for (int q = 0; q < sh.world; ++q) {
-                        // wrap-safe "flag has reached this epoch"
-                        while ((int)(ld_relaxed_sys(my_flags + q) - sh.epoch) < 0) {
-                            if (global_timer_ns() - t0 > kWaitLimitNs) {
-                                atomicOr(status, 2u);  // a peer's slice did not arrive in time
-                                q = sh.world;
-                                break;
-                            }
+                    // wrap-safe "flag has reached this epoch"
+                    while ((int)(ld_relaxed_sys(my_flags + lane) - sh.epoch) < 0) {
+                        if (global_timer_ns() - t0 > kWaitLimitNs) {
+                            atomicOr(status, 2u);  // rank `lane`'s slice did not arrive in time
+                            break;
                         }
                     }
-                    __threadfence_system();  // the peers' rows are visible to whatever runs next
                 }
+                __syncwarp();
+                __threadfence_system();  // the peers' rows are visible to whatever runs next
             }
         }
     }
