@@ -349,6 +349,11 @@ def run_ours(args) -> None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             extra["same_step_with_nccl_all_gather_us"] = round(float(t.item()) * 1e3, 3)
         extra["local_gemv_kernel_us"] = round(kern_ms * 1e3, 3)
+        try:  # TinyLlama-shaped GEMV chain, tensor-parallel over the ranks (NCCL all-reduce)
+            from feather_b200 import chain
+            extra["tinyllama_gemv_chain_tensor_parallel"] = chain.measure_tp(tokens=20)
+        except Exception as e:  # noqa: BLE001 - must not sink the headline
+            extra["tinyllama_gemv_chain_tensor_parallel"] = {"error": repr(e)}
         kern_name = "gemv_ring_kernel<E5M2> (per-rank block)"
     achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": kern_name, "achieved": round(achieved, 1),

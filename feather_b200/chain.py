@@ -72,6 +72,104 @@ class GemvChain:
         return sum(m * n + n + 4 * m for _, _, (m, n), _ in self.ops)
 
 
+class TensorParallelChain:
+    """The same chain split over the ranks of a process group (one process per GPU).
+
+    * q/k/v/gate/up/lm_head are split by OUTPUT rows: rank r holds rows
+      ``[r*M/W, (r+1)*M/W)`` of each and the whole activation; its outputs stay
+      sharded (they feed the next, input-split, GEMV of a real model).
+    * o and down are split by INPUT columns: rank r holds columns
+      ``[r*N/W, (r+1)*N/W)`` of every row and the matching slice of the packed
+      activation; each rank produces a full-length partial sum and the partials
+      are added with an NCCL all-reduce (2048 floats, 2 per layer).
+
+    Weights are generated from the same seed, in the same order, as GemvChain's,
+    so the two can be compared.
+    """
+
+    def __init__(self, mode: str = "E4M3", seed: int = 6, group=None, layers: int = LAYERS,
+                 static_matrix: bool = True):
+        import torch.distributed as dist
+        self.dist, self.group = dist, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        W, r = self.world, self.rank
+        device = torch.device("cuda", torch.cuda.current_device())
+        gen = torch.Generator(device=device).manual_seed(seed)
+        self.mode, self.static_matrix = mode, static_matrix
+        self.ops = []  # (kind, packed weight shard, packed activation (slice), (rows, cols), out)
+        acts = {}
+        for n in (HIDDEN, INTER):
+            a = torch.randn(n, device=device, generator=gen, dtype=torch.float16)
+            acts[n] = fb.pack_fp8_tensor(a, mode)
+
+        def add(name: str, m: int, n: int) -> None:
+            w = (0.02 * torch.randn(m, n, device=device, generator=gen)).to(torch.float16)
+            if name in ("o", "down"):  # input split
+                if n % (4 * W):
+                    raise ValueError(f"{name}: {n} columns do not split into {W} whole-word slices")
+                cols = n // W
+                shard = w[:, r * cols:(r + 1) * cols].contiguous()
+                act = acts[n][r * cols // 4:(r + 1) * cols // 4]
+                self.ops.append(("cols", fb.pack_fp8_tensor(shard, mode), act, (m, cols),
+                                 torch.empty(m, dtype=torch.float32, device=device)))
+            else:  # output split
+                if m % W:
+                    raise ValueError(f"{name}: {m} rows do not split over {W} ranks")
+                rows = m // W
+                shard = w[r * rows:(r + 1) * rows]
+                self.ops.append(("rows", fb.pack_fp8_tensor(shard, mode), acts[n], (rows, n),
+                                 torch.empty(rows, dtype=torch.float32, device=device)))
+        for _ in range(layers):
+            for name, m, n in LAYER_SHAPES:
+                add(name, m, n)
+        add("lm_head", VOCAB, HIDDEN)
+        torch.cuda.synchronize()
+
+    def token(self) -> None:
+        for kind, w, a, shape, out in self.ops:
+            fb.gemv_fp8_acc_fp32_gpu(w, a, shape, self.mode, out=out, static_matrix=self.static_matrix)
+            if kind == "cols" and self.world > 1:
+                self.dist.all_reduce(out, group=self.group)
+
+
+def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", group=None) -> dict:
+    """Tokens per second of the tensor-parallel chain (call on every rank)."""
+    import torch.distributed as dist
+    chain = TensorParallelChain(mode, group=group)
+    for _ in range(3):
+        chain.token()
+    torch.cuda.synchronize()
+    run, graphed = chain.token, False
+    if use_graph:
+        try:
+            stream = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(stream):
+                chain.token()
+                torch.cuda.synchronize()
+                with torch.cuda.graph(graph, stream=stream):
+                    chain.token()
+            graph.replay()
+            torch.cuda.synchronize()
+            run, graphed = graph.replay, True
+        except Exception:  # noqa: BLE001 - collectives that cannot be captured: time eagerly
+            torch.cuda.synchronize()
+    dist.barrier(group=group)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(tokens):
+        run()
+    end.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([start.elapsed_time(end) / tokens], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    ms = float(t.item())
+    return {"tokens_per_s": round(1e3 / ms, 1), "us_per_token": round(ms * 1e3, 1),
+            "gemvs_per_token_per_rank": len(chain.ops),
+            "all_reduces_per_token": sum(1 for o in chain.ops if o[0] == "cols"),
+            "world": chain.world, "cuda_graph": graphed, "mode": mode}
+
+
 def measure(tokens: int = 50, use_graph: bool = True, mode: str = "E4M3",
             merge_projections: bool = False) -> dict:
     chain = GemvChain(mode, merge_projections=merge_projections)

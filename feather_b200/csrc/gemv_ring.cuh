@@ -29,7 +29,7 @@
 //
 // Every wait is bounded: after kWaitLimitNs without progress a thread raises
 // the status word and stops waiting; the host reads the word with
-// feather_device_status().  No multicast copies are used anywhere.
+// feather_device_status().  Every copy has exactly one destination CTA.
 #pragma once
 #include "gemv_common.cuh"
 

@@ -54,7 +54,17 @@ def _worker(rank: int, world: int, port: int, q):
                 ok_bits &= bool(torch.equal(y, y_single))
                 ok_err &= O.normalised_error(y.cpu().numpy(), ref) < 1e-5
             fb.device_status()
-        q.put((rank, ok_bits and modes == ([False, True] if world > 1 else [False]), ok_err))
+        # tensor-parallel GEMV chain (one layer + lm_head) against the single-GPU chain
+        from feather_b200 import chain
+        tp = chain.TensorParallelChain(layers=1)
+        single = chain.GemvChain(layers=1)
+        tp.token(); single.token()
+        torch.cuda.synchronize()
+        ok_tp = len(tp.ops) == len(single.ops) == 8
+        for (kind, _, _, shape, out_tp), (_, _, (m, n), out_1) in zip(tp.ops, single.ops):
+            ref1 = out_1 if kind == "cols" else out_1[rank * shape[0]:(rank + 1) * shape[0]]
+            ok_tp &= O.normalised_error(out_tp.cpu().numpy(), ref1.cpu().numpy()) < 1e-5
+        q.put((rank, ok_bits and ok_tp and modes == ([False, True] if world > 1 else [False]), ok_err))
     except Exception as e:
         q.put((rank, "failed", repr(e)))
     finally:
