@@ -31,6 +31,10 @@ constexpr int gemv_rows_smem_bytes(int n_codes) {
     return (n_codes < kRowsTileCodes ? ((n_codes + 511) / 512) * 512 : kRowsTileCodes) * 2;
 }
 
+// Grid: when the whole vector fits one tile (N <= kRowsTileCodes) any grid up to
+// the number of row groups works and each CTA walks groups blockIdx.x,
+// blockIdx.x + gridDim.x, ... with the vector staged once; otherwise the grid
+// must equal the number of row groups (one group per CTA, tiles inside).
 template <int MODE, int RW, int U, bool EARLY>
 __global__ void __launch_bounds__(kRowsThreads)
 gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
@@ -39,9 +43,12 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
     uint4* vec = reinterpret_cast<uint4*>(rows_smem);
     constexpr int kWarps = kRowsThreads / 32;
     constexpr int kTileChunks = kRowsTileCodes / 16;
+    constexpr int kGroupRows = kWarps * RW;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int row0 = (blockIdx.x * kWarps + warp) * RW;
-    const bool active = row0 < M;                     // warp-uniform
+    const int n_groups = (M + kGroupRows - 1) / kGroupRows;
+    int group = blockIdx.x;
+    int row0 = (group * kWarps + warp) * RW;
+    bool active = row0 < M;                           // warp-uniform
     const uint4* rows[RW];
 #pragma unroll
     for (int r = 0; r < RW; ++r) rows[r] = m + (size_t)min(row0 + r, M - 1) * n16;
@@ -50,38 +57,99 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
     // first batch of matrix chunks; with the static-matrix promise they are
     // requested before the stream-order wait
     uint4 buf[U][RW];
-    auto issue = [&](int c0) {  // chunks c0 + u*32 + lane, u < U
+    auto issue = [&](const uint4* const (&rp)[RW], bool on, int c0) {  // chunks c0 + u*32 + lane
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int c = c0 + u * 32 + lane;
 #pragma unroll
             for (int r = 0; r < RW; ++r)
-                buf[u][r] = (active && c < n16) ? ldg_stream(rows[r] + c) : make_uint4(0, 0, 0, 0);
+                buf[u][r] = (on && c < n16) ? ldg_stream(rp[r] + c) : make_uint4(0, 0, 0, 0);
         }
     };
-    if (EARLY) issue(0);
+    if (EARLY) issue(rows, active, 0);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (!EARLY) issue(0);
+    if (!EARLY) issue(rows, active, 0);
 
     float acc[RW][4];
 #pragma unroll
     for (int r = 0; r < RW; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
-
-    for (int t0 = 0; t0 < n16; t0 += kTileChunks) {
-        // stage the vector tile as FP16 pairs: (group g, half k, lane l) is the
-        // uint4 at (g*2 + k)*32 + l and holds codes 16*(32g+l) + 8k .. +7
-        const int tile_chunks = min(kTileChunks, n16 - t0);
-        if (t0 > 0) __syncthreads();
-        {
-            uint2* vec2 = reinterpret_cast<uint2*>(vec);
-            const int w_valid = tile_chunks * 4, w_fill = ((tile_chunks + 31) / 32) * 128;
-            for (int wl = threadIdx.x; wl < w_fill; wl += kRowsThreads) {
-                uint32_t lo, hi;
-                decode_word_h2<MODE>(wl < w_valid ? __ldg(v + t0 * 4 + wl) : 0u, lo, hi);
-                const int chunk = wl >> 2, k = wl & 3;
-                vec2[(((chunk >> 5) * 2 + (k >> 1)) * 32 + (chunk & 31)) * 2 + (k & 1)] = make_uint2(lo, hi);
+    auto finish_rows = [&]() {  // butterfly over the warp, the row's lane writes
+        if (active) {
+            float sums[RW];
+#pragma unroll
+            for (int r = 0; r < RW; ++r) sums[r] = (acc[r][0] + acc[r][1]) + (acc[r][2] + acc[r][3]);
+            warp_reduce_rows<RW>(sums, lane);
+            if ((lane & (32 / RW - 1)) == 0) {
+                const int row = row0 + lane / (32 / RW);
+                if (row < M) out[row] = sums[0];
             }
         }
+#pragma unroll
+        for (int r = 0; r < RW; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+    };
+    // stage `tile_chunks` chunks of the vector from chunk t0 as FP16 pairs:
+    // (group g, half k, lane l) is the uint4 at (g*2 + k)*32 + l and holds
+    // codes 16*(32g+l) + 8k .. +7; the last group is padded with zero codes
+    auto stage = [&](int t0, int tile_chunks) {
+        uint2* vec2 = reinterpret_cast<uint2*>(vec);
+        const int w_valid = tile_chunks * 4, w_fill = ((tile_chunks + 31) / 32) * 128;
+        for (int wl = threadIdx.x; wl < w_fill; wl += kRowsThreads) {
+            uint32_t lo, hi;
+            decode_word_h2<MODE>(wl < w_valid ? __ldg(v + t0 * 4 + wl) : 0u, lo, hi);
+            const int chunk = wl >> 2, k = wl & 3;
+            vec2[(((chunk >> 5) * 2 + (k >> 1)) * 32 + (chunk & 31)) * 2 + (k & 1)] = make_uint2(lo, hi);
+        }
+    };
+    // one batch: U groups of 32 chunks starting at tile-local chunk `cl0`
+    auto compute = [&](const uint4 (&cur)[U][RW], int cl0, int tile_chunks) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int cl = cl0 + u * 32;
+            if (cl < tile_chunks) {  // warp-uniform; lanes past N hold zero codes
+                const uint4 va = vec[((cl >> 5) * 2) * 32 + lane];
+                const uint4 vb = vec[((cl >> 5) * 2 + 1) * 32 + lane];
+#pragma unroll
+                for (int r = 0; r < RW; ++r) fma_chunk<MODE>(cur[u][r], va, vb, acc[r]);
+            }
+        }
+    };
+
+    if (n16 <= kTileChunks) {
+        // the whole vector is resident: walk this CTA's row groups, always one
+        // batch of loads ahead (across the group boundary too)
+        stage(0, n16);
+        __syncthreads();
+        while (group < n_groups) {
+            const int next = group + (int)gridDim.x;
+            const int next_row0 = (next * kWarps + warp) * RW;
+            const bool next_active = next < n_groups && next_row0 < M;
+            const uint4* next_rows[RW];
+#pragma unroll
+            for (int r = 0; r < RW; ++r) next_rows[r] = m + (size_t)min(next_row0 + r, M - 1) * n16;
+            for (int c0 = 0; c0 < n16; c0 += U * 32) {
+                uint4 cur[U][RW];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+#pragma unroll
+                    for (int r = 0; r < RW; ++r) cur[u][r] = buf[u][r];
+                if (c0 + U * 32 < n16) issue(rows, active, c0 + U * 32);
+                else issue(next_rows, next_active, 0);
+                compute(cur, c0, n16);
+            }
+            finish_rows();
+            group = next;
+            row0 = next_row0;
+            active = next_active;
+#pragma unroll
+            for (int r = 0; r < RW; ++r) rows[r] = next_rows[r];
+        }
+        return;
+    }
+    // long rows: one row group per CTA, the vector in tiles
+    for (int t0 = 0; t0 < n16; t0 += kTileChunks) {
+        const int tile_chunks = min(kTileChunks, n16 - t0);
+        if (t0 > 0) __syncthreads();
+        stage(t0, tile_chunks);
         __syncthreads();
         const int c_end = t0 + tile_chunks;
         for (int c0 = t0; c0 < c_end; c0 += U * 32) {
@@ -90,28 +158,11 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
             for (int u = 0; u < U; ++u)
 #pragma unroll
                 for (int r = 0; r < RW; ++r) cur[u][r] = buf[u][r];
-            issue(c0 + U * 32);  // next batch (zeros past the end of the rows)
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int cl = c0 - t0 + u * 32;  // group offset inside the tile
-                if (cl < tile_chunks) {           // warp-uniform; lanes past N hold zero codes
-                    const uint4 va = vec[((cl >> 5) * 2) * 32 + lane];
-                    const uint4 vb = vec[((cl >> 5) * 2 + 1) * 32 + lane];
-#pragma unroll
-                    for (int r = 0; r < RW; ++r) fma_chunk<MODE>(cur[u][r], va, vb, acc[r]);
-                }
-            }
+            issue(rows, active, c0 + U * 32);  // next batch (zeros past the end of the rows)
+            compute(cur, c0 - t0, tile_chunks);
         }
     }
-    if (!active) return;
-    float sums[RW];
-#pragma unroll
-    for (int r = 0; r < RW; ++r) sums[r] = (acc[r][0] + acc[r][1]) + (acc[r][2] + acc[r][3]);
-    warp_reduce_rows<RW>(sums, lane);
-    if ((lane & (32 / RW - 1)) == 0) {
-        const int row = row0 + lane / (32 / RW);
-        if (row < M) out[row] = sums[0];
-    }
+    finish_rows();
 }
 
 // One warp per row, 4-byte loads: every N % 4 == 0, any 4-byte alignment.
