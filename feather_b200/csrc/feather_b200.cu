@@ -266,59 +266,8 @@ static int gemv_rows_launch(const uint32_t* m, const uint32_t* v, float* out, lo
     static std::atomic<unsigned long long> configured{0};
     if (int st = ensure_smem(kernel, gemv_rows_smem_bytes(kRowsTileCodes), configured)) return st;
     const long long rows_per_cta = (kRowsThreads / 32) * RW;
-    // one CTA per row group: a resident-sized grid that walks several groups was
-    // measured slower (uneven group counts per CTA) on every shape tried
-    const long long grid = (M + rows_per_cta - 1) / rows_per_cta;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(G::kThreads);
-    cfg.dynamicSmemBytes = G::kSmemBytes;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const unsigned char*>(m),
-                                             v, out, (int)M, (int)(N / 16), status, shard);
-    return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
-}
-
-// Shapes the bulk-copy ring kernel takes: 16-byte aligned rows, rows long
-// enough for 4 KiB copies, and at least two full tasks for every SM.
-static bool ring_eligible(const void* m, long long M, long long N, const DeviceInfo& dev) {
-    return (N % 16 == 0) && aligned(m, 16) && N >= 4096 &&
-           M >= 2ll * dev.sm_count * kRingCW * kRingRW;
-}
-
-template <int MODE, int RW, int U, bool EARLY>
-static int gemv_rows_launch(const uint32_t* m, const uint32_t* v, float* out, long long M,
-                            long long N, cudaStream_t s) {
-    auto kernel = gemv_rows_kernel<MODE, RW, U, EARLY>;
-    static std::atomic<unsigned long long> configured{0};
-    if (int st = ensure_smem(kernel, gemv_rows_smem_bytes(kRowsTileCodes), configured)) return st;
-    const long long rows_per_cta = (kRowsThreads / 32) * RW;
-    // one CTA per row group: a resident-sized grid that walks several groups was
-    // measured slower (uneven group counts per CTA) on every shape tried
-    const long long grid = (M + rows_per_cta - 1) / rows_per_cta;
-    if (N <= kRowsTileCodes) {
-        // the vector fits one tile: a resident-sized grid walks the groups
-        static std::atomic<int> ctas_per_sm[64];
-        int devid = 0, sms = 0;
-        cudaGetDevice(&devid);
-        int occ = ctas_per_sm[devid & 63].load(std::memory_order_acquire);
-        if (occ == 0) {
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-                    &occ, kernel, kRowsThreads, gemv_rows_smem_bytes(kRowsTileCodes)) != cudaSuccess || occ < 1)
-                occ = 1;
-            ctas_per_sm[devid & 63].store(occ, std::memory_order_release);
-        }
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, devid);
-        const long long resident = (long long)(sms > 0 ? sms : 1) * occ;
-        if (grid > resident) grid = resident;
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
+    cfg.gridDim = dim3((unsigned)((M + rows_per_cta - 1) / rows_per_cta));
     cfg.blockDim = dim3(kRowsThreads);
     cfg.dynamicSmemBytes = gemv_rows_smem_bytes((int)(N > kRowsTileCodes ? kRowsTileCodes : N));
     cfg.stream = s;
