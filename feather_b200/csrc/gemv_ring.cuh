@@ -15,13 +15,16 @@
 //     [M*b/G, M*(b+1)/G) and walks them in tasks of CW*RW rows;
 //   * a stage holds, for every row of the task, the same SEGB = CL*512 bytes
 //     of columns (one bulk copy per row and stage, issued by the lanes of the
-//     producer warp in parallel);
+//     producer warp in parallel); the walk is tasks, then column segments;
 //   * consumer warp w OWNS rows w*RW .. w*RW+RW-1 of the task for all columns,
 //     so a row's sum never leaves the warp: no CTA-wide barrier in the loop,
 //     only mbarrier waits, and one shuffle butterfly per task;
-//   * the vector is decoded ONCE per CTA and column tile to FP16 pairs in
-//     shared memory (the decoded values of both formats are FP16 numbers), in
-//     a layout whose 128-bit reads are conflict-free;
+//   * the vector lives in shared memory as FP16 pairs (the decoded values of
+//     both formats are FP16 numbers) in a layout whose 128-bit reads are
+//     conflict-free.  Up to 16384 codes it is decoded once per CTA; longer
+//     vectors are cut into pieces of 8192 codes that alternate between two
+//     buffers, staged by a dedicated warp one piece ahead of the consumers;
+//     partial row sums between pieces stay in shared memory;
 //   * matrix codes are decoded in registers to FP16 pairs (fp8_codec.cuh) and
 //     multiplied with the mixed-precision FMA fma.rn.f32.f16 (FP16 operands,
 //     FP32 accumulator, one rounding): the product of two FP16 numbers is
@@ -132,18 +135,62 @@ struct RingGeometry {
     static constexpr int kSegChunks = CL * 32;         // 16-byte chunks per row and stage
     static constexpr int kSegBytes = kSegChunks * 16;
     static constexpr int kStageBytes = kTaskRows * kSegBytes;
-    static constexpr int kTileChunks = TILE / 16;
-    static constexpr int kVecBytes = TILE * 2;         // FP16 vector tile
-    static constexpr int kSmemBytes = kVecBytes + STAGES * kStageBytes + (2 * STAGES + 2) * 8 +
+    static constexpr int kTileChunks = TILE / 16;      // vector chunks resident when N <= TILE
+    static constexpr int kHalfChunks = kTileChunks / 2;  // per buffer when the vector is longer
+    static constexpr int kVecBytes = TILE * 2;         // FP16 vector region (one tile or two halves)
+    // mbarriers: full[STAGES], empty[STAGES], start, vec_full[2], vec_empty[2]; then one counter word
+    static constexpr int kBarriers = 2 * STAGES + 5;
+    static constexpr int kSmemBytes = kVecBytes + STAGES * kStageBytes + (kBarriers + 1) * 8 +
                                       kShardStageRows * 4;
-    static constexpr int kThreads = (CW + 1) * 32;
-    static_assert(kTileChunks % kSegChunks == 0, "a tile holds whole segments");
+    static constexpr int kThreads = (CW + 2) * 32;     // consumers, producer warp, vector warp
+    static_assert(kHalfChunks % kSegChunks == 0, "a vector half holds whole segments");
 };
 
+// Stage `n_chunks` chunks (16 codes each) of the packed vector, starting at word
+// `v`, into `dst` as FP16 pairs: (group g, half k, lane l) is the uint4 at
+// (g*2 + k)*32 + l and holds codes 16*(32g+l) + 8k .. +7.  Chunks from n_chunks
+// up to `fill_chunks` are written as zero codes.  Called by `n_threads` threads
+// with ids `tid`; BATCH loads are in flight per thread (the loads come from L2,
+// so a single warp needs a deep batch to stage a piece in about a microsecond).
+template <int MODE, int BATCH>
+__device__ __forceinline__ void stage_vector(uint4* dst, const uint32_t* __restrict__ v,
+                                             int n_chunks, int fill_chunks, int tid, int n_threads) {
+    uint2* vec2 = reinterpret_cast<uint2*>(dst);
+    const int w_valid = n_chunks * 4, w_fill = fill_chunks * 4;
+    constexpr int kBatch = BATCH;
+    for (int w0 = tid; w0 < w_fill; w0 += kBatch * n_threads) {
+        uint32_t raw[kBatch];
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            const int wl = w0 + b * n_threads;
+            raw[b] = wl < w_valid ? __ldg(v + wl) : 0u;  // beyond N: code 0 = +0.0
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+            const int wl = w0 + b * n_threads;
+            if (wl < w_fill) {
+                uint32_t lo, hi;
+                decode_word_h2<MODE>(raw[b], lo, hi);
+                const int chunk = wl >> 2, k = wl & 3;
+                vec2[(((chunk >> 5) * 2 + (k >> 1)) * 32 + (chunk & 31)) * 2 + (k & 1)] = make_uint2(lo, hi);
+            }
+        }
+    }
+}
+
+// The walk every role follows: vector pieces outermost, then the tasks (row
+// groups of the CTA), then the 4 KiB segments of the piece.
+//   short rows (N <= TILE): one piece, the whole vector, staged once by the
+//     consumer warps;
+//   long rows: pieces of TILE/2 codes that alternate between the two halves of
+//     the vector region; a dedicated warp stages piece p+1 while the consumers
+//     use piece p, so the stream never drains at a piece boundary.  Partial row
+//     sums between pieces stay in shared memory.
+//
 // CTAS: CTAs resident per SM the launch is sized for.  PREFETCH: the producer
-// also asks L2 for the next task's rows (cp.async.bulk.prefetch.L2) when it
-// starts a task, so HBM reads run a whole task ahead of the ring.
-// FUSED: the kernel is one rank of a row-sharded GEMV.  Each finished row is
+// also asks L2 for the next task's rows (cp.async.bulk.prefetch.L2); measured
+// slower and left off.
+// FUSED: the kernel is one rank of a row-sharded GEMV.  Finished rows are
 // stored straight into EVERY rank's output buffer (plain stores to peer-mapped
 // memory over NVLink), so the gather of the output slices happens inside the
 // GEMV instead of in a separate collective.  When the last CTA of the rank is
@@ -157,7 +204,7 @@ struct RingGeometry {
 // drains; the vector is read and the output written only after the wait.
 template <int MODE, int CW, int RW, int CL, int STAGES, int TILE, int CTAS, bool PREFETCH,
           bool FUSED = false, bool EARLY = false>
-__global__ void __launch_bounds__((CW + 1) * 32, CTAS)
+__global__ void __launch_bounds__((CW + 2) * 32, CTAS)
 gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict__ v,
                  float* __restrict__ out, int M, int n16, unsigned int* __restrict__ status,
                  const __grid_constant__ ShardArgs sh = ShardArgs{}) {
@@ -172,66 +219,92 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
     uint4* vec = reinterpret_cast<uint4*>(smem);
     unsigned char* ring = smem + G::kVecBytes;
     const uint32_t ring_s = smem_u32(ring);
-    const uint32_t bars = smem_u32(ring + STAGES * G::kStageBytes);  // full[STAGES], empty[STAGES]
+    unsigned char* bar_mem = ring + STAGES * G::kStageBytes;
+    const uint32_t bars = smem_u32(bar_mem);
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    const uint32_t tile_bar = bars + 8u * (2 * STAGES);  // all consumer threads
-    unsigned int* warps_done = reinterpret_cast<unsigned int*>(ring + STAGES * G::kStageBytes +
-                                                               8 * (2 * STAGES + 1));
-    float* staged_rows = reinterpret_cast<float*>(ring + STAGES * G::kStageBytes + 8 * (2 * STAGES + 2));
+    const uint32_t start_bar = bars + 8u * (2 * STAGES);       // all consumer threads
+    auto vec_full = [&](int b) { return bars + 8u * (2 * STAGES + 1 + b); };
+    auto vec_empty = [&](int b) { return bars + 8u * (2 * STAGES + 3 + b); };
+    unsigned int* warps_done = reinterpret_cast<unsigned int*>(bar_mem + 8 * G::kBarriers);
+    float* staged_rows = reinterpret_cast<float*>(bar_mem + 8 * (G::kBarriers + 1));
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row_begin = (int)(((long long)M * blockIdx.x) / gridDim.x);
     const int row_end = (int)(((long long)M * (blockIdx.x + 1)) / gridDim.x);
     const int n_tasks = (row_end - row_begin + G::kTaskRows - 1) / G::kTaskRows;
-    const int n_tiles = (n16 + G::kTileChunks - 1) / G::kTileChunks;
+    // Rows per task.  E5M2 is bound by the bytes in flight, so its rows are
+    // balanced over the tasks: 55 rows are walked as 14+14+14+13, not 16+16+16+7,
+    // and no stage of the ring is mostly empty.  E4M3 is bound by instruction
+    // issue and keeps every consumer warp busy instead (full tasks, one short).
+    const int task_rows = (MODE == kE5M2 && n_tasks > 0)
+        ? ((row_end - row_begin + n_tasks * RW - 1) / (n_tasks * RW)) * RW : G::kTaskRows;
     const size_t row_bytes = (size_t)n16 * 16;
+    const bool long_rows = n16 > G::kTileChunks;
+    const int piece_chunks = long_rows ? G::kHalfChunks : G::kTileChunks;  // vector chunks per piece
+    const int n_pieces = (n16 + piece_chunks - 1) / piece_chunks;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(full_bar(s), 1);     // the producer's arrive + the copied bytes
             mbar_init(empty_bar(s), CW);   // one arrive per consumer warp
         }
-        mbar_init(tile_bar, CW * 32);
+        mbar_init(start_bar, CW * 32);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(vec_full(b), 1);     // the vector warp, once the piece is staged
+            mbar_init(vec_empty(b), CW);   // one arrive per consumer warp
+        }
         *warps_done = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     if (n_tasks == 0 && !FUSED) return;  // a fused rank needs every CTA at the final ticket
 
+    if (warp == CW + 1) {
+        // ---------------------------------------------------- vector warp --
+        if (!long_rows) return;
+        if (EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");  // it reads the vector
+        for (int piece = 0; piece < n_pieces; ++piece) {
+            const int b = piece & 1;  // pieces alternate between the two halves
+            // the half is free once the consumers are done with piece - 2
+            if (piece >= 2 && !mbar_wait(vec_empty(b), (uint32_t)((piece >> 1) - 1) & 1u, status)) return;
+            const int chunks = min(piece_chunks, n16 - piece * piece_chunks);
+            const int fill = ((chunks + G::kSegChunks - 1) / G::kSegChunks) * G::kSegChunks;
+            stage_vector<MODE, 8>(vec + b * (G::kHalfChunks * 2), v + (size_t)piece * piece_chunks * 4,
+                                   chunks, fill, lane, 32);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(vec_full(b));
+        }
+        return;
+    }
+
     if (warp == CW) {
         // ------------------------------------------------------- producer --
         int s = 0;               // ring slot of the next stage
         uint32_t round = 0;      // how many times the ring has wrapped
         bool alive = true;
-        for (int tile = 0; tile < n_tiles && alive; ++tile) {
-            const int tile_chunks = min(G::kTileChunks, n16 - tile * G::kTileChunks);
-            const int n_seg = (tile_chunks + G::kSegChunks - 1) / G::kSegChunks;
+        for (int piece = 0; piece < n_pieces && alive; ++piece) {
+            const int chunks_p = min(piece_chunks, n16 - piece * piece_chunks);
+            const int n_seg = (chunks_p + G::kSegChunks - 1) / G::kSegChunks;
             for (int task = 0; task < n_tasks && alive; ++task) {
-                const int row0 = row_begin + task * G::kTaskRows;
-                const int valid_rows = min(G::kTaskRows, row_end - row0);
-                if (PREFETCH) {
-                    // next task of this tile (or the first task of the next tile)
-                    int p_tile = tile, p_row0 = row0 + G::kTaskRows;
-                    if (task + 1 == n_tasks) { p_tile = tile + 1; p_row0 = row_begin; }
-                    if (p_tile < n_tiles) {
-                        const int p_chunks = min(G::kTileChunks, n16 - p_tile * G::kTileChunks);
-                        const int p_rows = min(G::kTaskRows, row_end - p_row0);
-                        for (int r = lane; r < p_rows; r += 32)
-                            bulk_prefetch_l2(m + (size_t)(p_row0 + r) * row_bytes +
-                                                 (size_t)p_tile * G::kTileChunks * 16,
-                                             (uint32_t)p_chunks * 16u);
-                    }
+                const int row0 = row_begin + task * task_rows;
+                const int valid_rows = min(task_rows, row_end - row0);
+                if (PREFETCH && task + 1 < n_tasks) {
+                    const int p_rows = min(task_rows, row_end - row0 - task_rows);
+                    for (int r = lane; r < p_rows; r += 32)
+                        bulk_prefetch_l2(m + (size_t)(row0 + task_rows + r) * row_bytes +
+                                             (size_t)piece * piece_chunks * 16,
+                                         (uint32_t)chunks_p * 16u);
                 }
                 for (int seg = 0; seg < n_seg; ++seg) {
                     if (round > 0 && !mbar_wait(empty_bar(s), (round & 1u) ^ 1u, status)) {
                         alive = false;
                         break;
                     }
-                    const int chunks = min(G::kSegChunks, tile_chunks - seg * G::kSegChunks);
+                    const int chunks = min(G::kSegChunks, chunks_p - seg * G::kSegChunks);
                     const uint32_t bytes = (uint32_t)chunks * 16u;
                     if (lane == 0) mbar_arrive_expect_tx(full_bar(s), bytes * (uint32_t)valid_rows);
-                    const size_t col = ((size_t)tile * G::kTileChunks + (size_t)seg * G::kSegChunks) * 16;
+                    const size_t col = ((size_t)piece * piece_chunks + (size_t)seg * G::kSegChunks) * 16;
                     for (int r = lane; r < valid_rows; r += 32)
                         bulk_load(ring_s + s * G::kStageBytes + r * G::kSegBytes,
                                   m + (size_t)(row0 + r) * row_bytes + col, bytes, full_bar(s));
@@ -253,45 +326,33 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
     int s = 0;            // ring slot of the next stage
     uint32_t phase = 0;   // its mbarrier parity
     bool alive = true;
-    uint32_t tile_parity = 0;
     const uint4* const ring_lane = reinterpret_cast<const uint4*>(ring) + (warp * RW) * G::kSegChunks + lane;
-    for (int tile = 0; tile < n_tiles && alive; ++tile) {
-        const int tile_chunks = min(G::kTileChunks, n16 - tile * G::kTileChunks);
-        const int n_seg = (tile_chunks + G::kSegChunks - 1) / G::kSegChunks;
-        const int n_full_seg = tile_chunks / G::kSegChunks;
-        // stage the vector tile: FP16 pairs, (group g, half k, lane l) is the
-        // uint4 at (g*2 + k)*32 + l and holds codes 16*(32g+l) + 8k .. +7.
-        if (tile > 0 && !mbar_sync(tile_bar, tile_parity, status)) break;  // previous tile consumed
-        {
-            const int w_begin = tile * (TILE / 4);
-            const int w_valid = tile_chunks * 4;
-            const int w_fill = n_seg * G::kSegChunks * 4;
-            uint2* vec2 = reinterpret_cast<uint2*>(vec);
-            constexpr int kBatch = 4;  // loads in flight per thread
-            for (int w0 = threadIdx.x; w0 < w_fill; w0 += kBatch * CW * 32) {
-                uint32_t raw[kBatch];
-#pragma unroll
-                for (int b = 0; b < kBatch; ++b) {
-                    const int wl = w0 + b * CW * 32;
-                    raw[b] = wl < w_valid ? __ldg(v + w_begin + wl) : 0u;  // beyond N: code 0 = +0.0
-                }
-#pragma unroll
-                for (int b = 0; b < kBatch; ++b) {
-                    const int wl = w0 + b * CW * 32;
-                    if (wl < w_fill) {
-                        uint32_t lo, hi;
-                        decode_word_h2<MODE>(raw[b], lo, hi);
-                        const int chunk = wl >> 2, k = wl & 3;
-                        vec2[(((chunk >> 5) * 2 + (k >> 1)) * 32 + (chunk & 31)) * 2 + (k & 1)] = make_uint2(lo, hi);
-                    }
-                }
-            }
+    if (!long_rows) {
+        // the whole vector, once, by all consumer warps
+        const int fill = ((n16 + G::kSegChunks - 1) / G::kSegChunks) * G::kSegChunks;
+        stage_vector<MODE, 4>(vec, v, n16, fill, threadIdx.x, CW * 32);
+        uint32_t parity = 0;
+        alive = mbar_sync(start_bar, parity, status);
+    }
+    // Partial row sums between pieces: in shared memory when the CTA's row block
+    // fits there (no global round trip in the loop), else in the output buffer.
+    const bool smem_acc = row_end - row_begin <= kShardStageRows;
+    float* const partial = FUSED ? sh.out[sh.rank] + sh.row_offset : out;
+    for (int piece = 0; piece < n_pieces && alive; ++piece) {
+        const int chunks_p = min(piece_chunks, n16 - piece * piece_chunks);
+        const int n_seg = (chunks_p + G::kSegChunks - 1) / G::kSegChunks;
+        const int n_full_seg = chunks_p / G::kSegChunks;
+        const bool last_piece = piece + 1 == n_pieces;
+        const uint4* vbase = vec;
+        if (long_rows) {
+            const int b = piece & 1;
+            vbase = vec + b * (G::kHalfChunks * 2);
+            if (!mbar_wait(vec_full(b), (uint32_t)(piece >> 1) & 1u, status)) break;
         }
-        if (!mbar_sync(tile_bar, tile_parity, status)) break;
-
         for (int task = 0; task < n_tasks && alive; ++task) {
-            const int row0 = row_begin + task * G::kTaskRows + warp * RW;
-            const bool all_rows = row0 + RW <= row_end;  // warp-uniform
+            const int task_end = min(row_end, row_begin + (task + 1) * task_rows);
+            const int row0 = row_begin + task * task_rows + warp * RW;
+            const bool all_rows = row0 + RW <= task_end;  // warp-uniform
             float acc[RW][4];
 #pragma unroll
             for (int r = 0; r < RW; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
@@ -302,7 +363,7 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
                     break;
                 }
                 const uint4* st = ring_lane + s * (G::kStageBytes / 16);
-                const uint4* vs = vec + (seg * CL * 2) * 32 + lane;
+                const uint4* vs = vbase + (seg * CL * 2) * 32 + lane;
                 if (all_rows && seg < n_full_seg) {
                     // whole segment, all rows: no predicates, fully unrolled
 #pragma unroll
@@ -313,14 +374,14 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
                             fma_chunk<MODE>(st[r * G::kSegChunks + c * 32], va, vb, acc[r]);
                     }
                 } else {
-                    const int chunks = min(G::kSegChunks, tile_chunks - seg * G::kSegChunks);
+                    const int chunks = min(G::kSegChunks, chunks_p - seg * G::kSegChunks);
 #pragma unroll 1
                     for (int c = 0; c < CL; ++c) {
                         if (c * 32 + lane < chunks) {
                             const uint4 va = vs[(c * 2) * 32], vb = vs[(c * 2 + 1) * 32];
 #pragma unroll
                             for (int r = 0; r < RW; ++r)
-                                if (row0 + r < row_end)
+                                if (row0 + r < task_end)
                                     fma_chunk<MODE>(st[r * G::kSegChunks + c * 32], va, vb, acc[r]);
                         }
                     }
@@ -330,35 +391,36 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
                 if (++s == STAGES) { s = 0; phase ^= 1u; }
             }
             if (!alive) break;
-            // the warp owns its rows: one butterfly, then the row's lane writes
+            // the warp owns its rows: one butterfly, then the row's lane adds the
+            // earlier pieces' partial sum and writes
             float sums[RW];
 #pragma unroll
             for (int r = 0; r < RW; ++r) sums[r] = (acc[r][0] + acc[r][1]) + (acc[r][2] + acc[r][3]);
             warp_reduce_rows<RW>(sums, lane);
             if ((lane & (32 / RW - 1)) == 0) {
                 const int row = row0 + lane / (32 / RW);
-                if (row < row_end) {
-                    if (!FUSED) {
-                        if (tile == 0) out[row] = sums[0];
-                        else out[row] += sums[0];  // the same lane owns the row in every tile
+                if (row < task_end) {
+                    float total = sums[0];
+                    if (piece > 0) total += smem_acc ? staged_rows[row - row_begin] : partial[row];
+                    if (!last_piece) {
+                        if (smem_acc) staged_rows[row - row_begin] = total;
+                        else partial[row] = total;  // the same lane owns the row in every piece
+                    } else if (!FUSED) {
+                        out[row] = total;
                     } else if (sh.staged) {
-                        // the CTA's rows are collected in shared memory (partial sums of
-                        // earlier column tiles too) and pushed once, coalesced, at the end
-                        const int i = row - row_begin;
-                        staged_rows[i] = tile == 0 ? sums[0] : staged_rows[i] + sums[0];
+                        // the CTA's rows are pushed once, coalesced, when the CTA is done
+                        staged_rows[row - row_begin] = total;
                     } else {
-                        // partial sums of earlier column tiles sit in this rank's own buffer
-                        float* mine = sh.out[sh.rank] + sh.row_offset;
-                        const float total = tile == 0 ? sums[0] : mine[row] + sums[0];
-                        if (tile + 1 < n_tiles) {
-                            mine[row] = total;
-                        } else {
-                            for (int p = 0; p < sh.world; ++p) sh.out[p][sh.row_offset + row] = total;
-                            __threadfence_system();  // before this warp reports itself finished
-                        }
+                        for (int p = 0; p < sh.world; ++p) sh.out[p][sh.row_offset + row] = total;
+                        __threadfence_system();  // before this warp reports itself finished
                     }
                 }
             }
+        }
+        if (!alive) break;
+        if (long_rows) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(vec_empty(piece & 1));  // this warp is done with the piece
         }
     }
     if (FUSED) {
