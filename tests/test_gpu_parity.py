@@ -192,7 +192,9 @@ def test_gemv_raw_bits_nonfinite_classes(fb, golden, mode):
 
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("shape", [(1, 4), (3, 8), (17, 20), (5, 4100), (1, 16384), (2, 16),
-                                   (300, 2048), (1031, 4096), (40, 16400), (9, 32784), (64, 65536)])
+                                   (300, 2048), (1031, 4096), (40, 16400), (9, 32784), (64, 65536),
+                                   (7, 2080), (295, 1056), (297, 528), (3000, 5632), (600, 32768),
+                                   (4097, 1040), (20000, 48), (513, 8208)])
 def test_gemv_edge_shapes_vs_oracle(fb, c_oracle, mode, shape):
     rng = np.random.default_rng(shape[0] * 131 + shape[1])
     A = rng.standard_normal(shape).astype(np.float16)
