@@ -354,6 +354,11 @@ def run_ours(args) -> None:
             extra["tinyllama_gemv_chain_tensor_parallel"] = chain.measure_tp(tokens=20)
         except Exception as e:  # noqa: BLE001 - must not sink the headline
             extra["tinyllama_gemv_chain_tensor_parallel"] = {"error": repr(e)}
+        try:  # the same with the all-reduce inside the column-sharded GEMV kernels
+            extra["tinyllama_gemv_chain_tensor_parallel_fused_allreduce"] = chain.measure_tp(
+                tokens=20, fused_allreduce=True)
+        except Exception as e:  # noqa: BLE001
+            extra["tinyllama_gemv_chain_tensor_parallel_fused_allreduce"] = {"error": repr(e)}
         kern_name = "gemv_ring_kernel<E5M2> (per-rank block)"
     achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": kern_name, "achieved": round(achieved, 1),

@@ -26,6 +26,8 @@ SYMBOLS = {
     "feather_gemv_fp8_sharded": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp, _vp, _i32, _i32,
                                         ctypes.c_uint32, _vp]),
     "feather_gemv_fp8_sharded_supported": (_i32, [_i64, _i64]),
+    "feather_gemv_fp8_allreduce": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _i64, _vp, _i32, _i32,
+                                          _vp]),
     "feather_enable_peer_access": (_i32, [_i32]),
     "feather_ipc_export": (_i32, [_vp, _vp, ctypes.POINTER(_i64)]),
     "feather_ipc_open": (_i32, [_vp, _i64, ctypes.POINTER(_vp)]),

@@ -81,21 +81,26 @@ class TensorParallelChain:
     * o and down are split by INPUT columns: rank r holds columns
       ``[r*N/W, (r+1)*N/W)`` of every row and the matching slice of the packed
       activation; each rank produces a full-length partial sum and the partials
-      are added with an NCCL all-reduce (2048 floats, 2 per layer).
+      are added either inside the GEMV kernel through peer-mapped inboxes
+      (``fused_allreduce=True``, sharded.ColumnShardedGemv) or with an NCCL
+      all-reduce after it (2048 floats, 2 per layer).
 
     Weights are generated from the same seed, in the same order, as GemvChain's,
     so the two can be compared.
     """
 
     def __init__(self, mode: str = "E4M3", seed: int = 6, group=None, layers: int = LAYERS,
-                 static_matrix: bool = True):
+                 static_matrix: bool = True, fused_allreduce: bool = False):
         import torch.distributed as dist
+        from .sharded import ColumnShardedGemv, PeerAllReduce
         self.dist, self.group = dist, group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         W, r = self.world, self.rank
         device = torch.device("cuda", torch.cuda.current_device())
         gen = torch.Generator(device=device).manual_seed(seed)
         self.mode, self.static_matrix = mode, static_matrix
+        self.fused_allreduce = bool(fused_allreduce) and self.world > 1
+        self.ctx = PeerAllReduce(HIDDEN, device, group) if self.fused_allreduce else None
         self.ops = []  # (kind, packed weight shard, packed activation (slice), (rows, cols), out)
         acts = {}
         for n in (HIDDEN, INTER):
@@ -110,8 +115,13 @@ class TensorParallelChain:
                 cols = n // W
                 shard = w[:, r * cols:(r + 1) * cols].contiguous()
                 act = acts[n][r * cols // 4:(r + 1) * cols // 4]
-                self.ops.append(("cols", fb.pack_fp8_tensor(shard, mode), act, (m, cols),
-                                 torch.empty(m, dtype=torch.float32, device=device)))
+                packed = fb.pack_fp8_tensor(shard, mode)
+                out = torch.empty(m, dtype=torch.float32, device=device)
+                if self.fused_allreduce:
+                    self.ops.append(("fused", ColumnShardedGemv(packed, (m, cols), mode, self.ctx, out=out),
+                                     act, (m, cols), out))
+                else:
+                    self.ops.append(("cols", packed, act, (m, cols), out))
             else:  # output split
                 if m % W:
                     raise ValueError(f"{name}: {m} rows do not split over {W} ranks")
@@ -127,15 +137,23 @@ class TensorParallelChain:
 
     def token(self) -> None:
         for kind, w, a, shape, out in self.ops:
+            if kind == "fused":
+                w(a)
+                continue
             fb.gemv_fp8_acc_fp32_gpu(w, a, shape, self.mode, out=out, static_matrix=self.static_matrix)
             if kind == "cols" and self.world > 1:
                 self.dist.all_reduce(out, group=self.group)
 
+    def close(self) -> None:
+        if self.ctx is not None:
+            self.ctx.close()
 
-def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", group=None) -> dict:
+
+def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", group=None,
+               fused_allreduce: bool = False) -> dict:
     """Tokens per second of the tensor-parallel chain (call on every rank)."""
     import torch.distributed as dist
-    chain = TensorParallelChain(mode, group=group)
+    chain = TensorParallelChain(mode, group=group, fused_allreduce=fused_allreduce)
     for _ in range(3):
         chain.token()
     torch.cuda.synchronize()
@@ -164,9 +182,11 @@ def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", gro
     t = torch.tensor([start.elapsed_time(end) / tokens], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     ms = float(t.item())
+    chain.close()
     return {"tokens_per_s": round(1e3 / ms, 1), "us_per_token": round(ms * 1e3, 1),
             "gemvs_per_token_per_rank": len(chain.ops),
-            "all_reduces_per_token": sum(1 for o in chain.ops if o[0] == "cols"),
+            "all_reduces_per_token": sum(1 for o in chain.ops if o[0] in ("cols", "fused")),
+            "fused_allreduce": chain.fused_allreduce,
             "world": chain.world, "cuda_graph": graphed, "mode": mode}
 
 

@@ -262,7 +262,7 @@ static bool ring_eligible(const void* m, long long M, long long N, const DeviceI
 template <int MODE, int RW, int U, bool EARLY>
 static int gemv_rows_launch(const uint32_t* m, const uint32_t* v, float* out, long long M,
                             long long N, cudaStream_t s) {
-    auto kernel = gemv_rows_kernel<MODE, RW, U, EARLY>;
+    auto kernel = gemv_rows_kernel<MODE, RW, U, EARLY, false>;
     static std::atomic<unsigned long long> configured{0};
     if (int st = ensure_smem(kernel, gemv_rows_smem_bytes(kRowsTileCodes), configured)) return st;
     const long long rows_per_cta = (kRowsThreads / 32) * RW;
@@ -277,7 +277,42 @@ static int gemv_rows_launch(const uint32_t* m, const uint32_t* v, float* out, lo
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const uint4*>(m), v, out,
-                                             (int)M, (int)(N / 16));
+                                             (int)M, (int)(N / 16), NoAllReduce{},
+                                             static_cast<unsigned int*>(nullptr));
+    return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
+}
+
+// Column-sharded GEMV with the all-reduce in the kernel's epilogue.  Its CTAs
+// wait for the peers' CTAs of the same index, so the whole grid must be resident
+// at once: FEATHER_ERR_TOO_LARGE when it is not.
+template <int MODE, int RW, int U>
+static int gemv_allreduce_launch(const uint32_t* m, const uint32_t* v, long long M, long long N,
+                                 const AllReduceArgs& ar, const DeviceInfo& dev, cudaStream_t s) {
+    auto kernel = gemv_rows_kernel<MODE, RW, U, true, true>;
+    static std::atomic<unsigned long long> configured{0};
+    if (int st = ensure_smem(kernel, gemv_rows_smem_bytes(kRowsTileCodes), configured)) return st;
+    unsigned int* status = nullptr;
+    if (int st = status_word(&status)) return st;
+    const long long rows_per_cta = (kRowsThreads / 32) * RW;
+    const long long grid = (M + rows_per_cta - 1) / rows_per_cta;
+    const int smem = gemv_rows_smem_bytes((int)(N > kRowsTileCodes ? kRowsTileCodes : N));
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kRowsThreads, smem) != cudaSuccess)
+        return FEATHER_ERR_LAUNCH;
+    if (grid > (long long)per_sm * dev.sm_count) return FEATHER_ERR_TOO_LARGE;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kRowsThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const uint4*>(m), v,
+                                             static_cast<float*>(nullptr), (int)M, (int)(N / 16), ar,
+                                             status);
     return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
 }
 
@@ -591,6 +626,49 @@ int feather_gemv_fp8_sharded(const uint32_t* m_local, const uint32_t* v, int64_t
     return mode == FEATHER_MODE_E5M2
                ? gemv_ring_launch<kE5M2, true>(m_local, v, mine, rows_local, N, *dev, s, sh)
                : gemv_ring_launch<kE4M3, true>(m_local, v, mine, rows_local, N, *dev, s, sh);
+}
+
+int feather_gemv_fp8_allreduce(const uint32_t* m_local, const uint32_t* v_local, float* result,
+                               int64_t M, int64_t N_local, int mode, float* const* peer_inbox,
+                               int64_t inbox_floats, uint32_t* const* peer_flags, int rank,
+                               int world, void* stream) {
+    if (M <= 0 || N_local <= 0 || (N_local & 15) || M > 0x7FFFFFFF || N_local > 0x7FFFFFFF ||
+        !peer_inbox || !peer_flags || world < 1 || world > kMaxShardRanks || rank < 0 ||
+        rank >= world || !m_local || !v_local || !result)
+        return FEATHER_ERR_BAD_ARG;
+    if (mode != FEATHER_MODE_E5M2 && mode != FEATHER_MODE_E4M3) return FEATHER_ERR_MODE;
+    const int64_t half = (inbox_floats / 2) & ~(int64_t)3;      // floats, 16-byte granular
+    const int64_t slot = 2 * ((M + 15) / 16 * 16);              // (sum, tag) pairs of one rank
+    if (half < (int64_t)world * slot) return FEATHER_ERR_TOO_LARGE;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    if (!aligned(m_local, 16) || !aligned(v_local, 4) || !aligned(result, 4))
+        return FEATHER_ERR_MISALIGNED;
+    AllReduceArgs ar = {};
+    for (int p = 0; p < world; ++p) {
+        if (!peer_inbox[p] || !peer_flags[p]) return FEATHER_ERR_BAD_ARG;
+        if (!aligned(peer_inbox[p], 16) || !aligned(peer_flags[p], 4)) return FEATHER_ERR_MISALIGNED;
+        ar.inbox[p] = peer_inbox[p];
+        ar.flags[p] = peer_flags[p];
+    }
+    ar.result = result;
+    ar.half = half;
+    ar.rank = rank;
+    ar.world = world;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // one row per warp while that keeps the grid resident, else two
+    const bool one = M < 2ll * dev->sm_count * 16;
+    int st = FEATHER_ERR_TOO_LARGE;
+    if (mode == FEATHER_MODE_E5M2) {
+        if (one) st = gemv_allreduce_launch<kE5M2, 1, 4>(m_local, v_local, M, N_local, ar, *dev, s);
+        if (st == FEATHER_ERR_TOO_LARGE)
+            st = gemv_allreduce_launch<kE5M2, 2, 4>(m_local, v_local, M, N_local, ar, *dev, s);
+    } else {
+        if (one) st = gemv_allreduce_launch<kE4M3, 1, 4>(m_local, v_local, M, N_local, ar, *dev, s);
+        if (st == FEATHER_ERR_TOO_LARGE)
+            st = gemv_allreduce_launch<kE4M3, 2, 4>(m_local, v_local, M, N_local, ar, *dev, s);
+    }
+    return st;
 }
 
 int feather_set_wait_limit_ms(int milliseconds) {

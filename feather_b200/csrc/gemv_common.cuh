@@ -79,4 +79,59 @@ __device__ __forceinline__ void warp_reduce_rows(float (&v)[RW], int lane) {
     for (; o > 0; o >>= 1) v[0] += __shfl_xor_sync(0xFFFFFFFFu, v[0], o);
 }
 
+// How long a bounded wait may go without progress before it gives up: 2 s
+// unless the host changed it (feather_set_wait_limit_ms).  One copy per kernel
+// image that includes this header; the library has one.
+__device__ unsigned long long g_wait_limit_ns = 2000000000ull;
+#define kWaitLimitNs g_wait_limit_ns
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// System-scope relaxed accesses for the epoch flags.  Ordering comes from ONE
+// system-scope fence before the flag stores (release pattern) and one after the
+// flag loads (acquire pattern): a release store per peer would pay a full
+// system fence per peer, which at eight ranks cost more than the whole exchange.
+__device__ __forceinline__ void st_relaxed_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_relaxed_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// 16-byte accesses that are neither cached in L1 nor reordered by the
+// compiler, for (value, tag) pairs that a peer GPU writes and this GPU polls.
+// An aligned 8-byte half of such a store arrives whole, so a pair whose tag
+// matches carries its value.
+__device__ __forceinline__ void st_volatile_v4(float* p, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};"
+                 :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const float* p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// Column-sharded GEMV with the all-reduce fused behind it (gemv_rows_kernel,
+// ALLREDUCE = true): where every rank's inbox and flag block live, as mapped
+// into this process.  An inbox is two halves used by alternate calls; a half
+// holds one slot per rank, a slot one (sum, call number) pair per row, M rounded
+// up to a multiple of 16 rows.
+constexpr int kMaxArRanks = 16;
+constexpr int kArTicketWord = 16;  // flag-block word: CTAs of the running call that have finished
+constexpr int kArEpochWord = 17;   // flag-block word: number of all-reduce calls completed so far
+struct AllReduceArgs {
+    float* inbox[kMaxArRanks];           // rank p's inbox
+    unsigned int* flags[kMaxArRanks];    // rank p's flag block (only this rank's own is used)
+    float* result;                       // this rank's reduced output, M floats
+    long long half;                      // floats per half of an inbox
+    int rank, world;
+};
+
 }  // namespace feather

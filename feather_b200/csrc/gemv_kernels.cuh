@@ -20,6 +20,7 @@
 // gemv_general_kernel: any N % 4 == 0, 4-byte aligned; one warp per row, word
 //   loads.  Used for ragged shapes.
 #pragma once
+#include <type_traits>
 #include "gemv_common.cuh"
 
 namespace feather {
@@ -35,10 +36,25 @@ constexpr int gemv_rows_smem_bytes(int n_codes) {
 // the number of row groups works and each CTA walks groups blockIdx.x,
 // blockIdx.x + gridDim.x, ... with the vector staged once; otherwise the grid
 // must equal the number of row groups (one group per CTA, tiles inside).
-template <int MODE, int RW, int U, bool EARLY>
+//
+// ALLREDUCE: the column-sharded GEMV of a tensor-parallel layer.  Every rank
+// holds a column slice of all M rows and the matching slice of the vector; its
+// row sums are partial and the result is the sum over the ranks.  Each CTA
+// exchanges ITS rows with the same CTA of every peer, through peer-mapped
+// inboxes: a row sum travels as an 8-byte (value, call number) pair, two per
+// 16-byte store, so the receiver polls the data itself -- no fence, no separate
+// flag, one NVLink crossing.  The CTA then adds the ranks' sums in rank order
+// and writes `ar.result`: the same bits on every rank, no collective launch.
+// The call counter lives in device memory (flag word kArEpochWord), so a
+// captured CUDA graph can be replayed.  `out` is ignored.  The grid must be one
+// CTA per row group and fit the GPU at once (CTAs wait for their peers).
+struct NoAllReduce {};
+template <int MODE, int RW, int U, bool EARLY, bool ALLREDUCE = false>
 __global__ void __launch_bounds__(kRowsThreads)
 gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
-                 float* __restrict__ out, int M, int n16) {
+                 float* __restrict__ out, int M, int n16,
+                 const __grid_constant__ std::conditional_t<ALLREDUCE, AllReduceArgs, NoAllReduce> ar,
+                 unsigned int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char rows_smem[];
     uint4* vec = reinterpret_cast<uint4*>(rows_smem);
     constexpr int kWarps = kRowsThreads / 32;
@@ -69,6 +85,13 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
     if (EARLY) issue(rows, active, 0);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (!EARLY) issue(rows, active, 0);
+    __shared__ float ar_part[ALLREDUCE ? kGroupRows : 1];
+    unsigned int epoch = 0;
+    if constexpr (ALLREDUCE) {
+        // this call's number: one more than the calls completed on this rank
+        epoch = __ldcg(ar.flags[ar.rank] + kArEpochWord) + 1u;
+        if (epoch == 0u) epoch = 2u;  // 0 is the tag of an untouched inbox; keep the parity
+    }
 
     float acc[RW][4];
 #pragma unroll
@@ -81,8 +104,11 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
             warp_reduce_rows<RW>(sums, lane);
             if ((lane & (32 / RW - 1)) == 0) {
                 const int row = row0 + lane / (32 / RW);
-                if (row < M) out[row] = sums[0];
+                if constexpr (ALLREDUCE) ar_part[warp * RW + lane / (32 / RW)] = sums[0];
+                else if (row < M) out[row] = sums[0];
             }
+        } else if constexpr (ALLREDUCE) {
+            if (lane < RW) ar_part[warp * RW + lane] = 0.f;
         }
 #pragma unroll
         for (int r = 0; r < RW; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
@@ -143,8 +169,7 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
 #pragma unroll
             for (int r = 0; r < RW; ++r) rows[r] = next_rows[r];
         }
-        return;
-    }
+    } else {
     // long rows: one row group per CTA, the vector in tiles
     for (int t0 = 0; t0 < n16; t0 += kTileChunks) {
         const int tile_chunks = min(kTileChunks, n16 - t0);
@@ -163,6 +188,61 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
         }
     }
     finish_rows();
+    }
+    if constexpr (ALLREDUCE) {
+        // ---- exchange this CTA's rows with the peers' same CTA and add ----
+        constexpr int kPieces = kGroupRows / 2;            // 16-byte pieces: two (sum, tag) pairs
+        __shared__ float ar_recv[kMaxArRanks][kGroupRows];
+        const int cta_row0 = (int)blockIdx.x * kGroupRows;
+        const size_t slot = 2 * (((size_t)M + 15) / 16 * 16);  // floats per rank slot
+        const size_t half0 = (size_t)(epoch & 1u) * ar.half;   // this call's half of an inbox
+        __syncthreads();                                    // ar_part is complete
+        for (int t = threadIdx.x; t < ar.world * kPieces; t += kRowsThreads) {
+            const int q = t / kPieces, j = t - q * kPieces;
+            const float s0 = ar_part[2 * j], s1 = ar_part[2 * j + 1];
+            if (q == ar.rank) {
+                ar_recv[q][2 * j] = s0;
+                ar_recv[q][2 * j + 1] = s1;
+                continue;
+            }
+            // my sums into rank q's inbox, slot `rank` ...
+            st_volatile_v4(ar.inbox[q] + half0 + (size_t)ar.rank * slot + 2 * (size_t)(cta_row0 + 2 * j),
+                           make_uint4(__float_as_uint(s0), epoch, __float_as_uint(s1), epoch));
+        }
+        for (int t = threadIdx.x; t < ar.world * kPieces; t += kRowsThreads) {
+            const int q = t / kPieces, j = t - q * kPieces;
+            if (q == ar.rank) continue;
+            // ... and rank q's sums out of my inbox, slot q, once both tags say "this call"
+            const float* src = ar.inbox[ar.rank] + half0 + (size_t)q * slot + 2 * (size_t)(cta_row0 + 2 * j);
+            uint4 x = ld_volatile_v4(src);
+            if (x.y != epoch || x.w != epoch) {
+                const unsigned long long t0 = global_timer_ns();
+                do {
+                    x = ld_volatile_v4(src);
+                    if (global_timer_ns() - t0 > kWaitLimitNs) {
+                        atomicOr(status, 2u);  // rank q's sums did not arrive in time
+                        break;
+                    }
+                } while (x.y != epoch || x.w != epoch);
+            }
+            ar_recv[q][2 * j] = __uint_as_float(x.x);
+            ar_recv[q][2 * j + 1] = __uint_as_float(x.z);
+        }
+        __syncthreads();
+        if (threadIdx.x < kGroupRows && cta_row0 + (int)threadIdx.x < M) {
+            float t = ar_recv[0][threadIdx.x];  // rank 0's sum, then the others in rank order
+            for (int q = 1; q < ar.world; ++q) t += ar_recv[q][threadIdx.x];
+            ar.result[cta_row0 + threadIdx.x] = t;
+        }
+        // the CTA that finishes last records the call as completed
+        if (threadIdx.x == 0) {
+            unsigned int* my_flags = ar.flags[ar.rank];
+            if (atomicAdd(my_flags + kArTicketWord, 1u) == gridDim.x - 1) {
+                my_flags[kArTicketWord] = 0u;
+                my_flags[kArEpochWord] = epoch;
+            }
+        }
+    }
 }
 
 // One warp per row, 4-byte loads: every N % 4 == 0, any 4-byte alignment.

@@ -38,12 +38,6 @@
 
 namespace feather {
 
-// How long a bounded wait may go without progress before it gives up: 2 s
-// unless the host changed it (feather_set_wait_limit_ms).  One copy per kernel
-// image that includes this header; the library has one.
-__device__ unsigned long long g_wait_limit_ns = 2000000000ull;
-#define kWaitLimitNs g_wait_limit_ns
-
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -63,11 +57,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
-}
-__device__ __forceinline__ unsigned long long global_timer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
 }
 // Bounded wait.  Returns false (and raises *status) if the phase did not
 // complete within kWaitLimitNs.
@@ -116,19 +105,6 @@ struct ShardArgs {
                                          //    to the peers as ONE coalesced block when it is done;
                                          // 0: each row is stored to the peers as it finishes
 };
-// System-scope relaxed accesses for the epoch flags.  Ordering comes from ONE
-// system-scope fence before the flag stores (release pattern) and one after the
-// flag loads (acquire pattern): a release store per peer would pay a full
-// system fence per peer, which at eight ranks cost more than the whole exchange.
-__device__ __forceinline__ void st_relaxed_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_relaxed_sys(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-
 template <int CW, int RW, int CL, int STAGES, int TILE>
 struct RingGeometry {
     static constexpr int kTaskRows = CW * RW;          // rows per task (= per stage)

@@ -30,7 +30,7 @@ from typing import Callable, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["row_block", "local_words", "RowShardedGemv"]
+__all__ = ["row_block", "local_words", "RowShardedGemv", "PeerAllReduce", "ColumnShardedGemv"]
 
 
 def row_block(M: int, world_size: int, rank: int) -> Tuple[int, int]:
@@ -51,6 +51,54 @@ def local_words(m_packed: torch.Tensor, m_shape, world_size: int, rank: int) -> 
         raise ValueError("N must be a multiple of 4")
     begin, end = row_block(M, world_size, rank)
     return m_packed.reshape(-1)[begin * (N // 4): end * (N // 4)]
+
+
+def _share_with_peers(shared: Optional[torch.Tensor], dev: torch.device, group, error=None):
+    """Map every rank's ``shared`` buffer into this process (CUDA IPC).
+
+    Collective over ``group``: every rank calls it, also a rank that already
+    failed (``shared=None`` and its ``error``), so that nobody waits for a rank
+    that gave up.  Returns ``(base, mapped, error)``: ``base[p]`` is the address
+    of rank p's buffer here, ``mapped`` the (pointer, offset) pairs to hand to
+    ``feather_ipc_close``; on failure ``error`` is the exception.
+    """
+    from . import _lib
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    payload = None
+    if error is None:
+        try:
+            lib = _lib.load()
+            with torch.cuda.device(dev):
+                torch.cuda.synchronize(dev)
+                handle = ctypes.create_string_buffer(64)
+                offset = ctypes.c_int64(0)
+                _lib.check(lib.feather_ipc_export(shared.data_ptr(), handle, ctypes.byref(offset)))
+            payload = (handle.raw, int(offset.value), dev.index)
+        except Exception as e:  # noqa: BLE001 - reported to the caller
+            error = e
+    gathered: List = [None] * world
+    dist.all_gather_object(gathered, payload, group=group)
+    if error is not None:
+        return [], [], error
+    base, mapped = [], []
+    try:
+        if any(g is None for g in gathered):
+            raise RuntimeError("a peer rank could not share its buffer")
+        with torch.cuda.device(dev):  # map with the device that runs the kernel current
+            for r, (raw, off, peer_dev) in enumerate(gathered):
+                if r == rank:
+                    base.append(shared.data_ptr())
+                    continue
+                if not torch.cuda.can_device_access_peer(dev.index, peer_dev):
+                    raise RuntimeError(f"GPU {dev.index} cannot access GPU {peer_dev} directly")
+                _lib.check(lib.feather_enable_peer_access(peer_dev))
+                ptr = ctypes.c_void_p(0)
+                _lib.check(lib.feather_ipc_open(raw, off, ctypes.byref(ptr)))
+                mapped.append((ptr.value, off))
+                base.append(ptr.value)
+    except Exception as e:  # noqa: BLE001
+        return base, mapped, e
+    return base, mapped, None
 
 
 class RowShardedGemv:
@@ -121,7 +169,7 @@ class RowShardedGemv:
         from . import _lib
         from .packers.fp8 import as_words
         dev = self.m_local.device
-        error, payload = None, None
+        error = None
         try:
             lib = _lib.load()
             if self.world_size > 16:
@@ -132,33 +180,14 @@ class RowShardedGemv:
                     raise ValueError(f"{self.rows}x{self.N} per rank is outside the fused kernel's range")
                 # [two output buffers | flag block]: one allocation per rank, exported by CUDA IPC
                 self._shared = torch.zeros(2 * self.M + 32, dtype=torch.float32, device=dev)
-                torch.cuda.synchronize(dev)
-                handle = ctypes.create_string_buffer(64)
-                offset = ctypes.c_int64(0)
-                _lib.check(lib.feather_ipc_export(self._shared.data_ptr(), handle, ctypes.byref(offset)))
-            payload = (handle.raw, int(offset.value), dev.index)
         except Exception as e:  # noqa: BLE001 - reported through the agreement step
             error = e
-        gathered: List = [None] * self.world_size
-        dist.all_gather_object(gathered, payload, group=self.group)
+        base, self._mapped, error = _share_with_peers(
+            None if error else self._shared, dev, self.group, error)
         if error is not None:
             return error
         try:
-            if any(g is None for g in gathered):
-                raise RuntimeError("a peer rank could not share its buffer")
-            base, self._mapped = [], []
-            with torch.cuda.device(dev):  # map with the device that runs the kernel current
-                for r, (raw, off, peer_dev) in enumerate(gathered):
-                    if r == self.rank:
-                        base.append(self._shared.data_ptr())
-                        continue
-                    if not torch.cuda.can_device_access_peer(dev.index, peer_dev):
-                        raise RuntimeError(f"GPU {dev.index} cannot access GPU {peer_dev} directly")
-                    _lib.check(lib.feather_enable_peer_access(peer_dev))
-                    mapped = ctypes.c_void_p(0)
-                    _lib.check(lib.feather_ipc_open(raw, off, ctypes.byref(mapped)))
-                    self._mapped.append((mapped.value, off))
-                    base.append(mapped.value)
+            lib = _lib.load()
             arr = ctypes.c_void_p * self.world_size
             self._out_ptrs = [arr(*[b + 4 * self.M * k for b in base]) for k in (0, 1)]
             self._flag_ptrs = arr(*[b + 4 * 2 * self.M for b in base])
@@ -235,4 +264,111 @@ class RowShardedGemv:
         if self.world_size > 1:
             # in place: rank r's slice already sits at offset r * rows
             dist.all_gather_into_tensor(self.out, mine, group=self.group)
+        return self.out
+
+
+class PeerAllReduce:
+    """Inbox and flag block for the all-reduce fused into column-sharded GEMVs.
+
+    One object serves any number of ``ColumnShardedGemv`` operators, provided
+    every rank calls them in the same order (the call counter lives in the flag
+    block on the device, so a captured CUDA graph of calls can be replayed).
+    ``max_rows`` is the largest M of those operators.  Collective: create it on
+    every rank of ``group``; ``close()`` likewise.
+    """
+
+    def __init__(self, max_rows: int, device: Optional[torch.device] = None, group=None):
+        from . import _lib
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        self.group = group
+        self.world_size, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.device, self.max_rows = dev, int(max_rows)
+        error = None
+        try:
+            if self.world_size > 16:
+                raise ValueError("the fused all-reduce supports at most 16 ranks")
+            # two halves x world slots x (sum, tag) pairs for max_rows rounded up to 16
+            self.inbox_floats = 2 * self.world_size * 2 * ((self.max_rows + 15) // 16 * 16)
+            # [inbox | flag block]
+            self._shared = torch.zeros(self.inbox_floats + 32, dtype=torch.float32, device=dev)
+        except Exception as e:  # noqa: BLE001 - every rank still takes part in the exchange below
+            error = e
+        base, self._mapped, error = _share_with_peers(None if error else self._shared, dev, group, error)
+        ok = torch.tensor([int(error is None)], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if not int(ok.item()):
+            self.close(collective=False)
+            raise RuntimeError(f"fused all-reduce not available: {error or 'a peer rank failed'}")
+        arr = ctypes.c_void_p * self.world_size
+        self.inbox_ptrs = arr(*base)
+        self.flag_ptrs = arr(*[b + 4 * self.inbox_floats for b in base])
+        self._lib = _lib.load()
+
+    def close(self, collective: bool = True) -> None:
+        """Unmap the peers' buffers.  Call on every rank after the last result
+        has been consumed and before the process group goes away."""
+        if getattr(self, "_mapped", None):
+            torch.cuda.synchronize(self.device)
+            if collective:
+                dist.barrier(group=self.group)  # nobody still writes into a buffer being unmapped
+            with torch.cuda.device(self.device):
+                for ptr, off in self._mapped:
+                    self._lib.feather_ipc_close(ptr, off)
+        self._mapped = []
+
+
+class ColumnShardedGemv:
+    """``y = A @ v`` with A's COLUMNS split over the ranks: rank r holds columns
+    ``[r*N/W, (r+1)*N/W)`` of every row (packed row-major, row stride N/(4W)
+    words) and is called with the matching slice of the packed vector.  The
+    partial sums are added inside the GEMV kernel through the ranks'
+    peer-mapped inboxes (``feather_gemv_fp8_allreduce``): one launch per call,
+    no collective, the same bits on every rank.
+
+    ``m_shape`` is the LOCAL unpacked shape ``(M, N/W)``; N/W must be a
+    multiple of 16.  The result is the object's own buffer.
+    """
+
+    def __init__(self, m_local: torch.Tensor, m_shape, mode: str, ctx: PeerAllReduce,
+                 out: Optional[torch.Tensor] = None):
+        from . import _lib
+        from .packers.fp8 import as_words
+        self.M, self.n_local = int(m_shape[0]), int(m_shape[1])
+        if self.n_local % 16:
+            raise ValueError("the local column count must be a multiple of 16")
+        if self.M > ctx.max_rows:
+            raise ValueError(f"M={self.M} exceeds the all-reduce inbox ({ctx.max_rows} rows)")
+        words = as_words(m_local, "m_local")
+        if words.numel() != self.M * (self.n_local // 4):
+            raise ValueError(f"local block holds {words.numel()} words, {self.M}x{self.n_local} "
+                             f"needs {self.M * (self.n_local // 4)}")
+        if words.device != ctx.device:
+            raise ValueError("the matrix shard must live on the context's device")
+        self.m_local, self.ctx, self.mode = m_local, ctx, mode
+        self.out = torch.empty(self.M, dtype=torch.float32, device=ctx.device) if out is None else out
+        self._m_ptr, self._out_ptr = words.data_ptr(), self.out.data_ptr()
+        self._mode_id = _lib.mode_id(mode)
+        self._fn, self._check = ctx._lib.feather_gemv_fp8_allreduce, _lib.check
+        self._stream_ptr = _lib.current_stream_ptr
+        self._n_words = self.n_local // 4
+
+    def __call__(self, v_local: torch.Tensor) -> torch.Tensor:
+        ctx = self.ctx
+        with torch._C.DisableTorchFunctionSubclass():
+            if v_local.numel() < self._n_words or v_local.device != ctx.device:
+                raise ValueError("v must hold the local N/4 packed words on this rank's device")
+            v_ptr = v_local.data_ptr()
+        idx = ctx.device.index
+        if torch.cuda.current_device() != idx:
+            with torch.cuda.device(idx):
+                return self._launch(v_ptr, idx)
+        return self._launch(v_ptr, idx)
+
+    def _launch(self, v_ptr: int, idx: int) -> torch.Tensor:
+        ctx = self.ctx
+        self._check(self._fn(self._m_ptr, v_ptr, self._out_ptr, self.M, self.n_local, self._mode_id,
+                             ctx.inbox_ptrs, ctx.inbox_floats, ctx.flag_ptrs, ctx.rank,
+                             ctx.world_size, self._stream_ptr(idx)))
         return self.out

@@ -148,6 +148,46 @@ int feather_gemv_fp8_sharded(const uint32_t* m_local, const uint32_t* v, int64_t
 int feather_gemv_fp8_sharded_supported(int64_t rows_local, int64_t N);
 
 /*
+ * One rank of a COLUMN-sharded GEMV with the all-reduce of the partial results
+ * fused into the kernel.  No reference counterpart (the reference is
+ * single-GPU, feather/routines/gemv.py:136, :187); it is the split a
+ * tensor-parallel layer needs when the vector arrives sharded: rank r holds
+ * columns [r * N_local, (r + 1) * N_local) of all M rows, packed row-major with
+ * row stride N_local / 4 words, and the matching N_local / 4 words of the
+ * vector.  Each rank's row sums are partial.  Every CTA of the kernel stores
+ * its rows' sums into all peers' inboxes through peer-mapped pointers, as
+ * 8-byte (sum, call number) pairs, polls its own inbox until the peers' pairs
+ * for those rows carry this call's number (bounded, see
+ * feather_set_wait_limit_ms) and adds them in rank order:
+ * result[i] = ((p0[i] + p1[i]) + p2[i]) + ..., the same bits on every rank.
+ *   m_local     M * N_local / 4 words, 16-byte aligned; N_local % 16 == 0
+ *   v_local     N_local / 4 words
+ *   result      M floats, local
+ *   peer_inbox  HOST array of `world` device pointers: rank p's inbox of
+ *               `inbox_floats` floats, 16-byte aligned, zero before the first
+ *               call, as mapped into THIS process.  Two halves are used by
+ *               alternate calls; a half holds one slot per rank of
+ *               2 * roundup(M, 16) floats.  inbox_floats / 2 smaller than
+ *               world slots returns FEATHER_ERR_TOO_LARGE, and so does an M
+ *               whose CTAs (8 or 16 rows each) do not fit the GPU at once: the
+ *               CTAs wait for one another across ranks.
+ *   peer_flags  HOST array of `world` device pointers: rank p's flag block, 32
+ *               words, zero before the first call (only the rank's own block
+ *               is used: the call counter lives there, so there is no epoch
+ *               argument and a captured CUDA graph of calls can be replayed).
+ *               Every rank must issue the same sequence of calls on a given
+ *               inbox / flag block; M may differ from call to call,
+ *               inbox_floats may not.
+ * One call per rank must be in flight at the same time on every rank, each on
+ * its own GPU.  A rank that never arrives makes the others raise the status
+ * word after the bounded wait (see feather_device_status) instead of hanging.
+ */
+int feather_gemv_fp8_allreduce(const uint32_t* m_local, const uint32_t* v_local, float* result,
+                               int64_t M, int64_t N_local, int mode, float* const* peer_inbox,
+                               int64_t inbox_floats, uint32_t* const* peer_flags, int rank,
+                               int world, void* stream);
+
+/*
  * Let kernels on the CURRENT device load and store memory that lives on
  * `peer_device` (cudaDeviceEnablePeerAccess; already-enabled is success).  The
  * fused sharded GEMV stores into its peers' buffers, so each rank calls this

@@ -522,3 +522,98 @@ def test_sharded_wait_gives_up_and_reports_instead_of_hanging(fb):
         assert st == 0 and lib.feather_device_status(None) == 0
     finally:
         assert lib.feather_set_wait_limit_ms(2000) == 0
+
+
+# ------------------------------------------- column-sharded GEMV + all-reduce --
+def _tagged(values: torch.Tensor, tag: int) -> torch.Tensor:
+    """(value, tag) pairs as the all-reduce kernel exchanges them, viewed as floats."""
+    pairs = torch.empty(values.numel(), 2, dtype=torch.int32, device=values.device)
+    pairs[:, 0] = values.view(torch.int32)
+    pairs[:, 1] = tag
+    return pairs.reshape(-1).view(torch.float32)
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_allreduce_gemv_with_hand_fed_peer(fb, mode):
+    """feather_gemv_fp8_allreduce as rank 0 of 2, the "peer" being a second inbox
+    on the same GPU that the test fills by hand (no second process): the result
+    is own partial + peer partial, the own partial lands tagged in the peer's
+    inbox, the call counter advances on the device, halves alternate, and M may
+    change between calls."""
+    lib = fb._lib.load()
+    max_rows, world = 2048, 2
+    slot_max = 2 * max_rows
+    inbox_floats = 2 * world * slot_max
+    half = inbox_floats // 2
+    inbox = [torch.zeros(inbox_floats, dtype=torch.float32, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(32, dtype=torch.int32, device="cuda") for _ in range(world)]
+    arr = ctypes.c_void_p * world
+    inb, flg = arr(*[t.data_ptr() for t in inbox]), arr(*[t.data_ptr() for t in flags])
+    gen = torch.Generator(device="cuda").manual_seed(23)
+    assert lib.feather_device_status(None) == 0
+    for call, (M, n_local) in enumerate([(2048, 256), (2048, 704), (1000, 48), (37, 2064), (2048, 256)],
+                                        start=1):
+        A = torch.randn(M, n_local, device="cuda", generator=gen, dtype=torch.float16)
+        v = torch.randn(n_local, device="cuda", generator=gen, dtype=torch.float16)
+        mw, vw = fb.pack_fp8_tensor(A, mode), fb.pack_fp8_tensor(v, mode)
+        own = fb.gemv_fp8_acc_fp32_gpu(mw, vw, (M, n_local), mode)
+        peer = torch.randn(M, device="cuda", generator=gen, dtype=torch.float32)
+        padded = (M + 15) // 16 * 16
+        slot = 2 * padded
+        base = (call & 1) * half
+        # rank 1's sums in rank 0's inbox, slot 1, as rank 1 would have stored them
+        # (whole 16-byte pieces: the rows past M carry the tag too)
+        inbox[0][base + slot: base + 2 * slot] = _tagged(torch.nn.functional.pad(peer, (0, padded - M)), call)
+        result = torch.full((M,), float("nan"), device="cuda")
+        st = lib.feather_gemv_fp8_allreduce(mw.data_ptr(), vw.data_ptr(), result.data_ptr(), M, n_local,
+                                            fb._lib.mode_id(mode), inb, inbox_floats, flg, 0, world, None)
+        assert st == 0 and lib.feather_device_status(None) == 0
+        assert torch.equal(result, own + peer)
+        # rank 0's sums went, tagged with the call number, to rank 1's inbox, slot 0
+        assert torch.equal(inbox[1][base: base + 2 * M].view(torch.int32), _tagged(own, call).view(torch.int32))
+        f0 = flags[0].cpu()
+        assert int(f0[17]) == call and int(f0[16]) == 0
+    # too small an inbox, bad shapes
+    p = inbox[0].data_ptr()
+    assert lib.feather_gemv_fp8_allreduce(p, p, p, 2048, 256, 0, inb, inbox_floats - 8, flg, 0, world, None) == -8
+    assert lib.feather_gemv_fp8_allreduce(p, p, p, 2048, 250, 0, inb, inbox_floats, flg, 0, world, None) == -1
+    assert lib.feather_gemv_fp8_allreduce(p, p, p, 2048, 256, 0, inb, inbox_floats, flg, 2, world, None) == -1
+    big = 1 << 20   # far more CTAs than the GPU holds at once: refused, not deadlocked
+    assert lib.feather_gemv_fp8_allreduce(p, p, p, big, 16, 0, inb, 8 * big * world, flg, 0, world, None) == -8
+
+
+def test_allreduce_gemv_world_1_and_missing_peer(fb):
+    """World size 1 is a plain GEMV.  With a peer that never delivers the wait
+    gives up after the limit, the status word reports it and the context stays
+    usable (nothing faults, nothing hangs)."""
+    lib = fb._lib.load()
+    M, n_local = 2048, 512
+    gen = torch.Generator(device="cuda").manual_seed(29)
+    A = torch.randn(M, n_local, device="cuda", generator=gen, dtype=torch.float16)
+    v = torch.randn(n_local, device="cuda", generator=gen, dtype=torch.float16)
+    mw, vw = fb.pack_fp8_tensor(A, "E4M3"), fb.pack_fp8_tensor(v, "E4M3")
+    own = fb.gemv_fp8_acc_fp32_gpu(mw, vw, (M, n_local), "E4M3")
+    inbox = [torch.zeros(8 * M, dtype=torch.float32, device="cuda") for _ in range(2)]
+    flags = [torch.zeros(32, dtype=torch.int32, device="cuda") for _ in range(2)]
+    arr1, arr2 = ctypes.c_void_p * 1, ctypes.c_void_p * 2
+    result = torch.zeros(M, dtype=torch.float32, device="cuda")
+    for _ in range(3):
+        result.zero_()
+        st = lib.feather_gemv_fp8_allreduce(mw.data_ptr(), vw.data_ptr(), result.data_ptr(), M, n_local, 1,
+                                            arr1(inbox[0].data_ptr()), 4 * M, arr1(flags[0].data_ptr()),
+                                            0, 1, None)
+        assert st == 0 and lib.feather_device_status(None) == 0
+        assert torch.equal(result, own)
+    flags[0].zero_()
+    assert lib.feather_set_wait_limit_ms(100) == 0
+    try:
+        st = lib.feather_gemv_fp8_allreduce(mw.data_ptr(), vw.data_ptr(), result.data_ptr(), M, n_local, 1,
+                                            arr2(*[t.data_ptr() for t in inbox]), 8 * M,
+                                            arr2(*[t.data_ptr() for t in flags]), 0, 2, None)
+        assert st == 0
+        assert lib.feather_device_status(None) == -7
+        assert lib.feather_device_status(None) == 0
+        # call 1 uses the odd half; slot 0 = rank 0's tagged sums
+        assert torch.equal(inbox[1][4 * M: 6 * M].view(torch.int32), _tagged(own, 1).view(torch.int32))
+    finally:
+        assert lib.feather_set_wait_limit_ms(2000) == 0

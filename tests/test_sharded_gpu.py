@@ -64,11 +64,65 @@ def _worker(rank: int, world: int, port: int, q):
         for (kind, _, _, shape, out_tp), (_, _, (m, n), out_1) in zip(tp.ops, single.ops):
             ref1 = out_1 if kind == "cols" else out_1[rank * shape[0]:(rank + 1) * shape[0]]
             ok_tp &= O.normalised_error(out_tp.cpu().numpy(), ref1.cpu().numpy()) < 1e-5
-        q.put((rank, ok_bits and ok_tp and modes == ([False, True] if world > 1 else [False]), ok_err))
+        ok_ar = True
+        if world > 1:
+            ok_ar = _check_fused_allreduce(rank, world, single)
+        q.put((rank, ok_bits and ok_tp and ok_ar and modes == ([False, True] if world > 1 else [False]),
+               ok_err))
     except Exception as e:
         q.put((rank, "failed", repr(e)))
     finally:
         dist.destroy_process_group()
+
+
+def _check_fused_allreduce(rank: int, world: int, single) -> bool:
+    """Column-sharded GEMVs with the all-reduce inside the kernel: equal to the
+    partial sums added in rank order, the same bits on every rank, close to the
+    single-GPU chain, over several calls (both inbox halves) and under CUDA
+    graph replay (the call counter lives on the device)."""
+    import feather_b200 as fb
+    from feather_b200 import chain
+    from oracle import feather_oracle as O
+    tp = chain.TensorParallelChain(layers=1, fused_allreduce=True)
+    ok = tp.fused_allreduce
+    fused = [(op, a, shape, out) for kind, op, a, shape, out in tp.ops if kind == "fused"]
+    refs = [single.ops[i][3] for i, (name, _, _) in enumerate(chain.LAYER_SHAPES) if name in ("o", "down")]
+    ok &= len(fused) == len(refs) == 2
+    expected = []
+    for op, a, shape, out in fused:
+        part = fb.gemv_fp8_acc_fp32_gpu(op.m_local, a, shape, tp.mode)
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        total = parts[0].clone()
+        for p in parts[1:]:
+            total += p
+        expected.append(total)
+
+    def verify() -> bool:
+        torch.cuda.synchronize()
+        good = True
+        for (op, a, shape, out), want, ref1 in zip(fused, expected, refs):
+            good &= bool(torch.equal(out, want))
+            good &= O.normalised_error(out.cpu().numpy(), ref1.cpu().numpy()) < 1e-5
+            out.zero_()
+        return good
+
+    for _ in range(3):  # odd number of calls per op in total: both inbox halves, shifting parity
+        tp.token()
+        ok &= verify()
+    stream, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        tp.token()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            tp.token()
+    ok &= verify()  # capture does not run the kernels; the warm-up call above did
+    for _ in range(3):
+        graph.replay()
+        ok &= verify()
+    fb.device_status()
+    tp.close()
+    return bool(ok)
 
 
 def _run(world: int):
