@@ -357,6 +357,8 @@ def run_ours(args) -> None:
         try:  # the same with the all-reduce inside the column-sharded GEMV kernels
             extra["tinyllama_gemv_chain_tensor_parallel_fused_allreduce"] = chain.measure_tp(
                 tokens=20, fused_allreduce=True)
+            extra["tinyllama_gemv_chain_tensor_parallel_fused_allreduce_merged"] = chain.measure_tp(
+                tokens=20, fused_allreduce=True, merge_projections=True)
         except Exception as e:  # noqa: BLE001
             extra["tinyllama_gemv_chain_tensor_parallel_fused_allreduce"] = {"error": repr(e)}
         kern_name = "gemv_ring_kernel<E5M2> (per-rank block)"

@@ -90,7 +90,8 @@ class TensorParallelChain:
     """
 
     def __init__(self, mode: str = "E4M3", seed: int = 6, group=None, layers: int = LAYERS,
-                 static_matrix: bool = True, fused_allreduce: bool = False):
+                 static_matrix: bool = True, fused_allreduce: bool = False,
+                 merge_projections: bool = False):
         import torch.distributed as dist
         from .sharded import ColumnShardedGemv, PeerAllReduce
         self.dist, self.group = dist, group
@@ -129,8 +130,13 @@ class TensorParallelChain:
                 shard = w[r * rows:(r + 1) * rows]
                 self.ops.append(("rows", fb.pack_fp8_tensor(shard, mode), acts[n], (rows, n),
                                  torch.empty(rows, dtype=torch.float32, device=device)))
+        # merge_projections: as in GemvChain, q/k/v and gate/up become one
+        # row-split GEMV each (a rank's rows of the members, concatenated)
+        shapes = LAYER_SHAPES if not merge_projections else (
+            ("qkv", HIDDEN + 2 * KV_DIM, HIDDEN), ("o", HIDDEN, HIDDEN),
+            ("gate_up", 2 * INTER, HIDDEN), ("down", HIDDEN, INTER))
         for _ in range(layers):
-            for name, m, n in LAYER_SHAPES:
+            for name, m, n in shapes:
                 add(name, m, n)
         add("lm_head", VOCAB, HIDDEN)
         torch.cuda.synchronize()
@@ -150,10 +156,21 @@ class TensorParallelChain:
 
 
 def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", group=None,
-               fused_allreduce: bool = False) -> dict:
+               fused_allreduce: bool = False, merge_projections: bool = False) -> dict:
     """Tokens per second of the tensor-parallel chain (call on every rank)."""
     import torch.distributed as dist
-    chain = TensorParallelChain(mode, group=group, fused_allreduce=fused_allreduce)
+    chain = TensorParallelChain(mode, group=group, fused_allreduce=fused_allreduce,
+                                merge_projections=merge_projections)
+    # First token with a short wait limit: if the ranks cannot reach each other the
+    # fused all-reduce gives up quickly and the status check raises here, instead of
+    # every later call waiting out the default limit.
+    lib = fb._lib.load()
+    fb._lib.check(lib.feather_set_wait_limit_ms(200))
+    try:
+        chain.token()
+        fb.device_status()
+    finally:
+        fb._lib.check(lib.feather_set_wait_limit_ms(2000))
     for _ in range(3):
         chain.token()
     torch.cuda.synchronize()
@@ -186,7 +203,7 @@ def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", gro
     return {"tokens_per_s": round(1e3 / ms, 1), "us_per_token": round(ms * 1e3, 1),
             "gemvs_per_token_per_rank": len(chain.ops),
             "all_reduces_per_token": sum(1 for o in chain.ops if o[0] in ("cols", "fused")),
-            "fused_allreduce": chain.fused_allreduce,
+            "fused_allreduce": chain.fused_allreduce, "merged_projections": merge_projections,
             "world": chain.world, "cuda_graph": graphed, "mode": mode}
 
 
