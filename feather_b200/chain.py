@@ -165,6 +165,8 @@ def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", gro
     # fused all-reduce gives up quickly and the status check raises here, instead of
     # every later call waiting out the default limit.
     lib = fb._lib.load()
+    torch.cuda.synchronize()
+    dist.barrier(group=group)  # all ranks have built their shards: they start the token together
     fb._lib.check(lib.feather_set_wait_limit_ms(200))
     try:
         chain.token()
