@@ -465,6 +465,12 @@ def run_ours(args) -> None:
             extra["tinyllama_gemv_chain_1gpu"] = chain.measure(tokens=20, use_graph=True)
             extra["tinyllama_gemv_chain_1gpu_merged_qkv_gateup"] = chain.measure(
                 tokens=20, use_graph=True, merge_projections=True)
+            # every result re-encoded to packed FP8 (what a chained model needs):
+            # in the GEMV epilogue, or as a second launch of the packer
+            extra["tinyllama_gemv_chain_1gpu_reencode_fused"] = chain.measure(
+                tokens=20, use_graph=True, reencode="fused")
+            extra["tinyllama_gemv_chain_1gpu_reencode_separate_launch"] = chain.measure(
+                tokens=20, use_graph=True, reencode="separate")
         except Exception as e:  # noqa: BLE001 - the extra section must not sink the headline
             extra["tinyllama_gemv_chain_1gpu"] = {"error": repr(e)}
         # dot on two 2^26-element E5M2 vectors: reuse the packed matrices as operands

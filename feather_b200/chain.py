@@ -37,10 +37,18 @@ class GemvChain:
     the 155 GEMVs of one token on the current stream."""
 
     def __init__(self, mode: str = "E4M3", seed: int = 6, device: str = "cuda",
-                 layers: int = LAYERS, static_matrix: bool = True, merge_projections: bool = False):
+                 layers: int = LAYERS, static_matrix: bool = True, merge_projections: bool = False,
+                 reencode: str | None = None):
+        """``reencode``: None = FP32 results only; "fused" = every GEMV writes its
+        result as packed FP8 words from its own epilogue (``gemv_fp8_ret_packed_gpu``);
+        "separate" = FP32 result, then the packer as a second launch."""
+        if reencode not in (None, "fused", "separate"):
+            raise ValueError("reencode must be None, 'fused' or 'separate'")
         gen = torch.Generator(device=device).manual_seed(seed)
         self.mode = mode
         self.static_matrix = static_matrix
+        self.reencode = reencode
+        self.packed = []  # per op: the packed-output buffer
         self.ops = []  # (packed weights, packed activation, (M, N), out)
         acts = {}
         for n in (HIDDEN, INTER):
@@ -51,6 +59,7 @@ class GemvChain:
             w = (0.02 * torch.randn(m, n, device=device, generator=gen)).to(torch.float16)
             self.ops.append((fb.pack_fp8_tensor(w, mode), acts[n], (m, n),
                              torch.empty(m, dtype=torch.float32, device=device)))
+            self.packed.append(torch.empty((m + 3) // 4, dtype=torch.uint32, device=device))
         # merge_projections: q/k/v share their input vector, and so do gate/up, so
         # each group is ONE GEMV over the row-concatenated weights (same results,
         # 89 instead of 155 launches per token)
@@ -64,9 +73,19 @@ class GemvChain:
         torch.cuda.synchronize()  # weights are final before any static_matrix GEMV runs
 
     def token(self) -> None:
-        for w, a, shape, out in self.ops:
+        if self.reencode == "fused":
+            for (w, a, shape, _), words in zip(self.ops, self.packed):
+                fb.gemv_fp8_ret_packed_gpu(w, a, shape, self.mode, out=words,
+                                           static_matrix=self.static_matrix)
+            return
+        for (w, a, shape, out), words in zip(self.ops, self.packed):
             fb.gemv_fp8_acc_fp32_gpu(w, a, shape, self.mode, out=out,
                                      static_matrix=self.static_matrix)
+            if self.reencode == "separate":  # the packer's kernel on the FP32 result
+                lib, idx = fb._lib.load(), out.device.index
+                fb._lib.check(lib.feather_encode_fp8(out.data_ptr(), fb._lib.SRC_F32, words.data_ptr(),
+                                                     out.numel(), fb._lib.mode_id(self.mode),
+                                                     fb._lib.current_stream_ptr(idx)))
 
     def bytes_per_token(self) -> int:
         return sum(m * n + n + 4 * m for _, _, (m, n), _ in self.ops)
@@ -210,8 +229,8 @@ def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", gro
 
 
 def measure(tokens: int = 50, use_graph: bool = True, mode: str = "E4M3",
-            merge_projections: bool = False) -> dict:
-    chain = GemvChain(mode, merge_projections=merge_projections)
+            merge_projections: bool = False, reencode: str | None = None) -> dict:
+    chain = GemvChain(mode, merge_projections=merge_projections, reencode=reencode)
     for _ in range(3):
         chain.token()
     torch.cuda.synchronize()
@@ -238,7 +257,7 @@ def measure(tokens: int = 50, use_graph: bool = True, mode: str = "E4M3",
     return {"tokens_per_s": round(1e3 / ms, 1), "us_per_token": round(ms * 1e3, 1),
             "gemvs_per_token": len(chain.ops), "GB/s": round(nbytes / ms / 1e6, 1),
             "bytes_per_token": nbytes, "cuda_graph": use_graph, "mode": mode,
-            "merged_projections": merge_projections}
+            "merged_projections": merge_projections, "reencode": reencode}
 
 
 if __name__ == "__main__":

@@ -261,7 +261,7 @@ static bool ring_eligible(const void* m, long long M, long long N, const DeviceI
 
 template <int MODE, int RW, int U, bool EARLY>
 static int gemv_rows_launch(const uint32_t* m, const uint32_t* v, float* out, long long M,
-                            long long N, cudaStream_t s) {
+                            long long N, cudaStream_t s, int out_code = -1) {
     auto kernel = gemv_rows_kernel<MODE, RW, U, EARLY, false>;
     static std::atomic<unsigned long long> configured{0};
     if (int st = ensure_smem(kernel, gemv_rows_smem_bytes(kRowsTileCodes), configured)) return st;
@@ -277,7 +277,7 @@ static int gemv_rows_launch(const uint32_t* m, const uint32_t* v, float* out, lo
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const uint4*>(m), v, out,
-                                             (int)M, (int)(N / 16), NoAllReduce{},
+                                             (int)M, (int)(N / 16), out_code, NoAllReduce{},
                                              static_cast<unsigned int*>(nullptr));
     return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
 }
@@ -311,36 +311,51 @@ static int gemv_allreduce_launch(const uint32_t* m, const uint32_t* v, long long
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const uint4*>(m), v,
-                                             static_cast<float*>(nullptr), (int)M, (int)(N / 16), ar,
+                                             static_cast<float*>(nullptr), (int)M, (int)(N / 16), -1, ar,
                                              status);
     return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
 }
 
+// out_code < 0: `out` receives M FP32 sums.  out_code = kE5M2 / kE4M3: `out`
+// receives ceil(M / 4) packed words of the sums encoded to that format; the
+// warp-owned-rows kernel encodes in its epilogue, the other kernels write the
+// sums to `workspace` (M floats) and the encoder runs behind them.
 template <int MODE>
 static int gemv_launch(const uint32_t* m, const uint32_t* v, float* out, long long M, long long N,
-                       const DeviceInfo& dev, cudaStream_t s, bool static_matrix = false) {
+                       const DeviceInfo& dev, cudaStream_t s, bool static_matrix = false,
+                       int out_code = -1, float* workspace = nullptr) {
     const bool vec_ok = (N % 16 == 0) && aligned(m, 16);
-    if (ring_eligible(m, M, N, dev))
-        return static_matrix
-                   ? gemv_ring_launch<MODE, false, true>(m, v, out, M, N, dev, s, ShardArgs{})
-                   : gemv_ring_launch<MODE, false>(m, v, out, M, N, dev, s, ShardArgs{});
-    if (!vec_ok) {
-        const long long blocks = (M + 7) / 8;  // 8 warps per CTA, one row per warp
-        const long long cap = (long long)dev.sm_count * 8;
-        gemv_general_kernel<MODE><<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(
-            m, v, out, (int)M, (int)(N / 4));
-        return launch_status();
+    const bool ring = ring_eligible(m, M, N, dev);
+    if (ring || !vec_ok) {
+        float* sums = out_code < 0 ? out : workspace;
+        if (!sums) return FEATHER_ERR_WORKSPACE;
+        int st;
+        if (ring) {
+            st = static_matrix
+                     ? gemv_ring_launch<MODE, false, true>(m, v, sums, M, N, dev, s, ShardArgs{})
+                     : gemv_ring_launch<MODE, false>(m, v, sums, M, N, dev, s, ShardArgs{});
+        } else {
+            const long long blocks = (M + 7) / 8;  // 8 warps per CTA, one row per warp
+            const long long cap = (long long)dev.sm_count * 8;
+            gemv_general_kernel<MODE><<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(
+                m, v, sums, (int)M, (int)(N / 4));
+            st = launch_status();
+        }
+        if (st != FEATHER_OK || out_code < 0) return st;
+        uint32_t* words = reinterpret_cast<uint32_t*>(out);
+        return out_code == kE5M2 ? encode_launch<kE5M2, true>(sums, words, M, s)
+                                 : encode_launch<kE4M3, true>(sums, words, M, s);
     }
     // warp-owned rows: as many rows per warp as still leaves ~16 warps per SM
     const long long warps_wanted = (long long)dev.sm_count * 16;
     if (M >= 4 * warps_wanted)
-        return static_matrix ? gemv_rows_launch<MODE, 4, 2, true>(m, v, out, M, N, s)
-                             : gemv_rows_launch<MODE, 4, 2, false>(m, v, out, M, N, s);
+        return static_matrix ? gemv_rows_launch<MODE, 4, 2, true>(m, v, out, M, N, s, out_code)
+                             : gemv_rows_launch<MODE, 4, 2, false>(m, v, out, M, N, s, out_code);
     if (M >= 2 * warps_wanted)
-        return static_matrix ? gemv_rows_launch<MODE, 2, 4, true>(m, v, out, M, N, s)
-                             : gemv_rows_launch<MODE, 2, 4, false>(m, v, out, M, N, s);
-    return static_matrix ? gemv_rows_launch<MODE, 1, 4, true>(m, v, out, M, N, s)
-                         : gemv_rows_launch<MODE, 1, 4, false>(m, v, out, M, N, s);
+        return static_matrix ? gemv_rows_launch<MODE, 2, 4, true>(m, v, out, M, N, s, out_code)
+                             : gemv_rows_launch<MODE, 2, 4, false>(m, v, out, M, N, s, out_code);
+    return static_matrix ? gemv_rows_launch<MODE, 1, 4, true>(m, v, out, M, N, s, out_code)
+                         : gemv_rows_launch<MODE, 1, 4, false>(m, v, out, M, N, s, out_code);
 }
 
 template <int MODE>
@@ -502,6 +517,40 @@ int feather_gemv_fp8_ex(const uint32_t* m, const uint32_t* v, float* out, int64_
     const bool static_matrix = (flags & FEATHER_GEMV_STATIC_MATRIX) != 0;
     return mode == FEATHER_MODE_E5M2 ? gemv_launch<kE5M2>(m, v, out, M, N, *dev, s, static_matrix)
                                      : gemv_launch<kE4M3>(m, v, out, M, N, *dev, s, static_matrix);
+}
+
+int64_t feather_gemv_fp8_packed_workspace_bytes(int64_t M, int64_t N) {
+    if (M <= 0 || N <= 0 || (N & 3)) return 0;
+    const DeviceInfo* dev;
+    if (device_info(&dev)) return 4 * M;
+    return ((N & 15) || ring_eligible(nullptr, M, N, *dev)) ? 4 * M : 0;
+}
+
+int feather_gemv_fp8_packed(const uint32_t* m, const uint32_t* v, uint32_t* out_words,
+                            void* workspace, int64_t M, int64_t N, int mode, int out_mode,
+                            uint32_t flags, void* stream) {
+    if (flags & ~(uint32_t)FEATHER_GEMV_STATIC_MATRIX) return FEATHER_ERR_BAD_ARG;
+    if (M < 0 || N < 0 || (N & 3) || M > 0x7FFFFFFF || N > 0x7FFFFFFFll * 4) return FEATHER_ERR_BAD_ARG;
+    if ((mode != FEATHER_MODE_E5M2 && mode != FEATHER_MODE_E4M3) ||
+        (out_mode != FEATHER_MODE_E5M2 && out_mode != FEATHER_MODE_E4M3))
+        return FEATHER_ERR_MODE;
+    if (M == 0) return FEATHER_OK;
+    if (!out_words || (N > 0 && (!m || !v))) return FEATHER_ERR_BAD_ARG;
+    if (!aligned(m, 4) || !aligned(v, 4) || !aligned(out_words, 4) || !aligned(workspace, 4))
+        return FEATHER_ERR_MISALIGNED;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (N == 0)  // empty rows sum to +0, which encodes as code 0 in both formats
+        return cudaMemsetAsync(out_words, 0, 4 * (size_t)((M + 3) / 4), s) == cudaSuccess
+                   ? FEATHER_OK : FEATHER_ERR_LAUNCH;
+    const bool static_matrix = (flags & FEATHER_GEMV_STATIC_MATRIX) != 0;
+    float* out = reinterpret_cast<float*>(out_words);
+    float* ws = static_cast<float*>(workspace);
+    const int out_code = out_mode == FEATHER_MODE_E5M2 ? kE5M2 : kE4M3;
+    return mode == FEATHER_MODE_E5M2
+               ? gemv_launch<kE5M2>(m, v, out, M, N, *dev, s, static_matrix, out_code, ws)
+               : gemv_launch<kE4M3>(m, v, out, M, N, *dev, s, static_matrix, out_code, ws);
 }
 
 // Base address of the cudaMalloc allocation that contains `ptr` (the driver's

@@ -17,6 +17,11 @@
 //   * launched with programmatic stream serialisation; with the static-matrix
 //     promise the first matrix loads are issued before the stream-order wait.
 //
+//   * out_code >= 0: the FP32 sums are not stored; the CTA encodes its rows'
+//     sums to FP8 codes of that format (the packer's rounding) and stores
+//     packed words, four rows per word, row r in byte r % 4 of word r / 4 --
+//     the packed vector the next GEMV of a chain consumes.
+//
 // gemv_general_kernel: any N % 4 == 0, 4-byte aligned; one warp per row, word
 //   loads.  Used for ragged shapes.
 #pragma once
@@ -52,7 +57,7 @@ struct NoAllReduce {};
 template <int MODE, int RW, int U, bool EARLY, bool ALLREDUCE = false>
 __global__ void __launch_bounds__(kRowsThreads)
 gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
-                 float* __restrict__ out, int M, int n16,
+                 float* __restrict__ out, int M, int n16, int out_code,
                  const __grid_constant__ std::conditional_t<ALLREDUCE, AllReduceArgs, NoAllReduce> ar,
                  unsigned int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char rows_smem[];
@@ -85,7 +90,7 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
     if (EARLY) issue(rows, active, 0);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (!EARLY) issue(rows, active, 0);
-    __shared__ float ar_part[ALLREDUCE ? kGroupRows : 1];
+    __shared__ float ar_part[kGroupRows];  // a CTA's row sums, for the all-reduce / packed output
     unsigned int epoch = 0;
     if constexpr (ALLREDUCE) {
         // this call's number: one more than the calls completed on this rank
@@ -104,11 +109,28 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
             warp_reduce_rows<RW>(sums, lane);
             if ((lane & (32 / RW - 1)) == 0) {
                 const int row = row0 + lane / (32 / RW);
-                if constexpr (ALLREDUCE) ar_part[warp * RW + lane / (32 / RW)] = sums[0];
+                if (ALLREDUCE || out_code >= 0) ar_part[warp * RW + lane / (32 / RW)] = row < M ? sums[0] : 0.f;
                 else if (row < M) out[row] = sums[0];
             }
-        } else if constexpr (ALLREDUCE) {
+        } else if (ALLREDUCE || out_code >= 0) {
             if (lane < RW) ar_part[warp * RW + lane] = 0.f;
+        }
+        if (!ALLREDUCE && out_code >= 0) {  // CTA-uniform
+            // rows past M encode as code 0, like the packer's zero-padded tail
+            __syncthreads();
+            const int cta_row0 = group * kGroupRows;
+            if (threadIdx.x < kGroupRows / 4 && cta_row0 + 4 * (int)threadIdx.x < M) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float x = ar_part[4 * threadIdx.x + i];
+                    const bool live = cta_row0 + 4 * (int)threadIdx.x + i < M;
+                    const uint32_t c = out_code == kE5M2 ? encode_f32<kE5M2>(x) : encode_f32<kE4M3>(x);
+                    word |= (live ? c : 0u) << (8 * i);
+                }
+                reinterpret_cast<uint32_t*>(out)[cta_row0 / 4 + threadIdx.x] = word;
+            }
+            __syncthreads();  // ar_part is free for the next row group
         }
 #pragma unroll
         for (int r = 0; r < RW; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;

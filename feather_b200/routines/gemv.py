@@ -15,7 +15,8 @@ import torch
 from .. import _lib
 from ..packers.fp8 import as_words
 
-__all__ = ["gemv_fp8_acc_fp32_gpu", "gemv_fp8_e5m2_acc_fp32_gpu", "gemv_fp8_e4m3_acc_fp32_gpu"]
+__all__ = ["gemv_fp8_acc_fp32_gpu", "gemv_fp8_e5m2_acc_fp32_gpu", "gemv_fp8_e4m3_acc_fp32_gpu",
+           "gemv_fp8_ret_packed_gpu"]
 
 
 def gemv_fp8_acc_fp32_gpu(m: torch.Tensor, v: torch.Tensor, m_shape, mode: str = "E5M2",
@@ -34,7 +35,28 @@ def gemv_fp8_acc_fp32_gpu(m: torch.Tensor, v: torch.Tensor, m_shape, mode: str =
         return _gemv(m, v, m_shape, mode, out, 1 if static_matrix else 0)
 
 
-def _gemv(m, v, m_shape, mode, out, flags):
+def gemv_fp8_ret_packed_gpu(m: torch.Tensor, v: torch.Tensor, m_shape, mode: str = "E5M2",
+                            out_mode: str | None = None, out: torch.Tensor | None = None,
+                            static_matrix: bool = False, workspace: torch.Tensor | None = None):
+    """The GEMV with its result re-encoded to packed FP8 in the same launch:
+    ``pack_fp8_tensor(gemv(m, v, m_shape), out_mode)`` bit for bit -- the packed
+    activation the next GEMV of a chain takes.  No reference counterpart (there
+    the result goes through the CPU packer, feather/packers/fp8.py:260-281).
+
+    Returns ``ceil(M / 4)`` packed words (a ``PackedFP8`` tagged ``out_mode``,
+    default: ``mode``).  Small and mid-size matrices encode in the GEMV kernel's
+    epilogue; large ones (and rows that are not whole 16-byte chunks) run the
+    encoder behind the GEMV kernel on ``workspace`` (M floats, allocated here
+    when not given)."""
+    from ..packers.fp8 import _tag
+    out_mode = mode if out_mode is None else out_mode
+    with torch._C.DisableTorchFunctionSubclass():
+        words = _gemv(m, v, m_shape, mode, out, 1 if static_matrix else 0,
+                      out_mode_id=_lib.mode_id(out_mode), workspace=workspace)
+        return words if out is not None else _tag(words, out_mode)
+
+
+def _gemv(m, v, m_shape, mode, out, flags, out_mode_id=None, workspace=None):
     mode_id = _lib.mode_id(mode)
     m = as_words(m, "m")
     v = as_words(v, "v")
@@ -49,6 +71,8 @@ def _gemv(m, v, m_shape, mode, out, flags):
         raise ValueError(f"v holds {v.numel()} words, N={N} needs {N // 4}")
     if v.device != m.device:
         raise ValueError("m and v must be on the same device")
+    if out_mode_id is not None:
+        return _gemv_packed(m, v, M, N, mode_id, out_mode_id, out, flags, workspace)
     if out is None:
         out = torch.empty((M,), dtype=torch.float32, device=m.device)
     elif (out.dtype != torch.float32 or out.numel() != M or out.device != m.device
@@ -64,6 +88,35 @@ def _gemv(m, v, m_shape, mode, out, flags):
             with torch.cuda.device(idx):
                 _lib.check(fn(m.data_ptr(), v.data_ptr(), out.data_ptr(), M, N, mode_id, flags,
                               _lib.current_stream_ptr(idx)))
+    return out
+
+
+def _gemv_packed(m, v, M, N, mode_id, out_mode_id, out, flags, workspace):
+    n_words = (M + 3) // 4
+    if out is None:
+        out = torch.empty((n_words,), dtype=torch.uint32, device=m.device)
+    else:
+        out = as_words(out, "out")
+        if out.numel() != n_words or out.device != m.device:
+            raise ValueError("out must hold ceil(M / 4) packed words on m's device")
+    if M:
+        lib = _lib.load()
+        idx = m.device.index
+        with torch.cuda.device(idx):
+            ws_ptr = None
+            need = int(lib.feather_gemv_fp8_packed_workspace_bytes(M, N))
+            if m.data_ptr() % 16:
+                need = 4 * M  # unaligned rows take the word-load kernel, which does not encode
+            if need:
+                if workspace is None:
+                    workspace = torch.empty((M,), dtype=torch.float32, device=m.device)
+                elif (workspace.dtype != torch.float32 or workspace.numel() < M
+                      or workspace.device != m.device or not workspace.is_contiguous()):
+                    raise ValueError("workspace must be a contiguous float32 tensor of >= M elements")
+                ws_ptr = workspace.data_ptr()
+            _lib.check(lib.feather_gemv_fp8_packed(m.data_ptr(), v.data_ptr(), out.data_ptr(), ws_ptr,
+                                                   M, N, mode_id, out_mode_id, flags,
+                                                   _lib.current_stream_ptr(idx)))
     return out
 
 

@@ -116,6 +116,28 @@ int feather_gemv_fp8_ex(const uint32_t* m, const uint32_t* v, float* out, int64_
                         int mode, uint32_t flags, void* stream);
 
 /*
+ * The GEMV with its result re-encoded to packed FP8: out_words receives
+ * ceil(M / 4) words holding encode(out[0..M)) in `out_mode`, the tail padded
+ * with zero codes -- exactly feather_encode_fp8 applied to feather_gemv_fp8's
+ * FP32 result, i.e. the packed activation the next GEMV of a chain takes.  No
+ * reference counterpart: there the FP32 result goes back through the CPU
+ * packer (feather/packers/fp8.py:260-281) before it can feed
+ * feather/routines/gemv.py:136 again.
+ *   workspace   M floats, or NULL.  Matrices of N % 16 == 0 with 16-byte aligned
+ *               rows that do not take the large-matrix kernel encode in the
+ *               GEMV kernel's epilogue and ignore it
+ *               (feather_gemv_fp8_packed_workspace_bytes returns 0 for their
+ *               (M, N)); all others write their sums there and the encoder
+ *               runs behind the GEMV on the same stream.  FEATHER_ERR_WORKSPACE
+ *               if it is needed and NULL.
+ *   flags       as feather_gemv_fp8_ex
+ */
+int feather_gemv_fp8_packed(const uint32_t* m, const uint32_t* v, uint32_t* out_words,
+                            void* workspace, int64_t M, int64_t N, int mode, int out_mode,
+                            uint32_t flags, void* stream);
+int64_t feather_gemv_fp8_packed_workspace_bytes(int64_t M, int64_t N);
+
+/*
  * One rank of a row-sharded GEMV with the gather of the output slices fused
  * into the kernel.  The reference is single-GPU (feather/routines/gemv.py:136,
  * :187 hard-code one device); rows are independent, so rank r of `world` holds

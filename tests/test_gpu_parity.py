@@ -617,3 +617,56 @@ def test_allreduce_gemv_world_1_and_missing_peer(fb):
         assert torch.equal(inbox[1][4 * M: 6 * M].view(torch.int32), _tagged(own, 1).view(torch.int32))
     finally:
         assert lib.feather_set_wait_limit_ms(2000) == 0
+
+
+# ---------------------------------------------- GEMV with re-encoded output --
+@pytest.mark.parametrize("mode,out_mode", [("E5M2", "E5M2"), ("E4M3", "E4M3"), ("E4M3", "E5M2")])
+@pytest.mark.parametrize("shape", [(8, 16), (37, 2064), (2048, 2048), (2046, 2048), (5632, 2048),
+                                   (2048, 5632), (32000, 2048), (19000, 1024), (33, 20), (7, 2052),
+                                   (4736, 4096), (4801, 8192), (100, 40000)])
+def test_gemv_packed_output_equals_gemv_then_pack(fb, c_oracle, mode, out_mode, shape):
+    """The fused GEMV -> re-encode result is, bit for bit, the packer applied to
+    the plain GEMV result (checked with the ORACLE packer on the GPU's FP32 sums,
+    and against this package's own packer): every dispatch path -- one, two and
+    four rows per warp, the word-load kernel, the large-matrix kernel -- ragged M
+    (zero-padded last word), and a different output format."""
+    M, N = shape
+    gen = torch.Generator(device="cuda").manual_seed(M * 31 + N)
+    # wide value range so that the sums hit subnormal, normal and overflowing codes
+    A = (torch.randn(M, N, device="cuda", generator=gen) *
+         torch.exp2(torch.randint(-9, 4, (M, 1), device="cuda", generator=gen).float())).to(torch.float16)
+    v = torch.randn(N, device="cuda", generator=gen, dtype=torch.float16)
+    mw, vw = fb.pack_fp8_tensor(A, mode), fb.pack_fp8_tensor(v, mode)
+    y = fb.gemv_fp8_acc_fp32_gpu(mw, vw, (M, N), mode)
+    got = fb.gemv_fp8_ret_packed_gpu(mw, vw, (M, N), mode, out_mode=out_mode)
+    assert got.dtype == torch.uint32 and got.numel() == (M + 3) // 4 and got.feather_mode == out_mode
+    want = c_oracle.pack(y.cpu().numpy(), out_mode)
+    assert np.array_equal(got.view(torch.int32).cpu().numpy().view(np.uint32), want)
+    assert torch.equal(got.view(torch.int32), fb.pack_fp8_tensor(y, out_mode).view(torch.int32))
+    # static-matrix flag and a caller-supplied output buffer: same words
+    out = torch.zeros((M + 3) // 4, dtype=torch.uint32, device="cuda")
+    fb.gemv_fp8_ret_packed_gpu(mw, vw, (M, N), mode, out_mode=out_mode, out=out, static_matrix=True)
+    assert torch.equal(out.view(torch.int32), got.view(torch.int32))
+
+
+def test_gemv_packed_output_feeds_next_gemv_and_rejects(fb):
+    lib = fb._lib.load()
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    A = (0.05 * torch.randn(2048, 2048, device="cuda", generator=gen)).to(torch.float16)
+    B = (0.05 * torch.randn(512, 2048, device="cuda", generator=gen)).to(torch.float16)
+    x = torch.randn(2048, device="cuda", generator=gen, dtype=torch.float16)
+    aw, bw, xw = (fb.pack_fp8_tensor(t, "E4M3") for t in (A, B, x))
+    h = fb.gemv_fp8_ret_packed_gpu(aw, xw, A.shape, "E4M3")          # packed activation
+    y = fb.gemv(bw, h, original_shape=B.shape)                        # mode read from the tag
+    h_ref = fb.pack_fp8_tensor(fb.gemv(aw, xw, original_shape=A.shape), "E4M3")
+    assert torch.equal(y, fb.gemv(bw, h_ref, original_shape=B.shape))
+    # the large-matrix path needs a workspace; without one the C entry says so
+    assert lib.feather_gemv_fp8_packed_workspace_bytes(2048, 2048) == 0
+    assert lib.feather_gemv_fp8_packed_workspace_bytes(16384, 16384) == 4 * 16384
+    assert lib.feather_gemv_fp8_packed_workspace_bytes(64, 20) == 4 * 64
+    p = aw.data_ptr()
+    assert lib.feather_gemv_fp8_packed(p, p, p, None, 64, 20, 0, 0, 0, None) == -6
+    assert lib.feather_gemv_fp8_packed(p, p, p, None, 64, 16, 0, 5, 0, None) == -3
+    assert lib.feather_gemv_fp8_packed(p, p, p, None, 64, 18, 0, 0, 0, None) == -1
+    assert fb.gemv_fp8_ret_packed_gpu(aw, xw, (0, 2048), "E4M3").numel() == 0
+    torch.cuda.synchronize()
