@@ -487,6 +487,21 @@ def run_ours(args) -> None:
         extra["dot_e5m2_2pow26"] = {"us_per_call": round(ms_d * 1e3, 3),
                                     "GB/s": round(db / ms_d / 1e6, 1),
                                     "frac_of_peak": round(db / ms_d / 1e6 / peak, 4)}
+        # ReLU on unpack, 2^26 E5M2 codes -> FP32 (reads 1 B, writes 4 B per element);
+        # inputs rotate, the 256 MiB output alone exceeds L2
+        from feather_b200.routines.activations import relu1d_fp8_ret_fp32_feather_gpu as relu
+        relu_out = torch.empty(4 * n_words, dtype=torch.float32, device=dev)
+        st4 = {"i": 0}
+
+        def step_r():
+            relu(ops[st4["i"] % n_buf][0], 4 * n_words, mode="E5M2", out=relu_out)
+            st4["i"] += 1
+        ms_r = time_calls(torch, step_r, n_it, 10)
+        rb = 5 * 4 * n_words
+        extra["relu_unpack_e5m2_2pow26"] = {"us_per_call": round(ms_r * 1e3, 3),
+                                            "GB/s": round(rb / ms_r / 1e6, 1),
+                                            "frac_of_peak": round(rb / ms_r / 1e6 / peak, 4)}
+        del relu_out
         # encoder: fp16 16384^2 -> E5M2 (reads 2 B, writes 1 B per element)
         gen.manual_seed(9)
         src = torch.randn(M, N, device=dev, generator=gen, dtype=torch.float16)

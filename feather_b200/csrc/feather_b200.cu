@@ -119,18 +119,37 @@ __device__ __forceinline__ float4 decode4(uint32_t w) {
     return decode_word_ordered<MODE>(w);  // E5M2: both semantics coincide
 }
 
-template <int MODE, bool IEEE>
+// One packed word per thread and step, four steps in flight: the word loads of a
+// warp are one 128-byte line, its float4 stores one 512-byte run.  RELU: the
+// reference's ReLU-on-unpack (feather/routines/activations.py:8-29), max(0, x)
+// with the compiled kernel's semantics of max: a NaN code gives 0, -0 gives +0.
+template <int MODE, bool IEEE, bool RELU>
 __global__ void __launch_bounds__(256)
 decode_kernel(const uint32_t* __restrict__ src, float* __restrict__ dst, long long n_elems) {
-    const long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long e = w * 4;
-    if (e >= n_elems) return;
-    const float4 f = decode4<MODE, IEEE>(__ldg(src + w));
-    if (e + 4 <= n_elems && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-        reinterpret_cast<float4*>(dst)[w] = f;
-    } else {
-        const float x[4] = {f.x, f.y, f.z, f.w};
-        for (int i = 0; i < 4 && e + i < n_elems; ++i) dst[e + i] = x[i];
+    const long long n_words = (n_elems + 3) >> 2;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const bool vec = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+    for (long long w0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; w0 < n_words; w0 += 4 * stride) {
+        uint32_t x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const long long w = w0 + u * stride;
+            x[u] = w < n_words ? __ldg(src + w) : 0u;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const long long w = w0 + u * stride;
+            if (w >= n_words) break;
+            float4 f = decode4<MODE, IEEE>(x[u]);
+            if (RELU) f = make_float4(fmaxf(0.f, f.x), fmaxf(0.f, f.y), fmaxf(0.f, f.z), fmaxf(0.f, f.w));
+            const long long e = w * 4;
+            if (vec && e + 4 <= n_elems) {
+                __stcs(reinterpret_cast<float4*>(dst) + w, f);
+            } else {
+                const float y[4] = {f.x, f.y, f.z, f.w};
+                for (int i = 0; i < 4 && e + i < n_elems; ++i) dst[e + i] = y[i];
+            }
+        }
     }
 }
 
@@ -358,6 +377,28 @@ static int gemv_launch(const uint32_t* m, const uint32_t* v, float* out, long lo
                          : gemv_rows_launch<MODE, 1, 4, false>(m, v, out, M, N, s, out_code);
 }
 
+// Decode (optionally through ReLU) n_elems codes: a grid of up to 16 CTAs per SM,
+// each thread walking words with four loads in flight.
+static int decode_launch(const uint32_t* src, float* dst, long long n_elems, int mode, bool ieee,
+                         bool relu, const DeviceInfo& dev, cudaStream_t s) {
+    const long long n_words = (n_elems + 3) / 4;
+    long long blocks = (n_words + 4 * 256 - 1) / (4 * 256);
+    const long long cap = (long long)dev.sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    const unsigned g = (unsigned)blocks;
+    if (mode == FEATHER_MODE_E5M2) {
+        if (relu) decode_kernel<kE5M2, false, true><<<g, 256, 0, s>>>(src, dst, n_elems);
+        else decode_kernel<kE5M2, false, false><<<g, 256, 0, s>>>(src, dst, n_elems);
+    } else if (relu) {
+        decode_kernel<kE4M3, false, true><<<g, 256, 0, s>>>(src, dst, n_elems);
+    } else if (ieee) {
+        decode_kernel<kE4M3, true, false><<<g, 256, 0, s>>>(src, dst, n_elems);
+    } else {
+        decode_kernel<kE4M3, false, false><<<g, 256, 0, s>>>(src, dst, n_elems);
+    }
+    return launch_status();
+}
+
 template <int MODE>
 static int dot_launch(const uint32_t* a, const uint32_t* b, float* out, void* workspace,
                       long long n_words, const DeviceInfo& dev, cudaStream_t s) {
@@ -484,15 +525,18 @@ int feather_decode_fp8(const uint32_t* src, float* dst, int64_t n_elems, int mod
     const DeviceInfo* dev;
     if (int st = device_info(&dev)) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const long long n_words = (n_elems + 3) / 4;
-    const unsigned blocks = (unsigned)((n_words + 255) / 256);
-    if (mode == FEATHER_MODE_E5M2)
-        decode_kernel<kE5M2, false><<<blocks, 256, 0, s>>>(src, dst, n_elems);
-    else if (semantics == FEATHER_DECODE_KERNEL)
-        decode_kernel<kE4M3, false><<<blocks, 256, 0, s>>>(src, dst, n_elems);
-    else
-        decode_kernel<kE4M3, true><<<blocks, 256, 0, s>>>(src, dst, n_elems);
-    return launch_status();
+    return decode_launch(src, dst, n_elems, mode, semantics == FEATHER_DECODE_IEEE, false, *dev, s);
+}
+
+int feather_relu_fp8(const uint32_t* src, float* dst, int64_t n_elems, int mode, void* stream) {
+    if (n_elems < 0) return FEATHER_ERR_BAD_ARG;
+    if (mode != FEATHER_MODE_E5M2 && mode != FEATHER_MODE_E4M3) return FEATHER_ERR_MODE;
+    if (n_elems == 0) return FEATHER_OK;
+    if (!src || !dst) return FEATHER_ERR_BAD_ARG;
+    if (!aligned(src, 4) || !aligned(dst, 4)) return FEATHER_ERR_MISALIGNED;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    return decode_launch(src, dst, n_elems, mode, false, true, *dev, static_cast<cudaStream_t>(stream));
 }
 
 int feather_gemv_fp8(const uint32_t* m, const uint32_t* v, float* out, int64_t M, int64_t N,

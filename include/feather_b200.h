@@ -77,6 +77,19 @@ int feather_decode_fp8(const uint32_t* src, float* dst, int64_t n_elems, int mod
                        int semantics, void* stream);
 
 /*
+ * ReLU on unpack: dst[i] = max(0, decode(code i)) as FP32, for i < n_elems.
+ * Replaces _relu_1d_fp8_ret_fp32_kernel / relu1d_fp8_ret_fp32_feather_gpu
+ * (feather/routines/activations.py:8-29, :32-41), which exist for E5M2 only;
+ * E4M3 uses the GEMV kernels' decode (feather/routines/gemv.py:83-88) and is an
+ * extension.  max has the compiled kernel's semantics: a NaN code gives 0
+ * (the other operand), -0 gives +0.
+ *   src  ceil(n_elems / 4) packed words, 4-byte aligned
+ *   dst  n_elems floats (the reference always writes 4 per word; here the
+ *        last word may be cut short)
+ */
+int feather_relu_fp8(const uint32_t* src, float* dst, int64_t n_elems, int mode, void* stream);
+
+/*
  * out[r] = sum_j decode(m[r, j]) * decode(v[j]),  FP32 products and sums.
  * Replaces feather/routines/gemv.py:136-184 (gemv_fp8_e5m2_acc_fp32_gpu) and
  * :187-235 (gemv_fp8_e4m3_acc_fp32_gpu) with their kernels gemv.py:8-61 and

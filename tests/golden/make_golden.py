@@ -26,6 +26,7 @@ import torch
 logging.disable(logging.WARNING)  # the packer logs whole arrays for fp32 input
 warnings.simplefilter("ignore")
 
+import feather.routines.activations as ref_act
 import feather.routines.dot as ref_dot
 import feather.routines.gemv as ref_gemv
 from feather.packers.fp8 import pack_fp8_ndarray, pack_fp8_tensor, unpack_into_fp8_ndarray
@@ -96,7 +97,31 @@ def run_dot(aw: np.ndarray, bw: np.ndarray) -> np.float32:
     return np.float32(out.item())
 
 
+def run_relu(xw: np.ndarray) -> np.ndarray:
+    x = torch.from_numpy(xw.view(np.int32).copy())
+    out = torch.empty((4 * x.numel(),), dtype=torch.float32)
+    grid = ((x.numel() + 8191) // 8192,)
+    ref_act._relu_1d_fp8_ret_fp32_kernel[grid](x, out, x.numel(), 8192)  # activations.py:36-40
+    return out.numpy().copy()
+
+
+def make_relu() -> None:
+    """ReLU of packed E5M2 through the reference kernel: every code (as a byte
+    stream, so every lane), and a seeded N(0, 1) vector that spans two blocks."""
+    r = {}
+    r["all_codes_out"] = run_relu(np.arange(256, dtype=np.uint8).view(np.uint32))
+    rng = np.random.default_rng(41)
+    x = rng.standard_normal(4 * 9000 + 4).astype(np.float16)
+    r["n36004_out"] = run_relu(ref_pack(x, "E5M2"))
+    r["n36004_seed"] = np.array(41, dtype=np.int64)
+    np.savez_compressed(os.path.join(HERE, "relu.npz"), **r)
+    print("relu", os.path.getsize(os.path.join(HERE, "relu.npz")), "bytes")
+
+
 def main() -> None:
+    if sys.argv[1:] == ["relu"]:  # only the ReLU fixture (the others are unchanged)
+        return make_relu()
+    make_relu()
     # 1. encode: every fp16 bit pattern, seeded fp32 samples, fp32 edge list
     enc = {}
     h = np.arange(65536, dtype=np.uint16).view(np.float16)

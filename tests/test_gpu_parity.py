@@ -670,3 +670,35 @@ def test_gemv_packed_output_feeds_next_gemv_and_rejects(fb):
     assert lib.feather_gemv_fp8_packed(p, p, p, None, 64, 18, 0, 0, 0, None) == -1
     assert fb.gemv_fp8_ret_packed_gpu(aw, xw, (0, 2048), "E4M3").numel() == 0
     torch.cuda.synchronize()
+
+
+# ------------------------------------------------------------ ReLU on unpack --
+@pytest.mark.parametrize("mode", MODES)
+def test_relu_all_codes_ragged_and_large_vs_oracle(fb, golden, mode):
+    from feather_b200.routines.activations import relu1d_fp8_ret_fp32_feather_gpu as relu
+    bits = lambda t: t.view(torch.int32).cpu().numpy()
+    codes = torch.arange(256, dtype=torch.uint8).view(torch.int32).cuda()
+    got = relu(codes, 256, mode=mode)
+    assert np.array_equal(bits(got), O.relu(codes.cpu().numpy(), 256, mode).view(np.int32))  # sign of zero too
+    if mode == "E5M2":  # the reference kernel's own output (NaN codes apart, see the oracle test)
+        want = golden("relu")["all_codes_out"]
+        keep = ~np.isnan(want)
+        assert np.array_equal(got.cpu().numpy()[keep], want[keep])
+        rng = np.random.default_rng(int(golden("relu")["n36004_seed"]))
+        x = torch.from_numpy(rng.standard_normal(4 * 9000 + 4).astype(np.float16)).cuda()
+        packed = fb.pack_fp8_tensor(x, "E5M2")
+        assert np.array_equal(relu(packed, x.numel()).cpu().numpy(), golden("relu")["n36004_out"])
+        assert torch.equal(relu(packed), relu(packed, x.numel()))    # n defaults to 4 per word, mode to the tag
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    words = torch.randint(-2 ** 31, 2 ** 31 - 1, ((1 << 22) + 3,), device="cuda", generator=gen, dtype=torch.int32)
+    for n in (4 * words.numel(), 4 * words.numel() - 3, 5, 1):
+        out = relu(words, n, mode=mode)
+        assert np.array_equal(bits(out), O.relu(words.cpu().numpy(), n, mode).view(np.int32))
+    off = relu(words[1:], 4 * (words.numel() - 1) - 1, mode=mode,
+               out=torch.empty(4 * words.numel() + 1, device="cuda")[1:4 * (words.numel() - 1)])  # unaligned dst
+    assert np.array_equal(bits(off), O.relu(words[1:].cpu().numpy(), off.numel(), mode).view(np.int32))
+    assert relu(words[:0], 0, mode=mode).numel() == 0
+    with pytest.raises(ValueError):
+        relu(words[:2], 9, mode=mode)
+    with pytest.raises(NotImplementedError):
+        relu(words[:2], 8, mode="E3M4")

@@ -172,3 +172,26 @@ def test_numpy_and_c_oracles_agree_bitwise(c_oracle, mode):
 def test_unknown_mode_raises():
     with pytest.raises(NotImplementedError):
         O.pack_fp8_ndarray(np.zeros(4, np.float16), "E3M4")
+
+
+# ------------------------------------------------------------ ReLU on unpack --
+def test_relu_matches_reference_kernel(golden):
+    """The restated ReLU (activations.py:8-29) against the reference kernel run
+    through Triton's interpreter.  All codes: equal where the value is not NaN;
+    on the six NaN codes the interpreter (numpy maximum) keeps NaN while the
+    compiled kernel's maximum -- which the restatement follows -- returns 0."""
+    g = golden("relu")
+    want = g["all_codes_out"]
+    got = O.relu(np.arange(256, dtype=np.uint8).view(np.uint32))
+    nan = np.isnan(want)
+    assert sorted(np.flatnonzero(nan)) == [0x7D, 0x7E, 0x7F, 0xFD, 0xFE, 0xFF]
+    assert np.array_equal(got[~nan], want[~nan]) and np.all(got[nan] == 0)
+    assert not np.signbit(got).any()            # -0 and negative codes give +0
+    assert got[0x7C] == np.inf and got[0xFC] == 0
+    rng = np.random.default_rng(int(g["n36004_seed"]))
+    x = rng.standard_normal(4 * 9000 + 4).astype(np.float16)
+    assert np.array_equal(O.relu(O.pack_fp8_ndarray(x, "E5M2").view(np.uint32)), g["n36004_out"])
+    # ragged length and the E4M3 extension (kernel decode: 0x7F is 480, 0x01 is 2^-17)
+    assert O.relu(np.array([0x3C3CBC3C], dtype=np.uint32), 3).tolist() == [1.0, 0.0, 1.0]
+    e4 = O.relu(np.array([0x8101FF7F], dtype=np.uint32), mode="E4M3")
+    assert e4.tolist() == [480.0, 0.0, 2.0 ** -17, 0.0]
