@@ -447,6 +447,25 @@ def run_ours(args) -> None:
             extra[f"gemv_e4m3_{mm}x{nn}"] = {"us_per_call": round(ms_s * 1e3, 3),
                                              "GB/s": round(b / ms_s / 1e6, 1),
                                              "frac_of_peak": round(b / ms_s / 1e6 / peak, 4)}
+        # several vectors in one pass over the matrix (feather_gemv_fp8_multi), both
+        # formats; "matrix_GB/s" counts the matrix once, "vs_single_calls" is batch x
+        # the single-vector time of this run divided by the multi-vector time
+        for name, mset, mmode, single_ms in (("e4m3", m4, "E4M3", ms4), ("e5m2", mats, mode, kern_ms)):
+            for nb in (4, 8):
+                gen.manual_seed(21)
+                Vn = fb.pack_fp8_tensor(torch.randn(nb, N, device=dev, generator=gen, dtype=torch.float16),
+                                        mmode)
+                outn = torch.empty(nb, M, dtype=torch.float32, device=dev)
+                stm = {"i": 0}
+
+                def step_m():
+                    fb.gemv_fp8_multi_acc_fp32_gpu(mset[stm["i"] % n_buf], Vn, (M, N), mmode, batch=nb,
+                                                   out=outn)
+                    stm["i"] += 1
+                ms_m = time_calls(torch, step_m, n_it, 10)
+                extra[f"gemv_multi{nb}_{name}_16384x16384"] = {
+                    "us_per_call": round(ms_m * 1e3, 3), "matrix_GB/s": round(M * N / ms_m / 1e6, 1),
+                    "vs_single_calls": round(nb * single_ms / ms_m, 2)}
         del m4
         # the headline workload with FEATHER_GEMV_STATIC_MATRIX (weights promised static)
         st5 = {"i": 0}

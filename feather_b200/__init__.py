@@ -20,12 +20,13 @@ from .packers.fp8 import PackedFP8, pack_fp8_tensor, unpack_fp8_tensor
 from .routines.dot import (dot_fp8_acc_fp32_gpu, dot_fp8_e4m3_acc_fp32_gpu,
                            dot_fp8_e5m2_acc_fp32_gpu)
 from .routines.gemv import (gemv_fp8_acc_fp32_gpu, gemv_fp8_e4m3_acc_fp32_gpu,
-                            gemv_fp8_e5m2_acc_fp32_gpu, gemv_fp8_ret_packed_gpu)
+                            gemv_fp8_e5m2_acc_fp32_gpu, gemv_fp8_multi_acc_fp32_gpu,
+                            gemv_fp8_ret_packed_gpu)
 
 __version__ = "0.1.0"
 __all__ = ["pack_fp8_tensor", "unpack_fp8_tensor", "gemv", "dot", "PackedFP8", "device_status",
            "gemv_fp8_acc_fp32_gpu", "gemv_fp8_e5m2_acc_fp32_gpu", "gemv_fp8_e4m3_acc_fp32_gpu",
-           "gemv_fp8_ret_packed_gpu", "dot_fp8_acc_fp32_gpu", "dot_fp8_e5m2_acc_fp32_gpu", "dot_fp8_e4m3_acc_fp32_gpu"]
+           "gemv_fp8_ret_packed_gpu", "gemv_fp8_multi_acc_fp32_gpu", "dot_fp8_acc_fp32_gpu", "dot_fp8_e5m2_acc_fp32_gpu", "dot_fp8_e4m3_acc_fp32_gpu"]
 
 
 def _mode_of(mode, *operands) -> str:

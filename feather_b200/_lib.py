@@ -24,6 +24,7 @@ SYMBOLS = {
     "feather_decode_fp8": (_i32, [_vp, _vp, _i64, _i32, _i32, _vp]),
     "feather_relu_fp8": (_i32, [_vp, _vp, _i64, _i32, _vp]),
     "feather_gemv_fp8": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp]),
+    "feather_gemv_fp8_multi": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, ctypes.c_uint32, _vp]),
     "feather_gemv_fp8_packed": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _i32, _i32, ctypes.c_uint32, _vp]),
     "feather_gemv_fp8_packed_workspace_bytes": (_i64, [_i64, _i64]),
     "feather_gemv_fp8_sharded": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp, _vp, _i32, _i32,

@@ -10,6 +10,8 @@
 #include "dot_kernels.cuh"
 #include "fp8_codec.cuh"
 #include "gemv_kernels.cuh"
+#include "gemv_multi.cuh"
+#include "gemv_mma.cuh"
 #include "gemv_ring.cuh"
 
 namespace feather {
@@ -377,6 +379,92 @@ static int gemv_launch(const uint32_t* m, const uint32_t* v, float* out, long lo
                          : gemv_rows_launch<MODE, 1, 4, false>(m, v, out, M, N, s, out_code);
 }
 
+template <int MODE, int NB, bool EARLY>
+static int gemv_multi_launch(const uint32_t* m, const uint32_t* v, float* out, long long M,
+                             long long N, int B, cudaStream_t s) {
+    auto kernel = gemv_multi_kernel<MODE, NB, EARLY>;
+    static std::atomic<unsigned long long> configured{0};
+    if (int st = ensure_smem(kernel, gemv_multi_smem_bytes(kRowsTileCodes, NB), configured)) return st;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((M + 15) / 16));
+    cfg.blockDim = dim3(kRowsThreads);
+    cfg.dynamicSmemBytes = gemv_multi_smem_bytes((int)(N > kRowsTileCodes ? kRowsTileCodes : N), NB);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const uint4*>(m), v, out,
+                                             (int)M, (int)(N / 16), B);
+    return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
+}
+
+template <int MODE, bool EARLY>
+static int gemv_mma_launch(const uint32_t* m, const uint32_t* v, float* out, long long M, long long N,
+                           int B, cudaStream_t s) {
+    auto kernel = gemv_mma_kernel<MODE, EARLY>;
+    static std::atomic<unsigned long long> configured{0};
+    if (int st = ensure_smem(kernel, kMmaSmemBytes, configured)) return st;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((M + kMmaCtaRows - 1) / kMmaCtaRows));
+    cfg.blockDim = dim3(kMmaThreads);
+    cfg.dynamicSmemBytes = kMmaSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const uint4*>(m), v, out,
+                                             (int)M, (int)(N / 16), B);
+    return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
+}
+
+template <int MODE>
+static int gemv_multi_dispatch(const uint32_t* m, const uint32_t* v, float* out, long long M,
+                               long long N, int B, const DeviceInfo& dev, cudaStream_t s,
+                               bool static_matrix) {
+    const long long n_words = N / 4;
+    if ((N % 16) || !aligned(m, 16)) {  // ragged rows: one single-vector GEMV per vector
+        for (int b = 0; b < B; ++b)
+            if (int st = gemv_launch<MODE>(m, v + b * n_words, out + (long long)b * M, M, N, dev, s,
+                                           static_matrix))
+                return st;
+        return FEATHER_OK;
+    }
+    if (M >= (long long)kMmaCtaRows * dev.sm_count) {
+        // large matrices: tensor-core kernel, up to eight vectors per pass
+        for (int b0 = 0; b0 < B; b0 += kMmaVectors) {
+            const int nb = B - b0 < kMmaVectors ? B - b0 : kMmaVectors;
+            const uint32_t* vb = v + b0 * n_words;
+            float* ob = out + (long long)b0 * M;
+            int st;
+            if (nb == 1) st = gemv_launch<MODE>(m, vb, ob, M, N, dev, s, static_matrix);
+            else st = static_matrix ? gemv_mma_launch<MODE, true>(m, vb, ob, M, N, nb, s)
+                                    : gemv_mma_launch<MODE, false>(m, vb, ob, M, N, nb, s);
+            if (st) return st;
+        }
+        return FEATHER_OK;
+    }
+    for (int b0 = 0; b0 < B; b0 += 4) {  // up to four vectors per pass over the matrix
+        const int nb = B - b0 < 4 ? B - b0 : 4;
+        const uint32_t* vb = v + b0 * n_words;
+        float* ob = out + (long long)b0 * M;
+        int st;
+        if (nb == 1)
+            st = gemv_launch<MODE>(m, vb, ob, M, N, dev, s, static_matrix);
+        else if (nb == 2)
+            st = static_matrix ? gemv_multi_launch<MODE, 2, true>(m, vb, ob, M, N, nb, s)
+                               : gemv_multi_launch<MODE, 2, false>(m, vb, ob, M, N, nb, s);
+        else
+            st = static_matrix ? gemv_multi_launch<MODE, 4, true>(m, vb, ob, M, N, nb, s)
+                               : gemv_multi_launch<MODE, 4, false>(m, vb, ob, M, N, nb, s);
+        if (st) return st;
+    }
+    return FEATHER_OK;
+}
+
 // Decode (optionally through ReLU) n_elems codes: a grid of up to 16 CTAs per SM,
 // each thread walking words with four loads in flight.
 static int decode_launch(const uint32_t* src, float* dst, long long n_elems, int mode, bool ieee,
@@ -561,6 +649,27 @@ int feather_gemv_fp8_ex(const uint32_t* m, const uint32_t* v, float* out, int64_
     const bool static_matrix = (flags & FEATHER_GEMV_STATIC_MATRIX) != 0;
     return mode == FEATHER_MODE_E5M2 ? gemv_launch<kE5M2>(m, v, out, M, N, *dev, s, static_matrix)
                                      : gemv_launch<kE4M3>(m, v, out, M, N, *dev, s, static_matrix);
+}
+
+int feather_gemv_fp8_multi(const uint32_t* m, const uint32_t* v, float* out, int64_t M, int64_t N,
+                           int B, int mode, uint32_t flags, void* stream) {
+    if (flags & ~(uint32_t)FEATHER_GEMV_STATIC_MATRIX) return FEATHER_ERR_BAD_ARG;
+    if (M < 0 || N < 0 || (N & 3) || M > 0x7FFFFFFF || N > 0x7FFFFFFFll * 4 || B < 0 || B > 64)
+        return FEATHER_ERR_BAD_ARG;
+    if (mode != FEATHER_MODE_E5M2 && mode != FEATHER_MODE_E4M3) return FEATHER_ERR_MODE;
+    if (M == 0 || B == 0) return FEATHER_OK;
+    if (!out || (N > 0 && (!m || !v))) return FEATHER_ERR_BAD_ARG;
+    if (!aligned(m, 4) || !aligned(v, 4) || !aligned(out, 4)) return FEATHER_ERR_MISALIGNED;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (N == 0)
+        return cudaMemsetAsync(out, 0, sizeof(float) * (size_t)M * B, s) == cudaSuccess
+                   ? FEATHER_OK : FEATHER_ERR_LAUNCH;
+    const bool static_matrix = (flags & FEATHER_GEMV_STATIC_MATRIX) != 0;
+    return mode == FEATHER_MODE_E5M2
+               ? gemv_multi_dispatch<kE5M2>(m, v, out, M, N, B, *dev, s, static_matrix)
+               : gemv_multi_dispatch<kE4M3>(m, v, out, M, N, B, *dev, s, static_matrix);
 }
 
 int64_t feather_gemv_fp8_packed_workspace_bytes(int64_t M, int64_t N) {

@@ -16,7 +16,7 @@ from .. import _lib
 from ..packers.fp8 import as_words
 
 __all__ = ["gemv_fp8_acc_fp32_gpu", "gemv_fp8_e5m2_acc_fp32_gpu", "gemv_fp8_e4m3_acc_fp32_gpu",
-           "gemv_fp8_ret_packed_gpu"]
+           "gemv_fp8_ret_packed_gpu", "gemv_fp8_multi_acc_fp32_gpu"]
 
 
 def gemv_fp8_acc_fp32_gpu(m: torch.Tensor, v: torch.Tensor, m_shape, mode: str = "E5M2",
@@ -54,6 +54,53 @@ def gemv_fp8_ret_packed_gpu(m: torch.Tensor, v: torch.Tensor, m_shape, mode: str
         words = _gemv(m, v, m_shape, mode, out, 1 if static_matrix else 0,
                       out_mode_id=_lib.mode_id(out_mode), workspace=workspace)
         return words if out is not None else _tag(words, out_mode)
+
+
+def gemv_fp8_multi_acc_fp32_gpu(m: torch.Tensor, v: torch.Tensor, m_shape, mode: str = "E5M2",
+                                batch: int | None = None, out: torch.Tensor | None = None,
+                                static_matrix: bool = False) -> torch.Tensor:
+    """``out[b] = gemv(m, v[b])`` for ``batch`` packed vectors in ONE pass over
+    the matrix (``feather_gemv_fp8_multi``).  No reference counterpart: there
+    every vector is its own launch and re-reads the matrix.
+
+    ``v`` holds the vectors one after the other, ``N / 4`` words each -- what
+    ``pack_fp8_tensor`` returns for a ``(batch, N)`` tensor; ``batch`` defaults
+    to ``v.numel() // (N / 4)``.  Returns a float32 ``(batch, M)`` tensor."""
+    with torch._C.DisableTorchFunctionSubclass():
+        mode_id = _lib.mode_id(mode)
+        m = as_words(m, "m")
+        v = as_words(v, "v")
+        if len(m_shape) != 2:
+            raise ValueError("m_shape must be the unpacked (M, N) of the matrix")
+        M, N = int(m_shape[0]), int(m_shape[1])
+        if M < 0 or N < 0 or N % 4:
+            raise ValueError("N must be a non-negative multiple of 4: rows are whole packed words")
+        n_words = N // 4
+        if batch is None:
+            if n_words == 0 or v.numel() % n_words:
+                raise ValueError("v must hold a whole number of N/4-word vectors (or pass batch=)")
+            batch = v.numel() // n_words
+        batch = int(batch)
+        if not 0 <= batch <= 64:
+            raise ValueError("batch must be between 0 and 64")
+        if m.numel() < M * n_words:
+            raise ValueError(f"m holds {m.numel()} words, {M}x{N} needs {M * n_words}")
+        if v.numel() < batch * n_words:
+            raise ValueError(f"v holds {v.numel()} words, {batch} vectors of N={N} need {batch * n_words}")
+        if v.device != m.device:
+            raise ValueError("m and v must be on the same device")
+        if out is None:
+            out = torch.empty((batch, M), dtype=torch.float32, device=m.device)
+        elif (out.dtype != torch.float32 or out.numel() != batch * M or out.device != m.device
+              or not out.is_contiguous()):
+            raise ValueError("out must be a contiguous float32 tensor of batch * M elements on m's device")
+        if M and batch:
+            idx = m.device.index
+            with torch.cuda.device(idx):
+                _lib.check(_lib.load().feather_gemv_fp8_multi(
+                    m.data_ptr(), v.data_ptr(), out.data_ptr(), M, N, batch, mode_id,
+                    1 if static_matrix else 0, _lib.current_stream_ptr(idx)))
+        return out
 
 
 def _gemv(m, v, m_shape, mode, out, flags, out_mode_id=None, workspace=None):

@@ -129,6 +129,24 @@ int feather_gemv_fp8_ex(const uint32_t* m, const uint32_t* v, float* out, int64_
                         int mode, uint32_t flags, void* stream);
 
 /*
+ * GEMV against B vectors in one pass over the matrix:
+ *   out[b * M + r] = sum_j decode(m[r, j]) * decode(v[b * N/4 words + j])
+ * The reference multiplies one vector per launch (feather/routines/gemv.py:136,
+ * :187), so B right-hand sides read the matrix B times; here each 16-byte chunk
+ * of a row is loaded and decoded once for up to four vectors (B > 4 runs
+ * ceil(B / 4) passes).  Per vector the result is what feather_gemv_fp8 gives
+ * (the same bits where that call takes the warp-owned-rows kernel, otherwise
+ * the same sums in another order).
+ *   v    B packed vectors of N / 4 words, one after the other
+ *   out  B rows of M floats
+ *   B    0 .. 64; rows that are not whole 16-byte chunks (N % 16 != 0 or m not
+ *        16-byte aligned) fall back to one single-vector GEMV per vector
+ *   flags as feather_gemv_fp8_ex
+ */
+int feather_gemv_fp8_multi(const uint32_t* m, const uint32_t* v, float* out, int64_t M, int64_t N,
+                           int B, int mode, uint32_t flags, void* stream);
+
+/*
  * The GEMV with its result re-encoded to packed FP8: out_words receives
  * ceil(M / 4) words holding encode(out[0..M)) in `out_mode`, the tail padded
  * with zero codes -- exactly feather_encode_fp8 applied to feather_gemv_fp8's

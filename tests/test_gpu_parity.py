@@ -702,3 +702,56 @@ def test_relu_all_codes_ragged_and_large_vs_oracle(fb, golden, mode):
         relu(words[:2], 9, mode=mode)
     with pytest.raises(NotImplementedError):
         relu(words[:2], 8, mode="E3M4")
+
+
+# ------------------------------------------------------- multi-vector GEMV --
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("shape,batch", [((2048, 2048), 4), ((2046, 2048), 3), ((5632, 2048), 2),
+                                         ((37, 2064), 4), ((300, 40000), 4), ((4801, 8192), 4),
+                                         ((32000, 2048), 9), ((64, 16), 1), ((33, 20), 3), ((2048, 5632), 5),
+                                         ((9472, 4096), 8), ((9500, 8208), 5), ((9473, 2048), 2),
+                                         ((12000, 16400), 3), ((9472, 528), 11)])
+def test_gemv_multi_vs_oracle_and_single_gemv(fb, c_oracle, mode, shape, batch):
+    """B vectors in one pass: every out[b] against the f64 oracle, and against
+    the single-vector GEMV -- bit for bit where both take FP32-FMA kernels with
+    the same summation order, within rounding where the single call takes the
+    large-matrix kernel or the batch takes the tensor-core kernel (M >= 64 rows
+    per SM; its accumulation is the tensor core's)."""
+    M, N = shape
+    gen = torch.Generator(device="cuda").manual_seed(M + 7 * N + batch)
+    A = torch.randn(M, N, device="cuda", generator=gen, dtype=torch.float16)
+    V = torch.randn(batch, N, device="cuda", generator=gen, dtype=torch.float16)
+    mw, vw = fb.pack_fp8_tensor(A, mode), fb.pack_fp8_tensor(V, mode)
+    Y = fb.gemv_fp8_multi_acc_fp32_gpu(mw, vw, (M, N), mode)
+    assert Y.shape == (batch, M) and Y.dtype == torch.float32
+    host = lambda t: t.view(torch.int32).cpu().numpy().view(np.uint32)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    large = (M >= 32 * sms and N >= 4096) or (M >= 64 * sms and N % 16 == 0 and batch > 1)
+    for b in range(batch):
+        vb = vw[b * (N // 4):(b + 1) * (N // 4)]
+        single = fb.gemv_fp8_acc_fp32_gpu(mw, vb, (M, N), mode)
+        if large:
+            assert O.normalised_error(Y[b].cpu().numpy(), single.cpu().numpy()) < 1e-5
+        else:
+            assert torch.equal(Y[b], single)
+        ref = c_oracle.gemv(host(mw), host(vb), (M, N), mode, acc="f64")
+        assert O.normalised_error(Y[b].cpu().numpy(), ref) < 1e-5
+    out = torch.zeros(batch, M, device="cuda")
+    fb.gemv_fp8_multi_acc_fp32_gpu(mw, vw, (M, N), mode, batch=batch, out=out, static_matrix=True)
+    assert torch.equal(out, Y)
+
+
+def test_gemv_multi_rejects(fb):
+    w = torch.zeros(64, dtype=torch.int32, device="cuda")
+    assert fb.gemv_fp8_multi_acc_fp32_gpu(w, w, (4, 16), "E5M2", batch=0).shape == (0, 4)
+    with pytest.raises(ValueError):
+        fb.gemv_fp8_multi_acc_fp32_gpu(w, w[:6], (4, 16), "E5M2")            # not whole vectors
+    with pytest.raises(ValueError):
+        fb.gemv_fp8_multi_acc_fp32_gpu(w, w, (4, 16), "E5M2", batch=65)
+    with pytest.raises(ValueError):
+        fb.gemv_fp8_multi_acc_fp32_gpu(w, w[:8], (4, 16), "E5M2", batch=3)   # too few words
+    lib = fb._lib.load()
+    p = w.data_ptr()
+    assert lib.feather_gemv_fp8_multi(p, p, p, 4, 16, 2, 3, 0, None) == -3
+    assert lib.feather_gemv_fp8_multi(p, p, p, 4, 16, -1, 0, 0, None) == -1
+    assert lib.feather_gemv_fp8_multi(p, p, p, 4, 16, 2, 0, 2, None) == -1
