@@ -402,12 +402,25 @@ static int gemv_multi_launch(const uint32_t* m, const uint32_t* v, float* out, l
 
 template <int MODE, bool EARLY>
 static int gemv_mma_launch(const uint32_t* m, const uint32_t* v, float* out, long long M, long long N,
-                           int B, cudaStream_t s) {
+                           int B, const DeviceInfo& dev, cudaStream_t s) {
     auto kernel = gemv_mma_kernel<MODE, EARLY>;
     static std::atomic<unsigned long long> configured{0};
     if (int st = ensure_smem(kernel, kMmaSmemBytes, configured)) return st;
+    // 16-row groups a CTA works on at a time: the count (at most 8, two warps each)
+    // that leaves the fewest idle SM-slots over the waves of the persistent grid;
+    // ties go to the larger count (more of the matrix in flight per SM)
+    const long long groups = (M + 15) / 16;
+    int gpc = 1;
+    double best = 0.0;
+    for (int c = 1; c <= kMmaMaxGroups; ++c) {
+        const long long passes = (groups + c - 1) / c;
+        const long long waves = (passes + dev.sm_count - 1) / dev.sm_count;
+        const double eff = (double)groups / (double)(waves * dev.sm_count * c);
+        if (eff >= best - 1e-9) { best = eff; gpc = c; }
+    }
+    const long long passes = (groups + gpc - 1) / gpc;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((M + kMmaCtaRows - 1) / kMmaCtaRows));
+    cfg.gridDim = dim3((unsigned)(passes < dev.sm_count ? passes : dev.sm_count));
     cfg.blockDim = dim3(kMmaThreads);
     cfg.dynamicSmemBytes = kMmaSmemBytes;
     cfg.stream = s;
@@ -417,7 +430,7 @@ static int gemv_mma_launch(const uint32_t* m, const uint32_t* v, float* out, lon
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const uint4*>(m), v, out,
-                                             (int)M, (int)(N / 16), B);
+                                             (int)M, (int)(N / 16), B, gpc);
     return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
 }
 
@@ -433,7 +446,7 @@ static int gemv_multi_dispatch(const uint32_t* m, const uint32_t* v, float* out,
                 return st;
         return FEATHER_OK;
     }
-    if (M >= (long long)kMmaCtaRows * dev.sm_count) {
+    if (M >= 64ll * dev.sm_count) {
         // large matrices: tensor-core kernel, up to eight vectors per pass
         for (int b0 = 0; b0 < B; b0 += kMmaVectors) {
             const int nb = B - b0 < kMmaVectors ? B - b0 : kMmaVectors;
@@ -441,8 +454,8 @@ static int gemv_multi_dispatch(const uint32_t* m, const uint32_t* v, float* out,
             float* ob = out + (long long)b0 * M;
             int st;
             if (nb == 1) st = gemv_launch<MODE>(m, vb, ob, M, N, dev, s, static_matrix);
-            else st = static_matrix ? gemv_mma_launch<MODE, true>(m, vb, ob, M, N, nb, s)
-                                    : gemv_mma_launch<MODE, false>(m, vb, ob, M, N, nb, s);
+            else st = static_matrix ? gemv_mma_launch<MODE, true>(m, vb, ob, M, N, nb, dev, s)
+                                    : gemv_mma_launch<MODE, false>(m, vb, ob, M, N, nb, dev, s);
             if (st) return st;
         }
         return FEATHER_OK;

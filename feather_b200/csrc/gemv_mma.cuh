@@ -16,26 +16,38 @@
 // and adds them in FP32 at the end, which keeps the result within the tolerance
 // the single-vector kernels are held to.
 //
-// Mapping.  A CTA owns 64 rows: warp w works on rows 16 * (w & 3) .. + 15 and on
-// every other 64-code unit of them (w >> 2 picks even or odd units).  In a unit,
-// lane (g, t) = (lane >> 2, lane & 3) loads the 16-byte chunk t of rows g and
-// g + 8; word s of those chunks, decoded, is exactly the A fragment of the s-th
-// mma (k slots 2t, 2t+1 and 2t+8, 2t+9 are the word's two FP16 pairs), and the
-// B fragment is the same word of vector g, read from shared memory where the
-// vectors' tiles sit decoded in the same pairing.  Any one-to-one assignment of
-// codes to k slots is valid as long as A and B agree, so nothing is shuffled.
+// Mapping.  A CTA works on up to 8 groups of 16 rows at a time, two warps per
+// group: warp w takes group w >> 1 and every other 64-code unit of its rows
+// (w & 1 picks even or odd units).  In a unit, lane (g, t) = (lane >> 2,
+// lane & 3) owns the 16-byte chunk t of rows g and g + 8; word s of those
+// chunks, decoded, is exactly the A fragment of the s-th mma (k slots 2t, 2t+1
+// and 2t+8, 2t+9 are the word's two FP16 pairs), and the B fragment is the same
+// word of vector g, read from shared memory where the vectors' tiles sit
+// decoded in the same pairing.  Any one-to-one assignment of codes to k slots is
+// valid as long as A and B agree, so nothing is shuffled.
+//
+// Streaming.  Every lane copies its own chunks with cp.async (16 bytes, L2 only)
+// into a lane-private slot of a per-warp ring, kMmaDepth units ahead, and reads
+// them back itself: no registers are held by loads in flight, no lane reads
+// another's data, so the only synchronisation is cp.async.wait_group -- and a
+// CTA (one per SM, sixteen warps) keeps up to 128 KiB of the matrix in flight.
+// The grid is persistent; groups per CTA are chosen so that the waves are full.
 #pragma once
 #include "gemv_kernels.cuh"
 
 namespace feather {
 
-constexpr int kMmaThreads = 256;
-constexpr int kMmaCtaRows = 64;
+constexpr int kMmaWarps = 16;
+constexpr int kMmaThreads = kMmaWarps * 32;
+constexpr int kMmaMaxGroups = kMmaWarps / 2;              // 16-row groups a CTA works on at a time
 constexpr int kMmaVectors = 8;
-constexpr int kMmaTileCodes = 4096;                       // codes of each vector resident at a time
+constexpr int kMmaTileCodes = 2048;                       // codes of each vector in a tile (two tiles resident)
 constexpr int kMmaVecStride = kMmaTileCodes * 2 + 16;     // bytes; the 16 spread the vectors over the banks
-constexpr int kMmaSmemBytes = kMmaVectors * kMmaVecStride;
-constexpr int kMmaUnroll = 4;                             // 64-code units in flight per warp
+constexpr int kMmaTileBytes = 8 * kMmaVecStride;          // one tile of all eight vectors
+constexpr int kMmaDepth = 8;                              // units a warp keeps in flight
+constexpr int kMmaSlotBytes = 2 * 32 * 16;                // a unit of a warp: two rows' chunks per lane
+constexpr int kMmaRingOffset = 2 * kMmaTileBytes;
+constexpr int kMmaSmemBytes = kMmaRingOffset + kMmaWarps * kMmaDepth * kMmaSlotBytes;
 
 __device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                             uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -45,121 +57,159 @@ __device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Grid: one CTA per 64 rows.  v: B vectors of n16 * 4 words, one after the
-// other; out: B rows of M floats.  Shared memory: kMmaSmemBytes.
+// 16 bytes global -> shared, not through L1; n_src = 0 writes zeros instead.
+__device__ __forceinline__ void cp_async_16(uint32_t smem_dst, const void* src, int n_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(smem_dst), "l"(src), "r"(n_src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+
+// Grid: any size up to the number of passes; pass p covers row groups
+// [p * gpc, (p + 1) * gpc), CTAs take passes blockIdx.x, blockIdx.x + gridDim.x, ...
+// v: B vectors of n16 * 4 words, one after the other; out: B rows of M floats.
 template <int MODE, bool EARLY>
-__global__ void __launch_bounds__(kMmaThreads, 2)
+__global__ void __launch_bounds__(kMmaThreads, 1)
 gemv_mma_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
-                float* __restrict__ out, int M, int n16, int B) {
+                float* __restrict__ out, int M, int n16, int B, int gpc) {
     extern __shared__ __align__(16) unsigned char mma_smem[];
-    __shared__ float part[4][16][kMmaVectors];            // the odd-unit warps' sums
-    constexpr int U = kMmaUnroll;
+    __shared__ float part[kMmaMaxGroups][16][kMmaVectors];    // the odd-unit warps' sums
+    constexpr int D = kMmaDepth;
     constexpr int kTileChunks = kMmaTileCodes / 16;
+    static_assert(kTileChunks % 16 == 0, "a tile is an even number of units for either warp of a group");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int group = warp & 3, split = warp >> 2;
-    const int row_a = (int)blockIdx.x * kMmaCtaRows + group * 16 + g;
-    const uint4* ra = m + (size_t)min(row_a, M - 1) * n16;      // rows past M: duplicates, never stored
-    const uint4* rb = m + (size_t)min(row_a + 8, M - 1) * n16;
+    const int group = warp >> 1, split = warp & 1;
+    const bool working = group < gpc;                         // warp-uniform
+    const int n_groups = (M + 15) / 16;
+    const int n_pass = (n_groups + gpc - 1) / gpc;
+    // lane-private ring slots: [warp][slot][row a | row b][lane]
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(mma_smem + kMmaRingOffset) +
+                          warp * (D * kMmaSlotBytes) + lane * 16;
+    const unsigned char* ring_ptr = mma_smem + kMmaRingOffset + warp * (D * kMmaSlotBytes) + lane * 16;
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    // unit k of this warp = global 64-code unit 2k + split = chunks 4 * (2k + split) .. + 3
-    uint4 buf_a[U], buf_b[U];
-    auto issue = [&](int slot, int k) {
-        const int c = 4 * (2 * k + split) + t;
-        const bool on = c < n16;
-        buf_a[slot] = on ? ldg_stream(ra + c) : make_uint4(0, 0, 0, 0);
-        buf_b[slot] = on ? ldg_stream(rb + c) : make_uint4(0, 0, 0, 0);
-    };
-    if (EARLY) {
+    bool waited = false;
+    for (int pass = blockIdx.x; pass < n_pass; pass += gridDim.x) {
+        const int row_a = (pass * gpc + group) * 16 + g;
+        const uint4* ra = m + (size_t)min(row_a, M - 1) * n16;      // rows past M: duplicates, never stored
+        const uint4* rb = m + (size_t)min(row_a + 8, M - 1) * n16;
+        // unit k of this warp = chunks 4 * (2k + split) .. + 3 of its rows; one commit group per unit
+        auto issue = [&](int k) {
+            if (working) {
+                const int c = 4 * (2 * k + split) + t;
+                const int n_src = c < n16 ? 16 : 0;
+                const int cc = min(c, n16 - 1);
+                const uint32_t slot = ring + (k % D) * kMmaSlotBytes;
+                cp_async_16(slot, ra + cc, n_src);
+                cp_async_16(slot + 512, rb + cc, n_src);
+            }
+            cp_async_commit();
+        };
+        if (EARLY || waited) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) issue(u, u);
-    }
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (!EARLY) {
+            for (int k = 0; k < D - 1; ++k) issue(k);
+        }
+        if (!waited) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            waited = true;
+            if (!EARLY) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) issue(u, u);
-    }
-
-    float acc[8][4];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-
-    // A batch is U = 4 units of this warp = 32 consecutive chunks of the row for
-    // the two splits together, so the tile (256 chunks) is a whole number of
-    // batches and a batch never straddles tiles.  Chunks past the row end are
-    // zero codes against zero vector values.
-    static_assert(U == 4 && kTileChunks % 32 == 0, "batches of 32 chunks must tile the vector tile");
-    const unsigned char* vec_g = mma_smem + (size_t)g * kMmaVecStride;
-    for (int t0 = 0; t0 < n16; t0 += kTileChunks) {
-        const int tile_chunks = min(kTileChunks, n16 - t0);
-        const int fill_chunks = (tile_chunks + 31) / 32 * 32;   // whole batches
-        if (t0 > 0) __syncthreads();
-        {   // stage the tile of all eight vectors as FP16 pairs, word after word;
-            // vectors B..7 and the chunks past the row end are zero
-            // (a thread takes the same word of all eight vectors: eight loads in flight)
-            const int w_valid = tile_chunks * 4, w_fill = fill_chunks * 4;
-            const uint32_t* src = v + (size_t)t0 * 4;
-            for (int wl = threadIdx.x; wl < w_fill; wl += kMmaThreads) {
-                uint32_t w[kMmaVectors];
-#pragma unroll
-                for (int b = 0; b < kMmaVectors; ++b)
-                    w[b] = (b < B && wl < w_valid) ? __ldg(src + (size_t)b * n16 * 4 + wl) : 0u;
-#pragma unroll
-                for (int b = 0; b < kMmaVectors; ++b) {
-                    uint32_t lo, hi;
-                    decode_word_h2<MODE>(w[b], lo, hi);
-                    reinterpret_cast<uint2*>(mma_smem + (size_t)b * kMmaVecStride)[wl] = make_uint2(lo, hi);
-                }
+                for (int k = 0; k < D - 1; ++k) issue(k);
             }
         }
-        __syncthreads();
-        const int k_end = t0 / 8 + fill_chunks / 8;           // this warp's units: k in [t0/8, k_end)
-        for (int k = t0 / 8; k < k_end; k += U) {
+
+        float acc[8][4];
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const uint4 xa = buf_a[u], xb = buf_b[u];
-                issue(u, k + u + U);                          // refill the slot one batch ahead
-                const int cl = 4 * (2 * (k + u) + split) + t - t0;   // chunk inside the tile
+        for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+        // Vector tiles are double-buffered and staged in two halves around the
+        // compute of the tile before: a thread owns word threadIdx.x of every
+        // vector's tile, loads the next tile's eight words before it computes and
+        // decodes them into the other buffer afterwards -- one barrier per tile and
+        // no load latency in front of it.  Vectors B..7 and chunks past the row end
+        // are zero.
+        static_assert(kMmaTileCodes / 4 == kMmaThreads, "one word of each vector's tile per thread");
+        uint32_t w[kMmaVectors];
+        auto fetch = [&](int t0) {
+            const int tile_chunks = min(kTileChunks, n16 - t0);
+            const bool on = t0 < n16 && (int)threadIdx.x < tile_chunks * 4;
+#pragma unroll
+            for (int b = 0; b < kMmaVectors; ++b)
+                w[b] = (on && b < B) ? __ldg(v + ((size_t)b * n16 + t0) * 4 + threadIdx.x) : 0u;
+        };
+        __syncthreads();                 // the previous pass has let go of both buffers
+        fetch(0);
+        for (int t0 = 0, tile = 0; t0 < n16; t0 += kTileChunks, ++tile) {
+            const int tile_chunks = min(kTileChunks, n16 - t0);
+            const int fill_chunks = (tile_chunks + 15) / 16 * 16;   // an even number of units per warp
+            unsigned char* tile_smem = mma_smem + (tile & 1) * kMmaTileBytes;
+#pragma unroll
+            for (int b = 0; b < kMmaVectors; ++b) {
+                uint32_t lo, hi;
+                decode_word_h2<MODE>(w[b], lo, hi);
+                reinterpret_cast<uint2*>(tile_smem + (size_t)b * kMmaVecStride)[threadIdx.x] = make_uint2(lo, hi);
+            }
+            __syncthreads();             // tile staged; everyone is done with the tile before the last
+            fetch(t0 + kTileChunks);     // in flight while this tile is computed
+            const unsigned char* vec_g = tile_smem + (size_t)g * kMmaVecStride;
+            if (!working) continue;
+            // this warp's units inside the tile: k in [t0 / 8, t0 / 8 + fill_chunks / 8)
+            const int k_end = t0 / 8 + fill_chunks / 8;
+            auto step = [&](int k, float (&a)[8][4], int set) {     // set: compile-time 0 or 4
+                issue(k + D - 1);                                   // into the slot read one step ago
+                cp_async_wait<D - 1>();                             // unit k has landed
+                const unsigned char* slot = ring_ptr + (k % D) * kMmaSlotBytes;
+                const uint4 xa = *reinterpret_cast<const uint4*>(slot);
+                const uint4 xb = *reinterpret_cast<const uint4*>(slot + 512);
+                const int cl = 4 * (2 * k + split) + t - t0;         // chunk inside the tile
                 const uint4 q0 = *reinterpret_cast<const uint4*>(vec_g + (size_t)cl * 32);
                 const uint4 q1 = *reinterpret_cast<const uint4*>(vec_g + (size_t)cl * 32 + 16);
                 uint32_t al, ah, bl, bh;
                 decode_word_h2<MODE>(xa.x, al, ah);
                 decode_word_h2<MODE>(xb.x, bl, bh);
-                mma_16x8x16(acc[(u & 1) * 4 + 0], al, bl, ah, bh, q0.x, q0.y);
+                mma_16x8x16(a[set + 0], al, bl, ah, bh, q0.x, q0.y);
                 decode_word_h2<MODE>(xa.y, al, ah);
                 decode_word_h2<MODE>(xb.y, bl, bh);
-                mma_16x8x16(acc[(u & 1) * 4 + 1], al, bl, ah, bh, q0.z, q0.w);
+                mma_16x8x16(a[set + 1], al, bl, ah, bh, q0.z, q0.w);
                 decode_word_h2<MODE>(xa.z, al, ah);
                 decode_word_h2<MODE>(xb.z, bl, bh);
-                mma_16x8x16(acc[(u & 1) * 4 + 2], al, bl, ah, bh, q1.x, q1.y);
+                mma_16x8x16(a[set + 2], al, bl, ah, bh, q1.x, q1.y);
                 decode_word_h2<MODE>(xa.w, al, ah);
                 decode_word_h2<MODE>(xb.w, bl, bh);
-                mma_16x8x16(acc[(u & 1) * 4 + 3], al, bl, ah, bh, q1.z, q1.w);
+                mma_16x8x16(a[set + 3], al, bl, ah, bh, q1.z, q1.w);
+            };
+            for (int k = t0 / 8; k < k_end; k += 2) {               // an even number of units per tile
+                step(k, acc, 0);
+                step(k + 1, acc, 4);
+            }
+        }
+        cp_async_wait<0>();   // only zero-fill copies past the row end are left; the ring is free again
+
+        // accumulator sets in fixed order, then the two halves of the row
+        float d[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            d[i] = ((acc[0][i] + acc[1][i]) + (acc[2][i] + acc[3][i])) +
+                   ((acc[4][i] + acc[5][i]) + (acc[6][i] + acc[7][i]));
+        if (working && split == 1) {
+            part[group][g][2 * t] = d[0];
+            part[group][g][2 * t + 1] = d[1];
+            part[group][g + 8][2 * t] = d[2];
+            part[group][g + 8][2 * t + 1] = d[3];
+        }
+        __syncthreads();
+        if (working && split == 0 && pass * gpc + group < n_groups) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int row = row_a + (i >> 1) * 8, b = 2 * t + (i & 1);
+                if (row < M && b < B)
+                    out[(size_t)b * M + row] = d[i] + part[group][g + (i >> 1) * 8][b];
             }
         }
     }
-    // accumulator sets in fixed order, then the two halves of the row
-    float d[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-        d[i] = ((acc[0][i] + acc[1][i]) + (acc[2][i] + acc[3][i])) +
-               ((acc[4][i] + acc[5][i]) + (acc[6][i] + acc[7][i]));
-    if (split == 1) {
-        part[group][g][2 * t] = d[0];
-        part[group][g][2 * t + 1] = d[1];
-        part[group][g + 8][2 * t] = d[2];
-        part[group][g + 8][2 * t + 1] = d[3];
-    }
-    __syncthreads();
-    if (split == 0) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int row = row_a + (i >> 1) * 8, b = 2 * t + (i & 1);
-            if (row < M && b < B)
-                out[(size_t)b * M + row] = d[i] + part[group][g + (i >> 1) * 8][b];
-        }
-    }
+    if (!waited) asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 }  // namespace feather

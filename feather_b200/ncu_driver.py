@@ -25,7 +25,9 @@ def _codes(n_words: int, seed: int) -> torch.Tensor:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", choices=("gemv", "dot", "encode", "decode"), default="gemv")
+    ap.add_argument("--op", choices=("gemv", "dot", "encode", "decode", "relu", "multi", "packed"),
+                    default="gemv")
+    ap.add_argument("--batch", type=int, default=8, help="vectors per call for --op multi")
     ap.add_argument("--mode", choices=("E5M2", "E4M3"), default="E5M2")
     ap.add_argument("--M", type=int, default=16384)
     ap.add_argument("--N", type=int, default=16384)
@@ -48,6 +50,24 @@ def main() -> None:
         xs = [torch.randn(M, N, device="cuda", generator=g, dtype=torch.float16) for _ in range(2)]
         call = lambda i: fb.pack_fp8_tensor(xs[i % 2], a.mode)
         nbytes = 3 * M * N
+    elif a.op == "multi":
+        mats = [_codes(M * N // 4, s) for s in (1, 2)]
+        v = _codes(a.batch * N // 4, 3)
+        out = torch.empty(a.batch, M, dtype=torch.float32, device="cuda")
+        call = lambda i: fb.gemv_fp8_multi_acc_fp32_gpu(mats[i % 2], v, (M, N), a.mode, batch=a.batch, out=out)
+        nbytes = M * N + a.batch * (N + 4 * M)
+    elif a.op == "packed":
+        mats = [_codes(M * N // 4, s) for s in (1, 2)]
+        v = _codes(N // 4, 3)
+        out = torch.empty((M + 3) // 4, dtype=torch.uint32, device="cuda")
+        call = lambda i: fb.gemv_fp8_ret_packed_gpu(mats[i % 2], v, (M, N), a.mode, out=out)
+        nbytes = M * N + N + M
+    elif a.op == "relu":
+        from feather_b200.routines.activations import relu1d_fp8_ret_fp32_feather_gpu as relu
+        ws = [_codes(M * N // 4, s) for s in (1, 2)]
+        out = torch.empty(M * N, dtype=torch.float32, device="cuda")
+        call = lambda i: relu(ws[i % 2], M * N, mode=a.mode, out=out)
+        nbytes = 5 * M * N
     else:
         ws = [_codes(M * N // 4, s) for s in (1, 2)]
         call = lambda i: fb.unpack_fp8_tensor(ws[i % 2], a.mode)
