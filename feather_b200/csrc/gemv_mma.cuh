@@ -17,19 +17,22 @@
 // the single-vector kernels are held to.
 //
 // Mapping.  A CTA works on up to 8 groups of 16 rows at a time, two warps per
-// group: warp w takes group w >> 1 and every other 64-code unit of its rows
-// (w & 1 picks even or odd units).  In a unit, lane (g, t) = (lane >> 2,
-// lane & 3) owns the 16-byte chunk t of rows g and g + 8; word s of those
-// chunks, decoded, is exactly the A fragment of the s-th mma (k slots 2t, 2t+1
-// and 2t+8, 2t+9 are the word's two FP16 pairs), and the B fragment is the same
-// word of vector g, read from shared memory where the vectors' tiles sit
-// decoded in the same pairing.  Any one-to-one assignment of codes to k slots is
-// valid as long as A and B agree, so nothing is shuffled.
+// group: warp w takes group w >> 1 and every other 128-code unit of its rows
+// (w & 1 picks even or odd units).  For the mma, lane (g, t) = (lane >> 2,
+// lane & 3) supplies rows g and g + 8: word s of their 16-byte chunk t (and of
+// chunk 4 + t for the second half of the unit), decoded, is exactly the A
+// fragment of one mma (k slots 2t, 2t+1 and 2t+8, 2t+9 are the word's two FP16
+// pairs), and the B fragment is the same word of vector g, read from shared
+// memory where the vectors' tiles sit decoded in the same pairing.  Any
+// one-to-one assignment of codes to k slots is valid as long as A and B agree,
+// so nothing is shuffled.
 //
-// Streaming.  Every lane copies its own chunks with cp.async (16 bytes, L2 only)
-// into a lane-private slot of a per-warp ring, kMmaDepth units ahead, and reads
-// them back itself: no registers are held by loads in flight, no lane reads
-// another's data, so the only synchronisation is cp.async.wait_group -- and a
+// Streaming.  A warp copies a unit with four cp.async instructions (16 bytes per
+// lane, L2 only; eight lanes cover the 128 bytes of one row, so every request is
+// a whole line) into a slot of its own ring, kMmaDepth units ahead, and its lanes
+// read their fragments back from the slot (rows XOR-swizzled by parity so the
+// quarter-warps do not collide on banks): no registers are held by loads in
+// flight and the only synchronisation is cp.async.wait_group + __syncwarp -- a
 // CTA (one per SM, sixteen warps) keeps up to 128 KiB of the matrix in flight.
 // The grid is persistent; groups per CTA are chosen so that the waves are full.
 #pragma once
@@ -44,8 +47,8 @@ constexpr int kMmaVectors = 8;
 constexpr int kMmaTileCodes = 2048;                       // codes of each vector in a tile (two tiles resident)
 constexpr int kMmaVecStride = kMmaTileCodes * 2 + 16;     // bytes; the 16 spread the vectors over the banks
 constexpr int kMmaTileBytes = 8 * kMmaVecStride;          // one tile of all eight vectors
-constexpr int kMmaDepth = 8;                              // units a warp keeps in flight
-constexpr int kMmaSlotBytes = 2 * 32 * 16;                // a unit of a warp: two rows' chunks per lane
+constexpr int kMmaDepth = 4;                              // units a warp keeps in flight
+constexpr int kMmaSlotBytes = 16 * 128;                   // a unit of a warp: 128 bytes of each of its 16 rows
 constexpr int kMmaRingOffset = 2 * kMmaTileBytes;
 constexpr int kMmaSmemBytes = kMmaRingOffset + kMmaWarps * kMmaDepth * kMmaSlotBytes;
 
@@ -77,46 +80,54 @@ gemv_mma_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
     __shared__ float part[kMmaMaxGroups][16][kMmaVectors];    // the odd-unit warps' sums
     constexpr int D = kMmaDepth;
     constexpr int kTileChunks = kMmaTileCodes / 16;
-    static_assert(kTileChunks % 16 == 0, "a tile is an even number of units for either warp of a group");
+    static_assert(kTileChunks % 16 == 0, "a tile is a whole number of unit pairs");
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int group = warp >> 1, split = warp & 1;
     const bool working = group < gpc;                         // warp-uniform
     const int n_groups = (M + 15) / 16;
     const int n_pass = (n_groups + gpc - 1) / gpc;
-    // lane-private ring slots: [warp][slot][row a | row b][lane]
-    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(mma_smem + kMmaRingOffset) +
-                          warp * (D * kMmaSlotBytes) + lane * 16;
-    const unsigned char* ring_ptr = mma_smem + kMmaRingOffset + warp * (D * kMmaSlotBytes) + lane * 16;
+    // the warp's ring: [slot][row 0..15][128 bytes, chunk c of row r at c ^ 4 * (r & 1)]
+    unsigned char* ring_ptr = mma_smem + kMmaRingOffset + warp * (D * kMmaSlotBytes);
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(ring_ptr);
+    // copy role: this lane moves chunk lane & 7 of rows (lane >> 3) + 0, 4, 8, 12
+    const int cp_row = lane >> 3, cp_chunk = lane & 7;
+    const uint32_t cp_dst = cp_row * 128 + ((cp_chunk ^ ((cp_row & 1) << 2)) << 4);   // + 512 per 4 rows
+    // fragment role: chunks t (first half of the unit) and 4 + t (second half) of rows
+    // g and g + 8, which have the same parity and so the same swizzle
+    const int frag_off0 = g * 128 + (((0 + t) ^ ((g & 1) << 2)) << 4);
+    const int frag_off1 = g * 128 + (((4 + t) ^ ((g & 1) << 2)) << 4);
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     bool waited = false;
     for (int pass = blockIdx.x; pass < n_pass; pass += gridDim.x) {
-        const int row_a = (pass * gpc + group) * 16 + g;
-        const uint4* ra = m + (size_t)min(row_a, M - 1) * n16;      // rows past M: duplicates, never stored
-        const uint4* rb = m + (size_t)min(row_a + 8, M - 1) * n16;
-        // unit k of this warp = chunks 4 * (2k + split) .. + 3 of its rows; one commit group per unit
+        const int row0 = (pass * gpc + group) * 16;
+        const int row_a = row0 + g;
+        const uint4* cp_src = m + (size_t)min(row0 + cp_row, M - 1) * n16;
+        // unit k of this warp = chunks 8 * (2k + split) .. + 7 of its rows; one commit
+        // group per unit.  Rows past M and chunks past the row end are zero-filled.
         auto issue = [&](int k) {
             if (working) {
-                const int c = 4 * (2 * k + split) + t;
-                const int n_src = c < n16 ? 16 : 0;
-                const int cc = min(c, n16 - 1);
-                const uint32_t slot = ring + (k % D) * kMmaSlotBytes;
-                cp_async_16(slot, ra + cc, n_src);
-                cp_async_16(slot + 512, rb + cc, n_src);
+                const int c = 8 * (2 * k + split) + cp_chunk;
+                const uint32_t slot = ring + (k % D) * kMmaSlotBytes + cp_dst;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const bool on = c < n16 && row0 + cp_row + 4 * i < M;
+                    cp_async_16(slot + i * 512, on ? cp_src + (size_t)i * 4 * n16 + c : m, on ? 16 : 0);
+                }
             }
             cp_async_commit();
         };
         if (EARLY || waited) {
 #pragma unroll
-            for (int k = 0; k < D - 1; ++k) issue(k);
+            for (int k = 0; k < D; ++k) issue(k);
         }
         if (!waited) {
             asm volatile("griddepcontrol.wait;" ::: "memory");
             waited = true;
             if (!EARLY) {
 #pragma unroll
-                for (int k = 0; k < D - 1; ++k) issue(k);
+                for (int k = 0; k < D; ++k) issue(k);
             }
         }
 
@@ -143,7 +154,7 @@ gemv_mma_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
         fetch(0);
         for (int t0 = 0, tile = 0; t0 < n16; t0 += kTileChunks, ++tile) {
             const int tile_chunks = min(kTileChunks, n16 - t0);
-            const int fill_chunks = (tile_chunks + 15) / 16 * 16;   // an even number of units per warp
+            const int fill_chunks = (tile_chunks + 15) / 16 * 16;   // whole units for both warps of a group
             unsigned char* tile_smem = mma_smem + (tile & 1) * kMmaTileBytes;
 #pragma unroll
             for (int b = 0; b < kMmaVectors; ++b) {
@@ -155,34 +166,39 @@ gemv_mma_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
             fetch(t0 + kTileChunks);     // in flight while this tile is computed
             const unsigned char* vec_g = tile_smem + (size_t)g * kMmaVecStride;
             if (!working) continue;
-            // this warp's units inside the tile: k in [t0 / 8, t0 / 8 + fill_chunks / 8)
-            const int k_end = t0 / 8 + fill_chunks / 8;
-            auto step = [&](int k, float (&a)[8][4], int set) {     // set: compile-time 0 or 4
-                issue(k + D - 1);                                   // into the slot read one step ago
-                cp_async_wait<D - 1>();                             // unit k has landed
+            // this warp's units inside the tile: k in [t0 / 16, t0 / 16 + fill_chunks / 16)
+            const int k_end = t0 / 16 + fill_chunks / 16;
+            for (int k = t0 / 16; k < k_end; ++k) {
+                cp_async_wait<D - 1>();                             // this lane's part of unit k has landed
+                __syncwarp();                                       // ... and everybody else's
                 const unsigned char* slot = ring_ptr + (k % D) * kMmaSlotBytes;
-                const uint4 xa = *reinterpret_cast<const uint4*>(slot);
-                const uint4 xb = *reinterpret_cast<const uint4*>(slot + 512);
-                const int cl = 4 * (2 * k + split) + t - t0;         // chunk inside the tile
-                const uint4 q0 = *reinterpret_cast<const uint4*>(vec_g + (size_t)cl * 32);
-                const uint4 q1 = *reinterpret_cast<const uint4*>(vec_g + (size_t)cl * 32 + 16);
-                uint32_t al, ah, bl, bh;
-                decode_word_h2<MODE>(xa.x, al, ah);
-                decode_word_h2<MODE>(xb.x, bl, bh);
-                mma_16x8x16(a[set + 0], al, bl, ah, bh, q0.x, q0.y);
-                decode_word_h2<MODE>(xa.y, al, ah);
-                decode_word_h2<MODE>(xb.y, bl, bh);
-                mma_16x8x16(a[set + 1], al, bl, ah, bh, q0.z, q0.w);
-                decode_word_h2<MODE>(xa.z, al, ah);
-                decode_word_h2<MODE>(xb.z, bl, bh);
-                mma_16x8x16(a[set + 2], al, bl, ah, bh, q1.x, q1.y);
-                decode_word_h2<MODE>(xa.w, al, ah);
-                decode_word_h2<MODE>(xb.w, bl, bh);
-                mma_16x8x16(a[set + 3], al, bl, ah, bh, q1.z, q1.w);
-            };
-            for (int k = t0 / 8; k < k_end; k += 2) {               // an even number of units per tile
-                step(k, acc, 0);
-                step(k + 1, acc, 4);
+                uint4 xa[2], xb[2];
+                xa[0] = *reinterpret_cast<const uint4*>(slot + frag_off0);
+                xb[0] = *reinterpret_cast<const uint4*>(slot + frag_off0 + 8 * 128);
+                xa[1] = *reinterpret_cast<const uint4*>(slot + frag_off1);
+                xb[1] = *reinterpret_cast<const uint4*>(slot + frag_off1 + 8 * 128);
+                __syncwarp();                                       // the slot is read: refill it
+                issue(k + D);
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int cl = 8 * (2 * k + split) + 4 * u + t - t0;   // chunk inside the tile
+                    const uint4 q0 = *reinterpret_cast<const uint4*>(vec_g + (size_t)cl * 32);
+                    const uint4 q1 = *reinterpret_cast<const uint4*>(vec_g + (size_t)cl * 32 + 16);
+                    float (*a)[4] = acc + 4 * u;
+                    uint32_t al, ah, bl, bh;
+                    decode_word_h2<MODE>(xa[u].x, al, ah);
+                    decode_word_h2<MODE>(xb[u].x, bl, bh);
+                    mma_16x8x16(a[0], al, bl, ah, bh, q0.x, q0.y);
+                    decode_word_h2<MODE>(xa[u].y, al, ah);
+                    decode_word_h2<MODE>(xb[u].y, bl, bh);
+                    mma_16x8x16(a[1], al, bl, ah, bh, q0.z, q0.w);
+                    decode_word_h2<MODE>(xa[u].z, al, ah);
+                    decode_word_h2<MODE>(xb[u].z, bl, bh);
+                    mma_16x8x16(a[2], al, bl, ah, bh, q1.x, q1.y);
+                    decode_word_h2<MODE>(xa[u].w, al, ah);
+                    decode_word_h2<MODE>(xb[u].w, bl, bh);
+                    mma_16x8x16(a[3], al, bl, ah, bh, q1.z, q1.w);
+                }
             }
         }
         cp_async_wait<0>();   // only zero-fill copies past the row end are left; the ring is free again
