@@ -406,6 +406,8 @@ static int gemv_mma_launch(const uint32_t* m, const uint32_t* v, float* out, lon
     auto kernel = gemv_mma_kernel<MODE, EARLY>;
     static std::atomic<unsigned long long> configured{0};
     if (int st = ensure_smem(kernel, kMmaSmemBytes, configured)) return st;
+    unsigned int* status = nullptr;
+    if (int st = status_word(&status)) return st;
     // 16-row groups a CTA works on at a time: the count (at most 8, two warps each)
     // that leaves the fewest idle SM-slots over the waves of the persistent grid;
     // ties go to the larger count (more of the matrix in flight per SM)
@@ -430,7 +432,7 @@ static int gemv_mma_launch(const uint32_t* m, const uint32_t* v, float* out, lon
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const uint4*>(m), v, out,
-                                             (int)M, (int)(N / 16), B, gpc);
+                                             (int)M, (int)(N / 16), B, gpc, status);
     return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
 }
 

@@ -37,6 +37,7 @@
 // The grid is persistent; groups per CTA are chosen so that the waves are full.
 #pragma once
 #include "gemv_kernels.cuh"
+#include "gemv_ring.cuh"  // mbarrier helpers with bounded waits
 
 namespace feather {
 
@@ -44,12 +45,13 @@ constexpr int kMmaWarps = 16;
 constexpr int kMmaThreads = kMmaWarps * 32;
 constexpr int kMmaMaxGroups = kMmaWarps / 2;              // 16-row groups a CTA works on at a time
 constexpr int kMmaVectors = 8;
-constexpr int kMmaTileCodes = 2048;                       // codes of each vector in a tile (two tiles resident)
+constexpr int kMmaTileCodes = 1024;                       // codes of each vector in a tile (three tiles resident)
+constexpr int kMmaTileBuffers = 3;
 constexpr int kMmaVecStride = kMmaTileCodes * 2 + 16;     // bytes; the 16 spread the vectors over the banks
 constexpr int kMmaTileBytes = 8 * kMmaVecStride;          // one tile of all eight vectors
-constexpr int kMmaDepth = 4;                              // units a warp keeps in flight
+constexpr int kMmaDepth = 5;                              // units a warp keeps in flight
 constexpr int kMmaSlotBytes = 16 * 128;                   // a unit of a warp: 128 bytes of each of its 16 rows
-constexpr int kMmaRingOffset = 2 * kMmaTileBytes;
+constexpr int kMmaRingOffset = kMmaTileBuffers * kMmaTileBytes;
 constexpr int kMmaSmemBytes = kMmaRingOffset + kMmaWarps * kMmaDepth * kMmaSlotBytes;
 
 __device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -75,9 +77,11 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 template <int MODE, bool EARLY>
 __global__ void __launch_bounds__(kMmaThreads, 1)
 gemv_mma_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
-                float* __restrict__ out, int M, int n16, int B, int gpc) {
+                float* __restrict__ out, int M, int n16, int B, int gpc,
+                unsigned int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char mma_smem[];
-    __shared__ float part[kMmaMaxGroups][16][kMmaVectors];    // the odd-unit warps' sums
+    __shared__ float part[2][kMmaMaxGroups][16][kMmaVectors]; // the odd-unit warps' sums, by pass parity
+    __shared__ __align__(8) unsigned long long tile_bar[kMmaTileBuffers];  // "tile staged" per buffer
     constexpr int D = kMmaDepth;
     constexpr int kTileChunks = kMmaTileCodes / 16;
     static_assert(kTileChunks % 16 == 0, "a tile is a whole number of unit pairs");
@@ -98,9 +102,48 @@ gemv_mma_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
     const int frag_off0 = g * 128 + (((0 + t) ^ ((g & 1) << 2)) << 4);
     const int frag_off1 = g * 128 + (((4 + t) ^ ((g & 1) << 2)) << 4);
 
+    // Vector tiles: three buffers, a sequence of tiles that runs on across passes.
+    // Every thread owns one word of four vectors' tile: it loads those words of
+    // tile s + 2 before the CTA computes tile s and decodes them into buffer
+    // (s + 1) % 3 one step later, then arrives on that buffer's mbarrier; a warp
+    // starts tile s once all 512 threads have arrived for it.  Nobody waits at a
+    // CTA-wide barrier: the arrivals a warp needs happened a whole compute step
+    // earlier.  Vectors B..7 and chunks past the row end are zero.
+    static_assert(kMmaTileCodes / 4 * 2 == kMmaThreads, "a word of four vectors' tile per thread");
+    const int st_word = threadIdx.x & (kMmaTileCodes / 4 - 1);    // staging role: this word ...
+    const int st_vec = (threadIdx.x / (kMmaTileCodes / 4)) * 4;   // ... of these four vectors
+    uint32_t w[4];
+    int fetch_t0 = 0;                                             // first chunk of the next tile to fetch
+    auto fetch_tile = [&]() {
+        const bool on = st_word < min(kTileChunks, n16 - fetch_t0) * 4;
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+            w[b] = (on && st_vec + b < B) ? __ldg(v + ((size_t)(st_vec + b) * n16 + fetch_t0) * 4 + st_word) : 0u;
+        fetch_t0 += kTileChunks;
+        if (fetch_t0 >= n16) fetch_t0 = 0;                        // on to the next pass: same vectors
+    };
+    auto store_tile = [&](int buffer) {   // what fetch_tile loaded last; every thread arrives
+        unsigned char* tile_smem = mma_smem + buffer * kMmaTileBytes;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            uint32_t lo, hi;
+            decode_word_h2<MODE>(w[b], lo, hi);
+            reinterpret_cast<uint2*>(tile_smem + (size_t)(st_vec + b) * kMmaVecStride)[st_word] = make_uint2(lo, hi);
+        }
+        mbar_arrive(smem_u32(&tile_bar[buffer]));
+    };
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < kMmaTileBuffers; ++i) mbar_init(smem_u32(&tile_bar[i]), kMmaThreads);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     bool waited = false;
-    for (int pass = blockIdx.x; pass < n_pass; pass += gridDim.x) {
+    int buf = 0;                                              // buffer of the tile being computed
+    uint32_t phases = 0;                                      // bit i: parity to wait for on buffer i
+    for (int pass = blockIdx.x, n_done = 0; pass < n_pass; pass += gridDim.x, ++n_done) {
         const int row0 = (pass * gpc + group) * 16;
         const int row_a = row0 + g;
         const uint4* cp_src = m + (size_t)min(row0 + cp_row, M - 1) * n16;
@@ -129,42 +172,25 @@ gemv_mma_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
 #pragma unroll
                 for (int k = 0; k < D; ++k) issue(k);
             }
+            fetch_tile();                // the vectors may come from the kernel before: after the wait
+            store_tile(0);
+            fetch_tile();
         }
 
         float acc[8][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
-        // Vector tiles are double-buffered and staged in two halves around the
-        // compute of the tile before: a thread owns word threadIdx.x of every
-        // vector's tile, loads the next tile's eight words before it computes and
-        // decodes them into the other buffer afterwards -- one barrier per tile and
-        // no load latency in front of it.  Vectors B..7 and chunks past the row end
-        // are zero.
-        static_assert(kMmaTileCodes / 4 == kMmaThreads, "one word of each vector's tile per thread");
-        uint32_t w[kMmaVectors];
-        auto fetch = [&](int t0) {
-            const int tile_chunks = min(kTileChunks, n16 - t0);
-            const bool on = t0 < n16 && (int)threadIdx.x < tile_chunks * 4;
-#pragma unroll
-            for (int b = 0; b < kMmaVectors; ++b)
-                w[b] = (on && b < B) ? __ldg(v + ((size_t)b * n16 + t0) * 4 + threadIdx.x) : 0u;
-        };
-        __syncthreads();                 // the previous pass has let go of both buffers
-        fetch(0);
-        for (int t0 = 0, tile = 0; t0 < n16; t0 += kTileChunks, ++tile) {
+        for (int t0 = 0; t0 < n16; t0 += kTileChunks) {
             const int tile_chunks = min(kTileChunks, n16 - t0);
             const int fill_chunks = (tile_chunks + 15) / 16 * 16;   // whole units for both warps of a group
-            unsigned char* tile_smem = mma_smem + (tile & 1) * kMmaTileBytes;
-#pragma unroll
-            for (int b = 0; b < kMmaVectors; ++b) {
-                uint32_t lo, hi;
-                decode_word_h2<MODE>(w[b], lo, hi);
-                reinterpret_cast<uint2*>(tile_smem + (size_t)b * kMmaVecStride)[threadIdx.x] = make_uint2(lo, hi);
-            }
-            __syncthreads();             // tile staged; everyone is done with the tile before the last
-            fetch(t0 + kTileChunks);     // in flight while this tile is computed
-            const unsigned char* vec_g = tile_smem + (size_t)g * kMmaVecStride;
+            // this tile is staged (by everybody, one compute step ago)
+            mbar_wait(smem_u32(&tile_bar[buf]), (phases >> buf) & 1u, status);
+            phases ^= 1u << buf;
+            const unsigned char* vec_g = mma_smem + buf * kMmaTileBytes + (size_t)g * kMmaVecStride;
+            buf = buf == kMmaTileBuffers - 1 ? 0 : buf + 1;
+            store_tile(buf);             // the next tile; its buffer was last read two tiles ago
+            fetch_tile();                // the tile after it, in flight while this one is computed
             if (!working) continue;
             // this warp's units inside the tile: k in [t0 / 16, t0 / 16 + fill_chunks / 16)
             const int k_end = t0 / 16 + fill_chunks / 16;
@@ -209,11 +235,12 @@ gemv_mma_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
         for (int i = 0; i < 4; ++i)
             d[i] = ((acc[0][i] + acc[1][i]) + (acc[2][i] + acc[3][i])) +
                    ((acc[4][i] + acc[5][i]) + (acc[6][i] + acc[7][i]));
+        float (*pp)[16][kMmaVectors] = part[n_done & 1];
         if (working && split == 1) {
-            part[group][g][2 * t] = d[0];
-            part[group][g][2 * t + 1] = d[1];
-            part[group][g + 8][2 * t] = d[2];
-            part[group][g + 8][2 * t + 1] = d[3];
+            pp[group][g][2 * t] = d[0];
+            pp[group][g][2 * t + 1] = d[1];
+            pp[group][g + 8][2 * t] = d[2];
+            pp[group][g + 8][2 * t + 1] = d[3];
         }
         __syncthreads();
         if (working && split == 0 && pass * gpc + group < n_groups) {
@@ -221,7 +248,7 @@ gemv_mma_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
             for (int i = 0; i < 4; ++i) {
                 const int row = row_a + (i >> 1) * 8, b = 2 * t + (i & 1);
                 if (row < M && b < B)
-                    out[(size_t)b * M + row] = d[i] + part[group][g + (i >> 1) * 8][b];
+                    out[(size_t)b * M + row] = d[i] + pp[group][g + (i >> 1) * 8][b];
             }
         }
     }
