@@ -1,4 +1,11 @@
-"""Row-sharded multi-GPU GEMV.
+"""Multi-GPU GEMV: row-sharded (``RowShardedGemv``, below) and column-sharded
+(``ColumnShardedGemv``: every rank holds a column block of all rows and the
+matching slice of the vector, the partial row sums are all-reduced -- inside
+the GEMV kernel through peer-mapped inboxes, or with the process group's
+all-reduce).
+
+Row-sharded GEMV
+----------------
 
 The reference is single-GPU; this is the row split its GEMV admits: rows are
 independent (feather/routines/gemv.py:17-18: one program per row, row stride
@@ -30,7 +37,8 @@ from typing import Callable, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-__all__ = ["row_block", "local_words", "RowShardedGemv", "PeerAllReduce", "ColumnShardedGemv"]
+__all__ = ["row_block", "local_words", "local_column_words", "local_vector_words", "RowShardedGemv",
+           "PeerAllReduce", "ColumnShardedGemv"]
 
 
 def row_block(M: int, world_size: int, rank: int) -> Tuple[int, int]:
@@ -51,6 +59,32 @@ def local_words(m_packed: torch.Tensor, m_shape, world_size: int, rank: int) -> 
         raise ValueError("N must be a multiple of 4")
     begin, end = row_block(M, world_size, rank)
     return m_packed.reshape(-1)[begin * (N // 4): end * (N // 4)]
+
+
+def _column_words(N: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Words [begin, end) of a packed row (or of the packed vector) that hold
+    rank's columns.  Column blocks are whole 16-byte chunks."""
+    if world_size < 1 or not 0 <= rank < world_size:
+        raise ValueError(f"bad rank {rank} for world size {world_size}")
+    if N % (16 * world_size):
+        raise ValueError(f"N={N} does not split into {world_size} blocks of whole 16-code chunks")
+    words = N // world_size // 4
+    return rank * words, (rank + 1) * words
+
+
+def local_column_words(m_packed: torch.Tensor, m_shape, world_size: int, rank: int) -> torch.Tensor:
+    """This rank's COLUMN block of a full packed matrix: columns
+    ``[r*N/W, (r+1)*N/W)`` of every row, packed row-major (a copy: the block is
+    strided in the full matrix)."""
+    M, N = int(m_shape[0]), int(m_shape[1])
+    begin, end = _column_words(N, world_size, rank)
+    return m_packed.reshape(-1)[: M * (N // 4)].reshape(M, N // 4)[:, begin:end].contiguous().reshape(-1)
+
+
+def local_vector_words(v_packed: torch.Tensor, N: int, world_size: int, rank: int) -> torch.Tensor:
+    """The slice of the packed vector that goes with ``local_column_words`` (a view)."""
+    begin, end = _column_words(int(N), world_size, rank)
+    return v_packed.reshape(-1)[begin:end]
 
 
 def _share_with_peers(shared: Optional[torch.Tensor], dev: torch.device, group, error=None):
@@ -322,40 +356,66 @@ class PeerAllReduce:
 class ColumnShardedGemv:
     """``y = A @ v`` with A's COLUMNS split over the ranks: rank r holds columns
     ``[r*N/W, (r+1)*N/W)`` of every row (packed row-major, row stride N/(4W)
-    words) and is called with the matching slice of the packed vector.  The
-    partial sums are added inside the GEMV kernel through the ranks'
-    peer-mapped inboxes (``feather_gemv_fp8_allreduce``): one launch per call,
-    no collective, the same bits on every rank.
+    words; see ``local_column_words``) and is called with the matching slice of
+    the packed vector.  Every rank's row sums are partial; the result is their
+    sum, on every rank.
+
+    * ``ctx`` given (a ``PeerAllReduce``): the partial sums are added inside the
+      GEMV kernel through the ranks' peer-mapped inboxes
+      (``feather_gemv_fp8_allreduce``): one launch per call, no collective, the
+      same bits on every rank.
+    * ``ctx=None``: local GEMV, then one all-reduce of the process group (NCCL
+      on GPUs).  ``local_gemv`` -- ``(m_local, v_local, (M, N/W), mode, out) ->
+      out`` -- replaces the CUDA kernel; tests on CPU ranks inject the oracle.
 
     ``m_shape`` is the LOCAL unpacked shape ``(M, N/W)``; N/W must be a
     multiple of 16.  The result is the object's own buffer.
     """
 
-    def __init__(self, m_local: torch.Tensor, m_shape, mode: str, ctx: PeerAllReduce,
-                 out: Optional[torch.Tensor] = None):
+    def __init__(self, m_local: torch.Tensor, m_shape, mode: str, ctx: Optional[PeerAllReduce] = None,
+                 out: Optional[torch.Tensor] = None, group: Optional[dist.ProcessGroup] = None,
+                 local_gemv: Optional[Callable] = None):
         from . import _lib
-        from .packers.fp8 import as_words
         self.M, self.n_local = int(m_shape[0]), int(m_shape[1])
         if self.n_local % 16:
             raise ValueError("the local column count must be a multiple of 16")
+        if m_local.numel() != self.M * (self.n_local // 4):
+            raise ValueError(f"local block holds {m_local.numel()} words, {self.M}x{self.n_local} "
+                             f"needs {self.M * (self.n_local // 4)}")
+        self.m_local, self.ctx, self.mode = m_local, ctx, mode
+        self._mode_id = _lib.mode_id(mode)
+        self._n_words = self.n_local // 4
+        if ctx is None:
+            if not dist.is_initialized():
+                raise RuntimeError("torch.distributed is not initialised")
+            self.group = group
+            if local_gemv is None:
+                from .routines.gemv import gemv_fp8_acc_fp32_gpu
+                local_gemv = gemv_fp8_acc_fp32_gpu
+            self._local_gemv = local_gemv
+            self.out = (torch.empty(self.M, dtype=torch.float32, device=m_local.device)
+                        if out is None else out)
+            return
+        if local_gemv is not None:
+            raise ValueError("local_gemv cannot be combined with the fused all-reduce")
+        from .packers.fp8 import as_words
         if self.M > ctx.max_rows:
             raise ValueError(f"M={self.M} exceeds the all-reduce inbox ({ctx.max_rows} rows)")
         words = as_words(m_local, "m_local")
-        if words.numel() != self.M * (self.n_local // 4):
-            raise ValueError(f"local block holds {words.numel()} words, {self.M}x{self.n_local} "
-                             f"needs {self.M * (self.n_local // 4)}")
         if words.device != ctx.device:
             raise ValueError("the matrix shard must live on the context's device")
-        self.m_local, self.ctx, self.mode = m_local, ctx, mode
         self.out = torch.empty(self.M, dtype=torch.float32, device=ctx.device) if out is None else out
         self._m_ptr, self._out_ptr = words.data_ptr(), self.out.data_ptr()
-        self._mode_id = _lib.mode_id(mode)
         self._fn, self._check = ctx._lib.feather_gemv_fp8_allreduce, _lib.check
         self._stream_ptr = _lib.current_stream_ptr
-        self._n_words = self.n_local // 4
 
     def __call__(self, v_local: torch.Tensor) -> torch.Tensor:
         ctx = self.ctx
+        if ctx is None:
+            self._local_gemv(self.m_local, v_local, (self.M, self.n_local), self.mode, out=self.out)
+            if dist.get_world_size(self.group) > 1:
+                dist.all_reduce(self.out, group=self.group)
+            return self.out
         with torch._C.DisableTorchFunctionSubclass():
             if v_local.numel() < self._n_words or v_local.device != ctx.device:
                 raise ValueError("v must hold the local N/4 packed words on this rank's device")

@@ -49,6 +49,34 @@ def _worker(rank: int, world: int, port: int, case: str, q):
             y = op(vw)
             ref = O.gemv(mw.numpy().view(np.uint32), vw.numpy().view(np.uint32), (M, N), mode)
             q.put((rank, bool(np.array_equal(y.numpy(), ref)), op.row_begin, op.row_end))
+        elif case == "columns":
+            # column-sharded GEMV, non-fused path: oracle partial sums + gloo all-reduce
+            from feather_b200.sharded import ColumnShardedGemv, local_column_words, local_vector_words
+            Mc, Nc = 24, 64 * world
+            Ac = rng.standard_normal((Mc, Nc)).astype(np.float16)
+            vc = rng.standard_normal(Nc).astype(np.float16)
+            mwc = torch.from_numpy(O.pack_fp8_ndarray(Ac, mode).view(np.int32))
+            vwc = torch.from_numpy(O.pack_fp8_ndarray(vc, mode).view(np.int32))
+            cols = Nc // world
+            op = ColumnShardedGemv(local_column_words(mwc, (Mc, Nc), world, rank), (Mc, cols), mode,
+                                   local_gemv=_oracle_local_gemv)
+            y = op(local_vector_words(vwc, Nc, world, rank)).numpy().copy()
+            # the same block taken from the unpacked matrix, packed on its own
+            blk = O.pack_fp8_ndarray(np.ascontiguousarray(Ac[:, rank * cols:(rank + 1) * cols]), mode)
+            same_block = np.array_equal(blk.view(np.uint32), op.m_local.numpy().view(np.uint32))
+            parts = [O.gemv(O.pack_fp8_ndarray(np.ascontiguousarray(Ac[:, r * cols:(r + 1) * cols]), mode).view(np.uint32),
+                            O.pack_fp8_ndarray(vc[r * cols:(r + 1) * cols], mode).view(np.uint32),
+                            (Mc, cols), mode) for r in range(world)]
+            ref = O.gemv(mwc.numpy().view(np.uint32), vwc.numpy().view(np.uint32), (Mc, Nc), mode, acc="f64")
+            q.put((rank, bool(np.array_equal(y, sum(parts[1:], parts[0]))) and same_block,
+                   O.normalised_error(y, ref) < 1e-5))
+        elif case == "bad_columns":
+            from feather_b200.sharded import local_column_words
+            try:
+                local_column_words(mw, (M, 520), world, rank)   # 520 / 2 is not whole 16-code chunks
+                q.put((rank, "no error"))
+            except ValueError:
+                q.put((rank, "ValueError"))
         elif case == "disagree":
             shape = (M, N) if rank == 0 else (M, N)
             mode_r = mode if rank == 0 else "E5M2"
@@ -102,3 +130,11 @@ def test_row_block_partition():
         row_block(10, 4, 0)      # not divisible
     with pytest.raises(ValueError):
         row_block(8, 4, 4)       # rank out of range
+
+
+def test_column_sharded_partition_and_all_reduce_world_2():
+    assert _run("columns") == [(0, True, True), (1, True, True)]
+
+
+def test_column_sharded_rejects_ragged_split():
+    assert _run("bad_columns") == [(0, "ValueError"), (1, "ValueError")]
