@@ -189,7 +189,10 @@ int64_t feather_gemv_fp8_packed_workspace_bytes(int64_t M, int64_t N);
  *   epoch       1 for the first call, +1 for every later call, equal on all
  *               ranks.  Use two output buffers alternately (even / odd epoch):
  *               a fast rank may start writing call k+1 while a slow rank's
- *               consumer still reads call k.
+ *               consumer still reads call k.  Because the epoch is a launch
+ *               argument, a captured CUDA graph of this call must not be
+ *               replayed (the second replay would find its epoch already
+ *               published and not wait); launch it from the stream.
  * One call per rank must be in flight at the same time on every rank, each on
  * its own GPU.  A rank that never arrives makes the others raise the status
  * word after the bounded wait (see feather_device_status) instead of hanging.
