@@ -521,6 +521,16 @@ def run_ours(args) -> None:
                                             "GB/s": round(rb / ms_r / 1e6, 1),
                                             "frac_of_peak": round(rb / ms_r / 1e6 / peak, 4)}
         del relu_out
+        # packed-E5M2 attention (single head, non-causal), tensor-core bound: 4 * seq^2 * d flops
+        from feather_b200.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu as attn
+        for seq, d in ((4096, 128), (8192, 64)):
+            gen.manual_seed(31)
+            qkv = [fb.pack_fp8_tensor(torch.randn(seq, d, device=dev, generator=gen, dtype=torch.float16), "E5M2")
+                   for _ in range(3)]
+            o_attn = torch.empty(seq, d, dtype=torch.float32, device=dev)
+            ms_a = time_calls(torch, lambda: attn(qkv[0], qkv[1], qkv[2], seq, d // 4, out=o_attn), 50, 5)
+            extra[f"attention_e5m2_seq{seq}_d{d}"] = {
+                "us_per_call": round(ms_a * 1e3, 2), "TFLOP/s": round(4.0 * seq * seq * d / ms_a / 1e9, 1)}
         # encoder: fp16 16384^2 -> E5M2 (reads 2 B, writes 1 B per element)
         gen.manual_seed(9)
         src = torch.randn(M, N, device=dev, generator=gen, dtype=torch.float16)

@@ -22,6 +22,7 @@ SYMBOLS = {
     "feather_strerror": (ctypes.c_char_p, [_i32]),
     "feather_encode_fp8": (_i32, [_vp, _i32, _vp, _i64, _i32, _vp]),
     "feather_decode_fp8": (_i32, [_vp, _vp, _i64, _i32, _i32, _vp]),
+    "feather_attention_fp8_e5m2": (_i32, [_vp, _vp, _vp, _vp, _i64, _i64, _vp]),
     "feather_relu_fp8": (_i32, [_vp, _vp, _i64, _i32, _vp]),
     "feather_gemv_fp8": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp]),
     "feather_gemv_fp8_multi": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _i32, ctypes.c_uint32, _vp]),

@@ -7,6 +7,7 @@
 #include <cstring>
 
 #include "../../include/feather_b200.h"
+#include "attention_kernels.cuh"
 #include "dot_kernels.cuh"
 #include "fp8_codec.cuh"
 #include "gemv_kernels.cuh"
@@ -480,6 +481,18 @@ static int gemv_multi_dispatch(const uint32_t* m, const uint32_t* v, float* out,
     return FEATHER_OK;
 }
 
+template <int D>
+static int attention_launch(const uint32_t* q, const uint32_t* k, const uint32_t* v, float* out,
+                            long long seq_len, const DeviceInfo& dev, cudaStream_t s) {
+    auto kernel = attention_e5m2_kernel<D>;
+    // warps (16 queries each) per CTA: as many as still gives every SM a CTA
+    int warps = 4;
+    while (warps > 1 && (seq_len + 16 * warps - 1) / (16 * warps) < dev.sm_count) warps >>= 1;
+    const long long grid = (seq_len + 16 * warps - 1) / (16 * warps);
+    kernel<<<(unsigned)grid, 32 * warps, 0, s>>>(q, k, v, out, (int)seq_len);
+    return launch_status();
+}
+
 // Decode (optionally through ReLU) n_elems codes: a grid of up to 16 CTAs per SM,
 // each thread walking words with four loads in flight.
 static int decode_launch(const uint32_t* src, float* dst, long long n_elems, int mode, bool ieee,
@@ -629,6 +642,24 @@ int feather_decode_fp8(const uint32_t* src, float* dst, int64_t n_elems, int mod
     if (int st = device_info(&dev)) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return decode_launch(src, dst, n_elems, mode, semantics == FEATHER_DECODE_IEEE, false, *dev, s);
+}
+
+int feather_attention_fp8_e5m2(const uint32_t* q, const uint32_t* k, const uint32_t* v, float* out,
+                               int64_t seq_len, int64_t h_dim_words, void* stream) {
+    if (seq_len < 0 || h_dim_words <= 0 || seq_len > 0x7FFFFFFF / 128) return FEATHER_ERR_BAD_ARG;
+    if (seq_len == 0) return FEATHER_OK;
+    if (!q || !k || !v || !out) return FEATHER_ERR_BAD_ARG;
+    if (!aligned(q, 4) || !aligned(k, 4) || !aligned(v, 4) || !aligned(out, 16)) return FEATHER_ERR_MISALIGNED;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (h_dim_words) {
+        case 4: return attention_launch<16>(q, k, v, out, seq_len, *dev, s);
+        case 8: return attention_launch<32>(q, k, v, out, seq_len, *dev, s);
+        case 16: return attention_launch<64>(q, k, v, out, seq_len, *dev, s);
+        case 32: return attention_launch<128>(q, k, v, out, seq_len, *dev, s);
+        default: return h_dim_words > 32 ? FEATHER_ERR_TOO_LARGE : FEATHER_ERR_BAD_ARG;
+    }
 }
 
 int feather_relu_fp8(const uint32_t* src, float* dst, int64_t n_elems, int mode, void* stream) {

@@ -77,6 +77,26 @@ int feather_decode_fp8(const uint32_t* src, float* dst, int64_t n_elems, int mod
                        int semantics, void* stream);
 
 /*
+ * Single-head, non-causal attention on packed E5M2 operands:
+ *   out = softmax(Q K^T / sqrt(d)) V,  d = 4 * h_dim_words
+ * Replaces _flash_attention_fp8_e5m2_acc_fp32_kernel and
+ * flash_attention_fp8_e5m2_acc_fp32_gpu(q, k, v, seq_len, h_dim)
+ * (feather/routines/attention.py:14-108, :110-179) with the same arithmetic:
+ * key tiles of 64, FP32 scores and softmax state, probabilities rounded to FP16
+ * before they multiply V.  Like the reference, keys past seq_len in the last
+ * tile of 64 are read as zeros and NOT masked: each enters the softmax with
+ * score 0 and value 0, so a seq_len that is not a multiple of 64 does not give
+ * the textbook result (the reference's README lists the routine as unfinished).
+ *   q, k, v      seq_len rows of h_dim_words packed words each
+ *   out          seq_len x (4 * h_dim_words) floats, 16-byte aligned
+ *   h_dim_words  4, 8, 16 or 32 (d = 16 .. 128); larger powers of two, which
+ *                the reference accepts, return FEATHER_ERR_TOO_LARGE, anything
+ *                else FEATHER_ERR_BAD_ARG
+ */
+int feather_attention_fp8_e5m2(const uint32_t* q, const uint32_t* k, const uint32_t* v, float* out,
+                               int64_t seq_len, int64_t h_dim_words, void* stream);
+
+/*
  * ReLU on unpack: dst[i] = max(0, decode(code i)) as FP32, for i < n_elems.
  * Replaces _relu_1d_fp8_ret_fp32_kernel / relu1d_fp8_ret_fp32_feather_gpu
  * (feather/routines/activations.py:8-29, :32-41), which exist for E5M2 only;

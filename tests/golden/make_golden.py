@@ -27,6 +27,7 @@ logging.disable(logging.WARNING)  # the packer logs whole arrays for fp32 input
 warnings.simplefilter("ignore")
 
 import feather.routines.activations as ref_act
+import feather.routines.attention as ref_attn
 import feather.routines.dot as ref_dot
 import feather.routines.gemv as ref_gemv
 from feather.packers.fp8 import pack_fp8_ndarray, pack_fp8_tensor, unpack_into_fp8_ndarray
@@ -118,10 +119,32 @@ def make_relu() -> None:
     print("relu", os.path.getsize(os.path.join(HERE, "relu.npz")), "bytes")
 
 
+def make_attention() -> None:
+    """Flash attention on packed E5M2 through the reference kernel (its jitted
+    function under the autotuner, launched as the wrapper does, attention.py:172-178):
+    N(0, 1) inputs at sequence lengths that do and do not fill the last key tile."""
+    a = {}
+    for seq, d, seed in ((128, 64, 51), (100, 32, 52), (200, 128, 53), (64, 16, 54)):
+        rng = np.random.default_rng(seed)
+        q, k, v = (ref_pack(rng.standard_normal((seq, d)).astype(np.float16), "E5M2") for _ in range(3))
+        tq, tk, tv = (torch.from_numpy(x.view(np.int32).copy()) for x in (q, k, v))
+        out = torch.empty((seq, d), dtype=torch.float32)
+        kern = ref_attn._flash_attention_fp8_e5m2_acc_fp32_kernel
+        kern = getattr(kern, "fn", kern)                       # the jitted function under the autotuner
+        kern[((seq + 63) // 64,)](tq, tk, tv, out, seq, d // 4, _tile_sz=64)
+        a[f"s{seq}_d{d}_out"] = out.numpy().copy()
+        a[f"s{seq}_d{d}_seed"] = np.array(seed, dtype=np.int64)
+    np.savez_compressed(os.path.join(HERE, "attention.npz"), **a)
+    print("attention", os.path.getsize(os.path.join(HERE, "attention.npz")), "bytes")
+
+
 def main() -> None:
     if sys.argv[1:] == ["relu"]:  # only the ReLU fixture (the others are unchanged)
         return make_relu()
+    if sys.argv[1:] == ["attention"]:
+        return make_attention()
     make_relu()
+    make_attention()
     # 1. encode: every fp16 bit pattern, seeded fp32 samples, fp32 edge list
     enc = {}
     h = np.arange(65536, dtype=np.uint16).view(np.float16)

@@ -755,3 +755,47 @@ def test_gemv_multi_rejects(fb):
     assert lib.feather_gemv_fp8_multi(p, p, p, 4, 16, 2, 3, 0, None) == -3
     assert lib.feather_gemv_fp8_multi(p, p, p, 4, 16, -1, 0, 0, None) == -1
     assert lib.feather_gemv_fp8_multi(p, p, p, 4, 16, 2, 0, 2, None) == -1
+
+
+# ------------------------------------------------------------------ attention --
+@pytest.mark.parametrize("seq,d", [(128, 64), (100, 32), (200, 128), (64, 16), (1, 64), (1000, 128),
+                                   (4096, 64), (2500, 32), (8192, 128)])
+def test_attention_vs_oracle_and_reference_outputs(fb, golden, seq, d):
+    """Packed-E5M2 attention against the oracle (same tiles, same FP16 rounding of the
+    probabilities), the reference kernel's own outputs where the fixture has them, and
+    torch's scaled_dot_product_attention when the key tiles are full."""
+    from feather_b200.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu as attn
+    g = golden("attention")
+    key = f"s{seq}_d{d}"
+    seed = int(g[key + "_seed"]) if key + "_seed" in g else seq + d
+    rng = np.random.default_rng(seed)
+    x = [torch.from_numpy(rng.standard_normal((seq, d)).astype(np.float16)).cuda() for _ in range(3)]
+    q, k, v = (fb.pack_fp8_tensor(t, "E5M2") for t in x)
+    out = attn(q, k, v, seq, d // 4)
+    assert out.shape == (seq, d) and out.dtype == torch.float32
+    got = out.cpu().numpy()
+    if key + "_out" in g:
+        assert O.normalised_error(got, g[key + "_out"]) < 5e-4
+    if seq <= 1000:
+        host = lambda t: t.view(torch.int32).cpu().numpy().view(np.uint32)
+        assert O.normalised_error(got, O.flash_attention(host(q), host(k), host(v), seq, d // 4)) < 5e-4
+    if seq % 64 == 0:
+        dec = [fb.unpack_fp8_tensor(t, "E5M2").reshape(seq, d) for t in (q, k, v)]
+        ref = torch.nn.functional.scaled_dot_product_attention(*(t[None] for t in dec))[0]
+        assert O.normalised_error(got, ref.cpu().numpy()) < 2e-3
+    assert torch.equal(attn(q, k, v, seq, d // 4), out)          # deterministic
+
+
+def test_attention_rejects(fb):
+    from feather_b200.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu as attn
+    w = torch.zeros(64 * 16, dtype=torch.int32, device="cuda")
+    assert attn(w, w, w, 0, 16).shape == (0, 64)
+    with pytest.raises(ValueError):
+        attn(w, w, w, 64, 12)
+    with pytest.raises(ValueError):
+        attn(w, w, w[:100], 64, 16)
+    lib = fb._lib.load()
+    p = w.data_ptr()
+    assert lib.feather_attention_fp8_e5m2(p, p, p, p, 64, 64, None) == -8
+    assert lib.feather_attention_fp8_e5m2(p, p, p, p, 64, 5, None) == -1
+    assert lib.feather_attention_fp8_e5m2(p, p, p, p + 4, 64, 16, None) == -2

@@ -195,3 +195,22 @@ def test_relu_matches_reference_kernel(golden):
     assert O.relu(np.array([0x3C3CBC3C], dtype=np.uint32), 3).tolist() == [1.0, 0.0, 1.0]
     e4 = O.relu(np.array([0x8101FF7F], dtype=np.uint32), mode="E4M3")
     assert e4.tolist() == [480.0, 0.0, 2.0 ** -17, 0.0]
+
+
+# ------------------------------------------------------------------ attention --
+@pytest.mark.parametrize("seq,d", [(128, 64), (100, 32), (200, 128), (64, 16)])
+def test_attention_matches_reference_kernel(golden, seq, d):
+    """The restated attention (attention.py:14-108) against the reference kernel run
+    through Triton's interpreter, including sequence lengths that leave the last key
+    tile partly empty (the reference does not mask those keys)."""
+    g = golden("attention")
+    rng = np.random.default_rng(int(g[f"s{seq}_d{d}_seed"]))
+    q, k, v = (O.pack_fp8_ndarray(rng.standard_normal((seq, d)).astype(np.float16), "E5M2").view(np.uint32)
+               for _ in range(3))
+    got = O.flash_attention(q, k, v, seq, d // 4)
+    assert got.shape == (seq, d) and O.normalised_error(got, g[f"s{seq}_d{d}_out"]) < 1e-6
+    if seq % 64 == 0:  # full tiles: the textbook softmax(Q K^T / sqrt(d)) V up to the FP16 probabilities
+        dec = lambda w: O.unpack(w, "E5M2")[: seq * d].reshape(seq, d).astype(np.float64)
+        s = dec(q) @ dec(k).T / np.sqrt(d)
+        p = np.exp(s - s.max(axis=1, keepdims=True))
+        assert O.normalised_error(got, (p / p.sum(axis=1, keepdims=True)) @ dec(v)) < 1e-3
