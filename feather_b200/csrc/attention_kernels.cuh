@@ -6,11 +6,17 @@
 // and follows it step by step: key tiles of 64, scores accumulated in FP32 and divided by
 // sqrt(d) (:83), online softmax with a running maximum and sum (:85-90), probabilities
 // rounded to FP16 before they multiply V (:97-101), one division by the sum at the end
-// (:103-106).  Like the reference, keys past seq_len in the last tile are read as zero
+// (:103-106).  The division by sqrt(d) and the exponentials use the fast hardware forms
+// (div.full, ex2.approx), as the compiled reference kernel does.  Like the reference, keys
+// past seq_len in the last tile are read as zero
 // codes and their scores (zero) are NOT masked: each takes part in the softmax.
 //
-// Mapping.  A CTA is one, two or four warps; a warp owns 16 query rows for the whole key
-// loop, so the softmax state never leaves the warp.  Codes become FP16 by a byte permute
+// Mapping.  A CTA owns 16 query rows.  With one warp per CTA the warp walks all key tiles
+// and the softmax state never leaves it.  Short sequences give too few such warps to fill
+// the GPU, so a CTA may be 2, 4 or 8 warps that take every 2nd / 4th / 8th key tile of the SAME
+// rows, each with its own running maximum, sum and output, merged at the end through
+// shared memory (out = sum_w O_w e^(m_w - m) / sum_w l_w e^(m_w - m)): the same result up
+// to the rounding of the FP16 probabilities against a per-warp instead of a global maximum.  Codes become FP16 by a byte permute
 // (an E5M2 code is the high byte of an FP16 number) in registers:
 //   * S = Q K^T with mma.sync.m16n8k16: lane (g, t) holds word t of each 16-code chunk of
 //     query rows g and g + 8 as its A fragments and loads word t of the same chunk of key
@@ -29,7 +35,7 @@
 
 namespace feather {
 
-constexpr int kAttnThreads = 128;    // at most: 1, 2 or 4 warps of 16 queries each
+constexpr int kAttnThreads = 256;    // at most: 1, 2, 4 or 8 warps per CTA
 constexpr int kAttnTile = 64;        // keys per step (the reference's tile, attention.py:9)
 
 __device__ __forceinline__ void attn_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -46,17 +52,21 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 }
 
 // D = 4 * words per row: 16, 32, 64 or 128.
+// Grid: one CTA per 16 queries; blockDim.x / 32 warps split the key tiles.  Dynamic shared
+// memory: nothing for one warp, else warps * (16 * D + 32) floats.
 template <int D>
 __global__ void __launch_bounds__(kAttnThreads)
 attention_e5m2_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict__ k,
                       const uint32_t* __restrict__ v, float* __restrict__ out, int seq_len) {
+    extern __shared__ __align__(16) float attn_merge[];
     constexpr int KS = D / 16;                  // k-steps of S = Q K^T (16 codes each)
     constexpr int WPR = D / 4;                  // words per row
     constexpr int NG = (WPR + 7) / 8;           // groups of four 8-column tiles of O (32 columns)
     constexpr int NT = 4 * NG;                  // column tiles held (D = 16: half of them are padding)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int row_a = ((int)blockIdx.x * ((int)blockDim.x >> 5) + warp) * 16 + g, row_b = row_a + 8;
+    const int n_split = (int)blockDim.x >> 5;
+    const int row_a = (int)blockIdx.x * 16 + g, row_b = row_a + 8;
 
     // Q fragments, kept for the whole loop; rows past seq_len are zero codes (:36)
     uint32_t qa[KS][2], qb[KS][2];
@@ -73,7 +83,7 @@ attention_e5m2_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
     const float sqrt_d = sqrtf((float)D);
 
-    for (int key0 = 0; key0 < seq_len; key0 += kAttnTile) {
+    for (int key0 = warp * kAttnTile; key0 < seq_len; key0 += n_split * kAttnTile) {
         // ---- S = Q K^T for this warp's 16 rows and the tile's 64 keys ----
         float sc[8][4];
 #pragma unroll
@@ -93,7 +103,7 @@ attention_e5m2_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) sc[n][i] = __fdiv_rn(sc[n][i], sqrt_d);
+            for (int i = 0; i < 4; ++i) sc[n][i] = __fdividef(sc[n][i], sqrt_d);
             mx_a = fmaxf(mx_a, fmaxf(sc[n][0], sc[n][1]));
             mx_b = fmaxf(mx_b, fmaxf(sc[n][2], sc[n][3]));
         }
@@ -102,13 +112,13 @@ attention_e5m2_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xFFFFFFFFu, mx_b, 1));
         mx_b = fmaxf(mx_b, __shfl_xor_sync(0xFFFFFFFFu, mx_b, 2));
         const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-        const float alpha_a = expf(m_a - mn_a), alpha_b = expf(m_b - mn_b);
+        const float alpha_a = __expf(m_a - mn_a), alpha_b = __expf(m_b - mn_b);
         float sum_a = 0.f, sum_b = 0.f;
         uint32_t p[8][2];                       // probabilities as FP16 pairs: [n][row a | row b]
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
-            const float e0 = expf(sc[n][0] - mn_a), e1 = expf(sc[n][1] - mn_a);
-            const float e2 = expf(sc[n][2] - mn_b), e3 = expf(sc[n][3] - mn_b);
+            const float e0 = __expf(sc[n][0] - mn_a), e1 = __expf(sc[n][1] - mn_a);
+            const float e2 = __expf(sc[n][2] - mn_b), e3 = __expf(sc[n][3] - mn_b);
             sum_a += e0 + e1;
             sum_b += e2 + e3;
             p[n][0] = pack_h2(e0, e1);
@@ -155,6 +165,45 @@ attention_e5m2_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict
                              b0[i], b1[i]);
             }
         }
+    }
+    if (n_split > 1) {
+        // ---- merge the warps' partial results: [warp][row][col] sums, then [warp][row] m and l ----
+        float* so = attn_merge + (size_t)warp * (16 * D + 32);
+#pragma unroll
+        for (int c = 0; c < NG; ++c) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int col = 32 * c + 4 * (2 * t + e);
+                if (col < D) {
+                    *reinterpret_cast<float4*>(so + g * D + col) =
+                        make_float4(o[4 * c][e], o[4 * c + 1][e], o[4 * c + 2][e], o[4 * c + 3][e]);
+                    *reinterpret_cast<float4*>(so + (g + 8) * D + col) =
+                        make_float4(o[4 * c][2 + e], o[4 * c + 1][2 + e], o[4 * c + 2][2 + e], o[4 * c + 3][2 + e]);
+                }
+            }
+        }
+        if (t == 0) {
+            so[16 * D + g] = m_a;
+            so[16 * D + g + 8] = m_b;
+            so[16 * D + 16 + g] = l_a;
+            so[16 * D + 16 + g + 8] = l_b;
+        }
+        __syncthreads();
+        const int rows_here = min(16, seq_len - (int)blockIdx.x * 16);
+        for (int idx = threadIdx.x; idx < rows_here * D; idx += blockDim.x) {
+            const int row = idx / D, col = idx - row * D;
+            float m = -INFINITY;
+            for (int w = 0; w < n_split; ++w) m = fmaxf(m, attn_merge[(size_t)w * (16 * D + 32) + 16 * D + row]);
+            float l = 0.f, acc = 0.f;
+            for (int w = 0; w < n_split; ++w) {       // warps in order: a fixed summation order
+                const float* sw = attn_merge + (size_t)w * (16 * D + 32);
+                const float scale = expf(sw[16 * D + row] - m);   // a warp without tiles: e^(-inf) = 0
+                l += sw[16 * D + 16 + row] * scale;
+                acc += sw[row * D + col] * scale;
+            }
+            out[((size_t)blockIdx.x * 16 + row) * D + col] = __fdiv_rn(acc, l);
+        }
+        return;
     }
     // ---- out = O / l (:103-106).  Fragment (tile 4c + i, value e / 2 + e): row g or g + 8,
     // column 32 c + 4 (2t + e) + i: four consecutive floats over i ----

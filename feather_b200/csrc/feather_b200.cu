@@ -485,11 +485,17 @@ template <int D>
 static int attention_launch(const uint32_t* q, const uint32_t* k, const uint32_t* v, float* out,
                             long long seq_len, const DeviceInfo& dev, cudaStream_t s) {
     auto kernel = attention_e5m2_kernel<D>;
-    // warps (16 queries each) per CTA: as many as still gives every SM a CTA
-    int warps = 4;
-    while (warps > 1 && (seq_len + 16 * warps - 1) / (16 * warps) < dev.sm_count) warps >>= 1;
-    const long long grid = (seq_len + 16 * warps - 1) / (16 * warps);
-    kernel<<<(unsigned)grid, 32 * warps, 0, s>>>(q, k, v, out, (int)seq_len);
+    // one CTA per 16 queries; 1, 2, 4 or 8 warps per CTA split the key tiles, so that short
+    // sequences still put a few warps on every scheduler (4 per SM); the merge buffer stays
+    // within the 48 KiB of shared memory a kernel gets without asking
+    const long long grid = (seq_len + 15) / 16;
+    const long long tiles = (seq_len + kAttnTile - 1) / kAttnTile;
+    int warps = 1;
+    while (warps < 8 && grid * warps < 8ll * dev.sm_count && 2 * warps <= tiles &&
+           2 * warps * (16 * D + 32) * sizeof(float) <= 48 * 1024)
+        warps <<= 1;
+    const size_t smem = warps > 1 ? (size_t)warps * (16 * D + 32) * sizeof(float) : 0;
+    kernel<<<(unsigned)grid, 32 * warps, smem, s>>>(q, k, v, out, (int)seq_len);
     return launch_status();
 }
 

@@ -38,9 +38,12 @@ __device__ __forceinline__ void fma_decoded(const uint32_t (&h)[8], const uint4 
     fma_h2(h[7], vb.w, acc[2], acc[3]);
 }
 
+// Shared memory: nb vector regions of FP16 values, each the row length rounded up to
+// 512 codes but no more than the tile of kRowsTileCodes / nb codes.
 constexpr int gemv_multi_smem_bytes(int n_codes, int nb) {
-    return nb * ((n_codes + 511) / 512 * 512 < kRowsTileCodes / nb ? (n_codes + 511) / 512 * 512
-                                                                    : kRowsTileCodes / nb) * 2;
+    const int padded = (n_codes + 511) / 512 * 512;
+    const int tile = kRowsTileCodes / nb;
+    return nb * (padded < tile ? padded : tile) * 2;
 }
 
 // Grid: one CTA per group of 16 rows.  v: B vectors of n16 * 4 words each, one

@@ -25,7 +25,7 @@ def _codes(n_words: int, seed: int) -> torch.Tensor:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", choices=("gemv", "dot", "encode", "decode", "relu", "multi", "packed"),
+    ap.add_argument("--op", choices=("gemv", "dot", "encode", "decode", "relu", "multi", "packed", "attention"),
                     default="gemv")
     ap.add_argument("--batch", type=int, default=8, help="vectors per call for --op multi")
     ap.add_argument("--mode", choices=("E5M2", "E4M3"), default="E5M2")
@@ -62,6 +62,12 @@ def main() -> None:
         out = torch.empty((M + 3) // 4, dtype=torch.uint32, device="cuda")
         call = lambda i: fb.gemv_fp8_ret_packed_gpu(mats[i % 2], v, (M, N), a.mode, out=out)
         nbytes = M * N + N + M
+    elif a.op == "attention":   # --M = sequence length, --N = model dimension (16 .. 128)
+        from feather_b200.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu as attn
+        qkv = [[_codes(M * N // 4, s + 3 * i) for s in (1, 2, 3)] for i in range(2)]
+        out = torch.empty(M, N, dtype=torch.float32, device="cuda")
+        call = lambda i: attn(*qkv[i % 2], M, N // 4, out=out)
+        nbytes = 3 * M * N + 4 * M * N
     elif a.op == "relu":
         from feather_b200.routines.activations import relu1d_fp8_ret_fp32_feather_gpu as relu
         ws = [_codes(M * N // 4, s) for s in (1, 2)]
