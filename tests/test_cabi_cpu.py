@@ -48,6 +48,23 @@ def test_argument_rejection_needs_no_device(lib):
     assert lib.feather_decode_fp8(None, None, 4, 0, 2, None) == -3       # semantics
     assert lib.feather_dot_fp8(None, None, None, None, -1, 0, None) == -1
     assert lib.feather_dot_fp8(None, None, None, None, 4, 0, None) == -1  # out is null
+    # the entry points added around the path
+    assert lib.feather_relu_fp8(None, None, -1, 0, None) == -1
+    assert lib.feather_relu_fp8(None, None, 4, 2, None) == -3
+    assert lib.feather_relu_fp8(None, None, 0, 1, None) == 0
+    assert lib.feather_gemv_fp8_multi(None, None, None, 4, 16, 65, 0, 0, None) == -1   # too many vectors
+    assert lib.feather_gemv_fp8_multi(None, None, None, 4, 18, 2, 0, 0, None) == -1   # N % 4
+    assert lib.feather_gemv_fp8_multi(None, None, None, 4, 16, 2, 5, 0, None) == -3
+    assert lib.feather_gemv_fp8_multi(None, None, None, 4, 16, 0, 0, 0, None) == 0    # no vectors
+    assert lib.feather_gemv_fp8_packed(None, None, None, None, 4, 16, 0, 7, 0, None) == -3  # output mode
+    assert lib.feather_gemv_fp8_packed(None, None, None, None, 4, 16, 0, 0, 8, None) == -1  # flags
+    assert lib.feather_gemv_fp8_packed(None, None, None, None, 0, 16, 0, 1, 0, None) == 0
+    assert lib.feather_gemv_fp8_packed_workspace_bytes(0, 16) == 0
+    assert lib.feather_attention_fp8_e5m2(None, None, None, None, -1, 16, None) == -1
+    assert lib.feather_attention_fp8_e5m2(None, None, None, None, 64, 0, None) == -1
+    assert lib.feather_attention_fp8_e5m2(None, None, None, None, 0, 16, None) == 0
+    assert lib.feather_gemv_fp8_allreduce(None, None, None, 8, 16, 0, None, 0, None, 0, 1, None) == -1
+    assert lib.feather_gemv_fp8_allreduce(None, None, None, 8, 20, 0, None, 0, None, 0, 1, None) == -1  # N % 16
 
 
 def test_python_surface_without_gpu():
@@ -59,6 +76,8 @@ def test_python_surface_without_gpu():
     from feather.packers.fp8 import pack_fp8_tensor
     from feather.routines.dot import dot_fp8_e5m2_acc_fp32_gpu  # noqa: F401
     from feather.routines.gemv import gemv_fp8_e4m3_acc_fp32_gpu, gemv_fp8_e5m2_acc_fp32_gpu  # noqa: F401
+    from feather.routines.activations import relu1d_fp8_ret_fp32_feather_gpu  # noqa: F401
+    from feather.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu  # noqa: F401
     with pytest.raises(NotImplementedError):
         pack_fp8_tensor(torch.zeros(4, dtype=torch.float16), mode="E3M4")
     if not torch.cuda.is_available():
