@@ -51,29 +51,39 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// D = 4 * words per row: 16, 32, 64 or 128.
-// Grid: one CTA per 16 queries; blockDim.x / 32 warps split the key tiles.  Dynamic shared
-// memory: nothing for one warp, else warps * (16 * D + 32) floats.
-template <int D>
+// D = 4 * words per row: 16, 32, 64, 128 (CS = 1), 256 (CS = 2) or 512 (CS = 4).
+// Grid: one CTA per 16 queries.
+//   CS = 1: blockDim.x / 32 warps split the key tiles.  Dynamic shared memory: nothing for
+//           one warp, else warps * (16 * D + 32) floats.
+//   CS > 1: the model dimension is too wide for one warp's registers, so the CTA is CS
+//           warps that each own D / CS = 128 columns: a warp multiplies its slice of Q
+//           with its slice of K (a partial S), the partials are added through shared
+//           memory in warp order (every warp then holds the same S and runs the same
+//           softmax), and each warp accumulates its own columns of O.  Dynamic shared
+//           memory: CS * 1024 floats.
+template <int D, int CS>
 __global__ void __launch_bounds__(kAttnThreads)
 attention_e5m2_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict__ k,
                       const uint32_t* __restrict__ v, float* __restrict__ out, int seq_len) {
     extern __shared__ __align__(16) float attn_merge[];
-    constexpr int KS = D / 16;                  // k-steps of S = Q K^T (16 codes each)
+    constexpr int DS = D / CS;                  // columns this warp contracts over and outputs
+    constexpr int KS = DS / 16;                 // k-steps of S = Q K^T (16 codes each)
     constexpr int WPR = D / 4;                  // words per row
-    constexpr int NG = (WPR + 7) / 8;           // groups of four 8-column tiles of O (32 columns)
+    constexpr int NG = (DS / 4 + 7) / 8;        // groups of four 8-column tiles of O (32 columns)
     constexpr int NT = 4 * NG;                  // column tiles held (D = 16: half of them are padding)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int n_split = (int)blockDim.x >> 5;
+    const int n_split = CS > 1 ? 1 : (int)blockDim.x >> 5;   // warps that split the key tiles
+    const int key_warp = CS > 1 ? 0 : warp;
+    const int woff = CS > 1 ? warp * (DS / 4) : 0;            // first word of this warp's column slice
     const int row_a = (int)blockIdx.x * 16 + g, row_b = row_a + 8;
 
     // Q fragments, kept for the whole loop; rows past seq_len are zero codes (:36)
     uint32_t qa[KS][2], qb[KS][2];
 #pragma unroll
     for (int s = 0; s < KS; ++s) {
-        const uint32_t wa = row_a < seq_len ? __ldg(q + (size_t)row_a * WPR + 4 * s + t) : 0u;
-        const uint32_t wb = row_b < seq_len ? __ldg(q + (size_t)row_b * WPR + 4 * s + t) : 0u;
+        const uint32_t wa = row_a < seq_len ? __ldg(q + (size_t)row_a * WPR + woff + 4 * s + t) : 0u;
+        const uint32_t wb = row_b < seq_len ? __ldg(q + (size_t)row_b * WPR + woff + 4 * s + t) : 0u;
         decode_word_h2<kE5M2>(wa, qa[s][0], qa[s][1]);
         decode_word_h2<kE5M2>(wb, qb[s][0], qb[s][1]);
     }
@@ -83,20 +93,37 @@ attention_e5m2_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
     const float sqrt_d = sqrtf((float)D);
 
-    for (int key0 = warp * kAttnTile; key0 < seq_len; key0 += n_split * kAttnTile) {
+    for (int key0 = key_warp * kAttnTile; key0 < seq_len; key0 += n_split * kAttnTile) {
         // ---- S = Q K^T for this warp's 16 rows and the tile's 64 keys ----
         float sc[8][4];
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
             sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
             const int key = key0 + 8 * n + g;
-            const uint32_t* kr = k + (size_t)min(key, seq_len - 1) * WPR + t;
+            const uint32_t* kr = k + (size_t)min(key, seq_len - 1) * WPR + woff + t;
 #pragma unroll
             for (int s = 0; s < KS; ++s) {
                 uint32_t b0, b1;
                 decode_word_h2<kE5M2>(key < seq_len ? __ldg(kr + 4 * s) : 0u, b0, b1);
                 attn_mma(sc[n], qa[s][0], qb[s][0], qa[s][1], qb[s][1], b0, b1);
             }
+        }
+        if (CS > 1) {
+            // ---- add the warps' partial scores: [warp][fragment value][lane], warps in order ----
+            __syncthreads();                    // the previous tile's partials have been read
+#pragma unroll
+            for (int n = 0; n < 8; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) attn_merge[(warp * 32 + n * 4 + i) * 32 + lane] = sc[n][i];
+            __syncthreads();
+#pragma unroll
+            for (int n = 0; n < 8; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float sum = attn_merge[(n * 4 + i) * 32 + lane];
+                    for (int w = 1; w < CS; ++w) sum += attn_merge[(w * 32 + n * 4 + i) * 32 + lane];
+                    sc[n][i] = sum;
+                }
         }
         // ---- online softmax on the fragments: rows g (values 0, 1) and g + 8 (values 2, 3) ----
         float mx_a = -INFINITY, mx_b = -INFINITY;
@@ -151,7 +178,7 @@ attention_e5m2_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int key = kk + (i & 1) + 8 * (i >> 1);
-                    x[i] = (w < WPR && key < seq_len) ? __ldg(v + (size_t)key * WPR + w) : 0u;
+                    x[i] = (w < DS / 4 && key < seq_len) ? __ldg(v + (size_t)key * WPR + woff + w) : 0u;
                 }
                 // bytes (col0: key a, key b, col1: key a, key b), then the E5M2 byte -> FP16 spread
                 uint32_t b0[4], b1[4];
@@ -166,7 +193,7 @@ attention_e5m2_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict
             }
         }
     }
-    if (n_split > 1) {
+    if (CS == 1 && n_split > 1) {
         // ---- merge the warps' partial results: [warp][row][col] sums, then [warp][row] m and l ----
         float* so = attn_merge + (size_t)warp * (16 * D + 32);
 #pragma unroll
@@ -212,13 +239,13 @@ attention_e5m2_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
             const int col = 32 * c + 4 * (2 * t + e);
-            if (col < D) {
+            if (col < DS) {
                 if (row_a < seq_len)
-                    *reinterpret_cast<float4*>(out + (size_t)row_a * D + col) = make_float4(
+                    *reinterpret_cast<float4*>(out + (size_t)row_a * D + 4 * woff + col) = make_float4(
                         __fdiv_rn(o[4 * c][e], l_a), __fdiv_rn(o[4 * c + 1][e], l_a),
                         __fdiv_rn(o[4 * c + 2][e], l_a), __fdiv_rn(o[4 * c + 3][e], l_a));
                 if (row_b < seq_len)
-                    *reinterpret_cast<float4*>(out + (size_t)row_b * D + col) = make_float4(
+                    *reinterpret_cast<float4*>(out + (size_t)row_b * D + 4 * woff + col) = make_float4(
                         __fdiv_rn(o[4 * c][2 + e], l_b), __fdiv_rn(o[4 * c + 1][2 + e], l_b),
                         __fdiv_rn(o[4 * c + 2][2 + e], l_b), __fdiv_rn(o[4 * c + 3][2 + e], l_b));
             }

@@ -484,18 +484,25 @@ static int gemv_multi_dispatch(const uint32_t* m, const uint32_t* v, float* out,
 template <int D>
 static int attention_launch(const uint32_t* q, const uint32_t* k, const uint32_t* v, float* out,
                             long long seq_len, const DeviceInfo& dev, cudaStream_t s) {
-    auto kernel = attention_e5m2_kernel<D>;
-    // one CTA per 16 queries; 1, 2, 4 or 8 warps per CTA split the key tiles, so that short
-    // sequences still put a few warps on every scheduler (4 per SM); the merge buffer stays
-    // within the 48 KiB of shared memory a kernel gets without asking
-    const long long grid = (seq_len + 15) / 16;
+    const long long grid = (seq_len + 15) / 16;   // one CTA per 16 queries
+    if (D > 128) {
+        // wide rows: D / 128 warps per CTA, each owning 128 columns
+        constexpr int kSplits = D > 128 ? D / 128 : 1;
+        attention_e5m2_kernel<D, kSplits><<<(unsigned)grid, 32 * kSplits, kSplits * 1024 * sizeof(float), s>>>(
+            q, k, v, out, (int)seq_len);
+        return launch_status();
+    }
+    // 1, 2, 4 or 8 warps per CTA split the key tiles, so that short sequences still put a
+    // few warps on every scheduler (4 per SM); the merge buffer stays within the 48 KiB of
+    // shared memory a kernel gets without asking
     const long long tiles = (seq_len + kAttnTile - 1) / kAttnTile;
     int warps = 1;
     while (warps < 8 && grid * warps < 8ll * dev.sm_count && 2 * warps <= tiles &&
            2 * warps * (16 * D + 32) * sizeof(float) <= 48 * 1024)
         warps <<= 1;
     const size_t smem = warps > 1 ? (size_t)warps * (16 * D + 32) * sizeof(float) : 0;
-    kernel<<<(unsigned)grid, 32 * warps, smem, s>>>(q, k, v, out, (int)seq_len);
+    attention_e5m2_kernel<(D > 128 ? 128 : D), 1><<<(unsigned)grid, 32 * warps, smem, s>>>(q, k, v, out,
+                                                                                         (int)seq_len);
     return launch_status();
 }
 
@@ -652,7 +659,7 @@ int feather_decode_fp8(const uint32_t* src, float* dst, int64_t n_elems, int mod
 
 int feather_attention_fp8_e5m2(const uint32_t* q, const uint32_t* k, const uint32_t* v, float* out,
                                int64_t seq_len, int64_t h_dim_words, void* stream) {
-    if (seq_len < 0 || h_dim_words <= 0 || seq_len > 0x7FFFFFFF / 128) return FEATHER_ERR_BAD_ARG;
+    if (seq_len < 0 || h_dim_words <= 0 || seq_len > 0x7FFFFFFF / 512) return FEATHER_ERR_BAD_ARG;
     if (seq_len == 0) return FEATHER_OK;
     if (!q || !k || !v || !out) return FEATHER_ERR_BAD_ARG;
     if (!aligned(q, 4) || !aligned(k, 4) || !aligned(v, 4) || !aligned(out, 16)) return FEATHER_ERR_MISALIGNED;
@@ -664,7 +671,9 @@ int feather_attention_fp8_e5m2(const uint32_t* q, const uint32_t* k, const uint3
         case 8: return attention_launch<32>(q, k, v, out, seq_len, *dev, s);
         case 16: return attention_launch<64>(q, k, v, out, seq_len, *dev, s);
         case 32: return attention_launch<128>(q, k, v, out, seq_len, *dev, s);
-        default: return h_dim_words > 32 ? FEATHER_ERR_TOO_LARGE : FEATHER_ERR_BAD_ARG;
+        case 64: return attention_launch<256>(q, k, v, out, seq_len, *dev, s);
+        case 128: return attention_launch<512>(q, k, v, out, seq_len, *dev, s);
+        default: return h_dim_words > 128 ? FEATHER_ERR_TOO_LARGE : FEATHER_ERR_BAD_ARG;
     }
 }
 

@@ -22,8 +22,8 @@ def flash_attention_fp8_e5m2_acc_fp32_gpu(q: torch.Tensor, k: torch.Tensor, v: t
                                           seq_len: int, h_dim: int,
                                           out: torch.Tensor | None = None) -> torch.Tensor:
     seq_len, h_dim = int(seq_len), int(h_dim)
-    if seq_len < 0 or h_dim not in (4, 8, 16, 32):
-        raise ValueError("h_dim (packed words per row) must be 4, 8, 16 or 32 and seq_len >= 0")
+    if seq_len < 0 or h_dim not in (4, 8, 16, 32, 64, 128):
+        raise ValueError("h_dim (packed words per row) must be a power of two from 4 to 128 and seq_len >= 0")
     with torch._C.DisableTorchFunctionSubclass():
         q, k, v = as_words(q, "q"), as_words(k, "k"), as_words(v, "v")
         need = seq_len * h_dim

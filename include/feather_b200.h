@@ -89,9 +89,10 @@ int feather_decode_fp8(const uint32_t* src, float* dst, int64_t n_elems, int mod
  * the textbook result (the reference's README lists the routine as unfinished).
  *   q, k, v      seq_len rows of h_dim_words packed words each
  *   out          seq_len x (4 * h_dim_words) floats, 16-byte aligned
- *   h_dim_words  4, 8, 16 or 32 (d = 16 .. 128); larger powers of two, which
- *                the reference accepts, return FEATHER_ERR_TOO_LARGE, anything
- *                else FEATHER_ERR_BAD_ARG
+ *   h_dim_words  a power of two from 4 to 128 (d = 16 .. 512, which covers the
+ *                reference's benchmark shapes 64, 256 and 512); larger powers
+ *                of two return FEATHER_ERR_TOO_LARGE, anything else
+ *                FEATHER_ERR_BAD_ARG
  */
 int feather_attention_fp8_e5m2(const uint32_t* q, const uint32_t* k, const uint32_t* v, float* out,
                                int64_t seq_len, int64_t h_dim_words, void* stream);

@@ -124,7 +124,8 @@ def make_attention() -> None:
     function under the autotuner, launched as the wrapper does, attention.py:172-178):
     N(0, 1) inputs at sequence lengths that do and do not fill the last key tile."""
     a = {}
-    for seq, d, seed in ((128, 64, 51), (100, 32, 52), (200, 128, 53), (64, 16, 54)):
+    for seq, d, seed in ((128, 64, 51), (100, 32, 52), (200, 128, 53), (64, 16, 54), (130, 256, 55),
+                         (64, 512, 56)):
         rng = np.random.default_rng(seed)
         q, k, v = (ref_pack(rng.standard_normal((seq, d)).astype(np.float16), "E5M2") for _ in range(3))
         tq, tk, tv = (torch.from_numpy(x.view(np.int32).copy()) for x in (q, k, v))

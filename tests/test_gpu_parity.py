@@ -759,7 +759,8 @@ def test_gemv_multi_rejects(fb):
 
 # ------------------------------------------------------------------ attention --
 @pytest.mark.parametrize("seq,d", [(128, 64), (100, 32), (200, 128), (64, 16), (1, 64), (1000, 128),
-                                   (4096, 64), (2500, 32), (8192, 128)])
+                                   (4096, 64), (2500, 32), (8192, 128), (130, 256), (64, 512),
+                                   (1024, 256), (777, 512), (4096, 512)])
 def test_attention_vs_oracle_and_reference_outputs(fb, golden, seq, d):
     """Packed-E5M2 attention against the oracle (same tiles, same FP16 rounding of the
     probabilities), the reference kernel's own outputs where the fixture has them, and
@@ -796,6 +797,6 @@ def test_attention_rejects(fb):
         attn(w, w, w[:100], 64, 16)
     lib = fb._lib.load()
     p = w.data_ptr()
-    assert lib.feather_attention_fp8_e5m2(p, p, p, p, 64, 64, None) == -8
+    assert lib.feather_attention_fp8_e5m2(p, p, p, p, 64, 256, None) == -8
     assert lib.feather_attention_fp8_e5m2(p, p, p, p, 64, 5, None) == -1
     assert lib.feather_attention_fp8_e5m2(p, p, p, p + 4, 64, 16, None) == -2

@@ -198,7 +198,7 @@ def test_relu_matches_reference_kernel(golden):
 
 
 # ------------------------------------------------------------------ attention --
-@pytest.mark.parametrize("seq,d", [(128, 64), (100, 32), (200, 128), (64, 16)])
+@pytest.mark.parametrize("seq,d", [(128, 64), (100, 32), (200, 128), (64, 16), (130, 256), (64, 512)])
 def test_attention_matches_reference_kernel(golden, seq, d):
     """The restated attention (attention.py:14-108) against the reference kernel run
     through Triton's interpreter, including sequence lengths that leave the last key
