@@ -23,7 +23,7 @@ from .routines.gemv import (gemv_fp8_acc_fp32_gpu, gemv_fp8_e4m3_acc_fp32_gpu,
                             gemv_fp8_e5m2_acc_fp32_gpu, gemv_fp8_multi_acc_fp32_gpu,
                             gemv_fp8_ret_packed_gpu)
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 __all__ = ["pack_fp8_tensor", "unpack_fp8_tensor", "gemv", "dot", "PackedFP8", "device_status",
            "gemv_fp8_acc_fp32_gpu", "gemv_fp8_e5m2_acc_fp32_gpu", "gemv_fp8_e4m3_acc_fp32_gpu",
            "gemv_fp8_ret_packed_gpu", "gemv_fp8_multi_acc_fp32_gpu", "dot_fp8_acc_fp32_gpu", "dot_fp8_e5m2_acc_fp32_gpu", "dot_fp8_e4m3_acc_fp32_gpu"]

@@ -605,7 +605,7 @@ using namespace feather;
 
 extern "C" {
 
-int feather_version(void) { return 100; /* 0.1.0 */ }
+int feather_version(void) { return 200; /* 0.2.0: + packed-output, multi-vector and all-reduce GEMV, ReLU, attention */ }
 
 const char* feather_strerror(int status) {
     switch (status) {
@@ -617,7 +617,7 @@ const char* feather_strerror(int status) {
         case FEATHER_ERR_LAUNCH: return "CUDA reported an error at launch";
         case FEATHER_ERR_WORKSPACE: return "workspace is missing or too small";
         case FEATHER_ERR_TIMEOUT: return "a bounded device-side wait gave up";
-        case FEATHER_ERR_TOO_LARGE: return "size exceeds what the built-in scratch of the no-allocation entry point covers";
+        case FEATHER_ERR_TOO_LARGE: return "size exceeds what this entry point covers (built-in scratch, inbox, resident grid or model dimension)";
         default: return "unknown feather status";
     }
 }
