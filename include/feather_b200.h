@@ -35,7 +35,7 @@ typedef enum feather_status {
     FEATHER_ERR_LAUNCH = -5,      /* CUDA reported a launch error               */
     FEATHER_ERR_WORKSPACE = -6,   /* workspace missing or too small             */
     FEATHER_ERR_TIMEOUT = -7,     /* a bounded device-side wait gave up         */
-    FEATHER_ERR_TOO_LARGE = -8    /* beyond the built-in scratch of a *_static call */
+    FEATHER_ERR_TOO_LARGE = -8    /* beyond what the entry point covers: built-in scratch, inbox, resident grid, model dimension */
 } feather_status;
 
 #define FEATHER_MODE_E5M2 0
