@@ -86,3 +86,13 @@ def test_python_surface_without_gpu():
         with pytest.raises(ValueError):
             feather.gemv(torch.zeros(4, dtype=torch.int32), torch.zeros(1, dtype=torch.int32),
                          original_shape=(4, 4))
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 on its own (no C++, no
+    CUDA or torch types), which is what a cgo / FFI binding would consume."""
+    import subprocess
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "feather_b200.h"\nint main(void) { return feather_version() == 0; }\n')
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only",
+                    "-I", os.path.join(ROOT, "include"), str(src)], check=True)
