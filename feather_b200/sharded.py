@@ -319,8 +319,9 @@ class PeerAllReduce:
         self.world_size, self.rank = dist.get_world_size(group), dist.get_rank(group)
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.device, self.max_rows = dev, int(max_rows)
-        error = None
+        error, self._mapped = None, []
         try:
+            self._lib = _lib.load()
             if self.world_size > 16:
                 raise ValueError("the fused all-reduce supports at most 16 ranks")
             # two halves x world slots x (sum, tag) pairs for max_rows rounded up to 16
@@ -338,7 +339,6 @@ class PeerAllReduce:
         arr = ctypes.c_void_p * self.world_size
         self.inbox_ptrs = arr(*base)
         self.flag_ptrs = arr(*[b + 4 * self.inbox_floats for b in base])
-        self._lib = _lib.load()
 
     def close(self, collective: bool = True) -> None:
         """Unmap the peers' buffers.  Call on every rank after the last result
