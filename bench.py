@@ -11,9 +11,10 @@ matrix + packed vector + FP32 output, divided by time), whole job.
   step finds its matrix in the 126 MB L2.
 * N > 1 (launched by torch.distributed.run, one rank per GPU): the row-sharded
   E5M2 GEMV, 65536 x 65536 (4 GiB packed), rows split in contiguous blocks,
-  vector replicated, output slices exchanged with an NCCL all-gather.  A step
-  is local GEMV + all-gather; time is the max over ranks.  Total work is fixed
-  ("strong" scaling).
+  vector replicated, output slices exchanged inside the GEMV kernel through
+  peer-mapped buffers (the same step with an NCCL all-gather is reported in
+  "extra").  A step is one call of the sharded operator; time is the max over
+  ranks.  Total work is fixed ("strong" scaling).
 * --impl reference: the reference's CPU path (decode with the kernel bit
   semantics + FP32 matvec, the C restatement in oracle/) on the host cores.
 
