@@ -39,12 +39,25 @@ SYMBOLS = {
     "feather_ipc_close": (_i32, [_vp, _i64]),
     "feather_device_status": (_i32, [_vp]),
     "feather_set_wait_limit_ms": (_i32, [_i32]),
+    "feather_set_tuning": (_i32, [ctypes.c_char_p]),
+    "feather_gemv_chain_plan_bytes": (_i64, [_i32]),
+    "feather_gemv_chain_plan": (_i32, [_vp, _i32, _vp, _i64, _vp]),
+    "feather_gemv_chain_fp8": (_i32, [_vp, _i32, ctypes.c_uint32, _vp]),
     "feather_gemv_fp8_ex": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, ctypes.c_uint32, _vp]),
     "feather_dot_fp8": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _vp]),
     "feather_dot_workspace_bytes": (_i64, [_i64]),
     "feather_dot_fp8_static": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp]),
     "feather_dot_fp8_static_max_words": (_i64, []),
 }
+
+
+
+class ChainOp(ctypes.Structure):
+    """feather_chain_op of include/feather_b200.h."""
+    _fields_ = [("m", _vp), ("v", _vp), ("out", _vp), ("M", ctypes.c_int32), ("N", ctypes.c_int32),
+                ("mode", ctypes.c_int32), ("out_mode", ctypes.c_int32), ("wait_op", ctypes.c_int32),
+                ("reserved", ctypes.c_int32)]
+
 
 _lib = None
 

@@ -91,6 +91,100 @@ class GemvChain:
         return sum(m * n + n + 4 * m for _, _, (m, n), _ in self.ops)
 
 
+class PersistentGemvChain:
+    """A table of GEMVs run by ONE persistent kernel launch
+    (``feather_gemv_chain_fp8``): the matrix stream does not stop at the op
+    boundaries, which is what the 155 separate launches of ``GemvChain`` pay for.
+
+    ``ops`` is a list of dicts with keys ``m`` (packed matrix), ``v`` (packed
+    vector), ``shape`` (unpacked (M, N)), optional ``mode`` (default the
+    chain's), ``out`` (float32 (M,) tensor, or packed words with ``out_mode``),
+    ``out_mode`` (None = FP32 sums, else "E5M2"/"E4M3": the sums re-encoded,
+    bit for bit ``gemv_fp8_ret_packed_gpu``) and ``wait_op`` (index of the
+    earlier op that writes ``v``).  Missing outputs are allocated.  Every op's
+    result has the bits of the single-op call on the same operands.
+    """
+
+    def __init__(self, ops, mode: str = "E4M3", static_matrix: bool = True):
+        import ctypes
+        from ._lib import ChainOp
+        from .packers.fp8 import as_words
+        if not ops:
+            raise ValueError("the chain needs at least one op")
+        self.lib = fb._lib.load()
+        self.static_matrix = static_matrix
+        self.outs, self._keep = [], []
+        table = (ChainOp * len(ops))()
+        device = None
+        for i, op in enumerate(ops):
+            m, v = as_words(op["m"], "m"), as_words(op["v"], "v")
+            M, N = int(op["shape"][0]), int(op["shape"][1])
+            device = m.device if device is None else device
+            if m.device != device or v.device != device:
+                raise ValueError("all operands of a chain live on one device")
+            if m.numel() < M * (N // 4) or v.numel() < N // 4:
+                raise ValueError(f"op {i}: operands are shorter than {M}x{N} needs")
+            out_mode = op.get("out_mode")
+            out = op.get("out")
+            if out is None:
+                out = (torch.empty(M, dtype=torch.float32, device=device) if out_mode is None
+                       else torch.empty((M + 3) // 4, dtype=torch.int32, device=device).view(torch.uint32))
+            elif out_mode is None:
+                if out.dtype != torch.float32 or out.numel() != M or out.device != device or not out.is_contiguous():
+                    raise ValueError(f"op {i}: out must be a contiguous float32 tensor of M elements")
+            else:
+                out = as_words(out, "out")
+                if out.numel() != (M + 3) // 4 or out.device != device:
+                    raise ValueError(f"op {i}: out must hold ceil(M / 4) packed words")
+            self.outs.append(out)
+            self._keep.append((m, v))
+            t = table[i]
+            t.m, t.v, t.out = m.data_ptr(), v.data_ptr(), out.data_ptr()
+            t.M, t.N = M, N
+            t.mode = fb._lib.mode_id(op.get("mode", mode))
+            t.out_mode = -1 if out_mode is None else fb._lib.mode_id(out_mode)
+            t.wait_op = int(op.get("wait_op", -1))
+            t.reserved = 0
+        self.n_ops, self.device = len(ops), device
+        nbytes = int(self.lib.feather_gemv_chain_plan_bytes(self.n_ops))
+        self.plan = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        with torch.cuda.device(device):
+            fb._lib.check(self.lib.feather_gemv_chain_plan(
+                ctypes.cast(table, ctypes.c_void_p), self.n_ops, self.plan.data_ptr(), nbytes,
+                fb._lib.current_stream_ptr(device.index)))
+
+    def token(self) -> None:
+        idx = self.device.index
+        with torch.cuda.device(idx):
+            fb._lib.check(self.lib.feather_gemv_chain_fp8(self.plan.data_ptr(), self.n_ops,
+                                                          1 if self.static_matrix else 0,
+                                                          fb._lib.current_stream_ptr(idx)))
+
+    __call__ = token
+
+    @classmethod
+    def from_chain(cls, chain: "GemvChain", dependent: bool = False) -> "PersistentGemvChain":
+        """The ops of a ``GemvChain`` as one launch.  ``dependent=False``: the same
+        independent GEMVs on the chain's fixed activations.  ``dependent=True``: a real
+        dependency chain -- every op writes packed FP8 and every op whose input
+        length matches the latest packed output of that length reads it (and
+        waits for the op that wrote it)."""
+        ops, last = [], {}
+        for i, ((w, a, (m, n), out), words) in enumerate(zip(chain.ops, chain.packed)):
+            op = {"m": w, "v": a, "shape": (m, n)}
+            if dependent:
+                op.update(out=words, out_mode=chain.mode)
+                if n in last:
+                    op.update(v=last[n][1], wait_op=last[n][0])
+                last[m] = (i, words)
+            elif chain.reencode == "fused":
+                op.update(out=words, out_mode=chain.mode)
+            else:
+                op.update(out=out)
+            ops.append(op)
+        return cls(ops, chain.mode, chain.static_matrix)
+
+
 class TensorParallelChain:
     """The same chain split over the ranks of a process group (one process per GPU).
 
@@ -229,20 +323,28 @@ def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", gro
 
 
 def measure(tokens: int = 50, use_graph: bool = True, mode: str = "E4M3",
-            merge_projections: bool = False, reencode: str | None = None) -> dict:
+            merge_projections: bool = False, reencode: str | None = None,
+            persistent: str | None = None) -> dict:
+    """``persistent``: None = one launch per GEMV; "independent" / "dependent" =
+    the whole token as one persistent launch (PersistentGemvChain.from_chain)."""
     chain = GemvChain(mode, merge_projections=merge_projections, reencode=reencode)
+    step = chain.token
+    if persistent is not None:
+        step = PersistentGemvChain.from_chain(chain, dependent=persistent == "dependent").token
     for _ in range(3):
-        chain.token()
+        step()
     torch.cuda.synchronize()
-    run = chain.token
+    if persistent is not None:
+        fb.device_status()
+    run = step
     if use_graph:
         stream = torch.cuda.Stream()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(stream):
-            chain.token()
+            step()
             torch.cuda.synchronize()
             with torch.cuda.graph(graph, stream=stream):
-                chain.token()
+                step()
         run = graph.replay
         run()
         torch.cuda.synchronize()
@@ -255,9 +357,10 @@ def measure(tokens: int = 50, use_graph: bool = True, mode: str = "E4M3",
     ms = start.elapsed_time(end) / tokens
     nbytes = chain.bytes_per_token()
     return {"tokens_per_s": round(1e3 / ms, 1), "us_per_token": round(ms * 1e3, 1),
-            "gemvs_per_token": len(chain.ops), "GB/s": round(nbytes / ms / 1e6, 1),
+            "gemvs_per_token": len(chain.ops), "launches_per_token": 1 if persistent else len(chain.ops),
+            "GB/s": round(nbytes / ms / 1e6, 1),
             "bytes_per_token": nbytes, "cuda_graph": use_graph, "mode": mode,
-            "merged_projections": merge_projections, "reencode": reencode}
+            "merged_projections": merge_projections, "reencode": reencode, "persistent": persistent}
 
 
 if __name__ == "__main__":

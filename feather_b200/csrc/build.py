@@ -16,10 +16,17 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 LIB = os.path.join(PKG, "libfeather_b200.so")
 SOURCES = ["feather_b200.cu"]
-HEADERS = ["fp8_codec.cuh", "gemv_common.cuh", "gemv_kernels.cuh", "gemv_ring.cuh", "dot_kernels.cuh",
-           os.path.join("..", "..", "include", "feather_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--use_fast_math=false", "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared"]
+              "-Xcompiler", "-fPIC", "-shared", "-cudart", "shared"]
+
+
+def dependencies() -> list:
+    """Every file the library is built from: all kernel sources and headers in
+    this directory plus the public C header."""
+    import glob
+    deps = sorted(glob.glob(os.path.join(HERE, "*.cu")) + glob.glob(os.path.join(HERE, "*.cuh")))
+    deps.append(os.path.join(os.path.dirname(PKG), "include", "feather_b200.h"))
+    return deps
 
 
 def _nvcc() -> str:
@@ -33,15 +40,13 @@ def is_stale() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(HERE, f) for f in SOURCES + HEADERS]
-    return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
+    return any(os.path.getmtime(d) > t for d in dependencies() if os.path.exists(d))
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, extra_flags=()) -> str:
     if not force and not is_stale():
         return LIB
-    flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
-    cmd = [_nvcc(), *flags, *(["-Xptxas", "-v"] if verbose else []), "-o", LIB,
+    cmd = [_nvcc(), *NVCC_FLAGS, *extra_flags, *(["-Xptxas", "-v"] if verbose else []), "-o", LIB,
            *[os.path.join(HERE, s) for s in SOURCES]]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode:

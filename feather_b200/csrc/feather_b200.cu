@@ -4,18 +4,74 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
+#include <memory>
+#include <mutex>
+#include <new>
 
 #include "../../include/feather_b200.h"
 #include "attention_kernels.cuh"
 #include "dot_kernels.cuh"
 #include "fp8_codec.cuh"
+#include "gemv_chain.cuh"
 #include "gemv_kernels.cuh"
 #include "gemv_multi.cuh"
 #include "gemv_mma.cuh"
 #include "gemv_ring.cuh"
 
 namespace feather {
+
+// ------------------------------------------------------------ tuning -------
+// Knobs for A/B runs in benchmarks, never needed for correct results.  Set by
+// feather_set_tuning("key=value,key=value") or, once, from the environment
+// variable FEATHER_KERNEL when the library first touches a device.
+//   ring_pre_kb      KiB of a CTA's first rows the ring kernel asks L2 for ahead
+//                    of its stream-order wait (0 = none)
+//   rows_pre         1: the warp-owned-rows kernel does the same for its first batch
+//   dot_unroll       16-byte loads per operand a dot thread keeps in flight (1, 2, 4)
+//   dot_ctas_per_sm  grid of the dot kernel, in CTAs per SM
+//   ring_pre_kb_e4m3 the same for E4M3 matrices; -1 = 64 KiB for matrices up to 128 MiB,
+//                    none above (measured: the decode-bound kernel loses there)
+//   dot_ring         0: register-load dot kernel only; 1, 2, 3: long aligned operands take the
+//                    bulk-copy ring kernel with 6 x 32 KiB, 3 x 64 KiB or 12 x 16 KiB stages
+//   dot_pre_kb       KiB the dot ring kernel asks L2 for ahead of its stream-order wait
+struct Tuning {
+    std::atomic<int> ring_pre_kb{128};
+    std::atomic<int> rows_pre{1};
+    std::atomic<int> dot_unroll{4};
+    std::atomic<int> dot_ctas_per_sm{6};
+    std::atomic<int> dot_ring{1};
+    std::atomic<int> dot_pre_kb{128};
+    std::atomic<int> ring_pre_kb_e4m3{-1};
+};
+static Tuning g_tune;
+
+static int apply_tuning(const char* spec) {
+    if (!spec) return FEATHER_ERR_BAD_ARG;
+    const char* p = spec;
+    while (*p) {
+        while (*p == ',' || *p == ' ') ++p;
+        if (!*p) break;
+        const char* eq = strchr(p, '=');
+        if (!eq) return FEATHER_ERR_BAD_ARG;
+        const size_t klen = (size_t)(eq - p);
+        char* end = nullptr;
+        const long val = strtol(eq + 1, &end, 10);
+        if (end == eq + 1 || (*end && *end != ',' && *end != ' ')) return FEATHER_ERR_BAD_ARG;
+        auto is = [&](const char* k) { return strlen(k) == klen && strncmp(p, k, klen) == 0; };
+        if (is("ring_pre_kb") && val >= 0 && val <= 16384) g_tune.ring_pre_kb = (int)val;
+        else if (is("rows_pre") && (val == 0 || val == 1)) g_tune.rows_pre = (int)val;
+        else if (is("dot_unroll") && (val == 1 || val == 2 || val == 4)) g_tune.dot_unroll = (int)val;
+        else if (is("dot_ctas_per_sm") && val >= 1 && val <= 16) g_tune.dot_ctas_per_sm = (int)val;
+        else if (is("dot_ring") && val >= 0 && val <= 3) g_tune.dot_ring = (int)val;
+        else if (is("dot_pre_kb") && val >= 0 && val <= 16384) g_tune.dot_pre_kb = (int)val;
+        else if (is("ring_pre_kb_e4m3") && val >= -1 && val <= 16384) g_tune.ring_pre_kb_e4m3 = (int)val;
+        else return FEATHER_ERR_BAD_ARG;
+        p = end;
+    }
+    return FEATHER_OK;
+}
 
 // ------------------------------------------------------------ encode -------
 // One thread per 16 elements: 128-bit loads of the source, one 128-bit store
@@ -164,6 +220,10 @@ struct DeviceInfo {
 static DeviceInfo g_dev[64];
 
 static int device_info(const DeviceInfo** info) {
+    static std::once_flag env_once;
+    std::call_once(env_once, [] {
+        if (const char* spec = getenv("FEATHER_KERNEL")) apply_tuning(spec);  // a bad spec is ignored
+    });
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FEATHER_ERR_LAUNCH;
     DeviceInfo& d = g_dev[dev];
@@ -245,6 +305,17 @@ static int ensure_smem(K kernel, int smem, std::atomic<unsigned long long>& conf
     return FEATHER_OK;
 }
 
+// Bytes of a CTA's first rows the ring kernel asks L2 for ahead of its
+// stream-order wait.  Measured on B200, back-to-back calls: E5M2 gains ~1 us per
+// call with 64-128 KiB (more than 512 KiB per CTA overflows L2 and loses); E4M3,
+// bound by decode issue, gains on matrices up to 128 MiB and loses above.
+static int ring_pre_bytes(int mode, long long M, long long N) {
+    if (mode == kE5M2) return g_tune.ring_pre_kb.load(std::memory_order_relaxed) * 1024;
+    const int e4 = g_tune.ring_pre_kb_e4m3.load(std::memory_order_relaxed);
+    if (e4 >= 0) return e4 * 1024;
+    return M * N <= (128ll << 20) ? 64 * 1024 : 0;
+}
+
 template <int MODE, bool FUSED, bool EARLY = false>
 static int gemv_ring_launch(const uint32_t* m, const uint32_t* v, float* out, long long M,
                             long long N, const DeviceInfo& dev, cudaStream_t s,
@@ -270,7 +341,8 @@ static int gemv_ring_launch(const uint32_t* m, const uint32_t* v, float* out, lo
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const unsigned char*>(m),
-                                             v, out, (int)M, (int)(N / 16), status, shard);
+                                             v, out, (int)M, (int)(N / 16), status,
+                                             ring_pre_bytes(MODE, M, N), shard);
     return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
 }
 
@@ -300,7 +372,8 @@ static int gemv_rows_launch(const uint32_t* m, const uint32_t* v, float* out, lo
     cfg.numAttrs = 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const uint4*>(m), v, out,
                                              (int)M, (int)(N / 16), out_code, NoAllReduce{},
-                                             static_cast<unsigned int*>(nullptr));
+                                             static_cast<unsigned int*>(nullptr),
+                                             g_tune.rows_pre.load(std::memory_order_relaxed));
     return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
 }
 
@@ -334,7 +407,7 @@ static int gemv_allreduce_launch(const uint32_t* m, const uint32_t* v, long long
     cfg.numAttrs = 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, reinterpret_cast<const uint4*>(m), v,
                                              static_cast<float*>(nullptr), (int)M, (int)(N / 16), -1, ar,
-                                             status);
+                                             status, 0);
     return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
 }
 
@@ -528,23 +601,89 @@ static int decode_launch(const uint32_t* src, float* dst, long long n_elems, int
     return launch_status();
 }
 
+// One launch of the dot kernel.  The grid is CTAs-per-SM x SMs, never more CTAs
+// than fit the GPU at once (the kernel walks the operands grid-strided, so a
+// second wave would only add imbalance), than there is work for, or than
+// `max_ctas` partial-sum slots.
+template <int MODE, bool VEC, int UNROLL>
+static int dot_launch_as(const uint32_t* a, const uint32_t* b, float* out, unsigned int* ticket,
+                         float* partial, long long n_words, long long max_ctas,
+                         const DeviceInfo& dev, cudaStream_t s) {
+    auto kernel = dot_kernel<MODE, VEC, UNROLL>;
+    static std::atomic<int> resident[64];
+    int devid = 0;
+    if (cudaGetDevice(&devid) != cudaSuccess || devid < 0 || devid >= 64) return FEATHER_ERR_LAUNCH;
+    int per_sm = resident[devid].load(std::memory_order_acquire);
+    if (per_sm == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kDotThreads, 0) != cudaSuccess ||
+            per_sm < 1)
+            return FEATHER_ERR_LAUNCH;
+        resident[devid].store(per_sm, std::memory_order_release);
+    }
+    const int want = g_tune.dot_ctas_per_sm.load(std::memory_order_relaxed);
+    long long grid = (long long)dev.sm_count * (want < per_sm ? want : per_sm);
+    const long long need = (n_words / 4 + kDotThreads - 1) / kDotThreads;
+    if (grid > need) grid = need;
+    if (grid < 1) grid = 1;
+    if (grid > max_ctas) grid = max_ctas;
+    kernel<<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket, partial, n_words);
+    return launch_status();
+}
+
+// Long operands: the bulk-copy ring kernel, one CTA per SM.
+template <int MODE, int STAGES, int STAGE_CHUNKS>
+static int dot_ring_launch(const uint32_t* a, const uint32_t* b, float* out, unsigned int* ticket,
+                           float* partial, long long n_words, long long max_ctas,
+                           const DeviceInfo& dev, cudaStream_t s) {
+    auto kernel = dot_ring_kernel<MODE, STAGES, STAGE_CHUNKS>;
+    constexpr int kSmem = dot_ring_smem_bytes(STAGES, STAGE_CHUNKS);
+    static std::atomic<unsigned long long> configured{0};
+    if (int st = ensure_smem(kernel, kSmem, configured)) return st;
+    unsigned int* status = nullptr;
+    if (int st = status_word(&status)) return st;
+    long long grid = dev.sm_count;
+    if (grid > max_ctas) grid = max_ctas;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kDotRingThreads);
+    cfg.dynamicSmemBytes = kSmem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, a, b, out, ticket, partial, n_words, status,
+                                             g_tune.dot_pre_kb.load(std::memory_order_relaxed) * 1024);
+    return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
+}
+
+template <int MODE>
+static int dot_launch_any(const uint32_t* a, const uint32_t* b, float* out, unsigned int* ticket,
+                          float* partial, long long n_words, long long max_ctas,
+                          const DeviceInfo& dev, cudaStream_t s) {
+    if (!(aligned(a, 16) && aligned(b, 16)))
+        return dot_launch_as<MODE, false, 1>(a, b, out, ticket, partial, n_words, max_ctas, dev, s);
+    // at least four full stages for every CTA of the ring kernel
+    const int ring = g_tune.dot_ring.load(std::memory_order_relaxed);
+    if (ring && (n_words >> 2) >= 8192ll * dev.sm_count) {
+        if (ring == 2) return dot_ring_launch<MODE, 3, 2048>(a, b, out, ticket, partial, n_words, max_ctas, dev, s);
+        if (ring == 3) return dot_ring_launch<MODE, 12, 512>(a, b, out, ticket, partial, n_words, max_ctas, dev, s);
+        return dot_ring_launch<MODE, 6, 1024>(a, b, out, ticket, partial, n_words, max_ctas, dev, s);
+    }
+    switch (g_tune.dot_unroll.load(std::memory_order_relaxed)) {
+        case 1: return dot_launch_as<MODE, true, 1>(a, b, out, ticket, partial, n_words, max_ctas, dev, s);
+        case 2: return dot_launch_as<MODE, true, 2>(a, b, out, ticket, partial, n_words, max_ctas, dev, s);
+        default: return dot_launch_as<MODE, true, 4>(a, b, out, ticket, partial, n_words, max_ctas, dev, s);
+    }
+}
+
 template <int MODE>
 static int dot_launch(const uint32_t* a, const uint32_t* b, float* out, void* workspace,
                       long long n_words, const DeviceInfo& dev, cudaStream_t s) {
     unsigned int* ticket = reinterpret_cast<unsigned int*>(workspace);
     float* partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + 16);
-    long long grid = (long long)dev.sm_count * 6;  // measured best on B200 (sweep 2..12 per SM)
-    const long long need = (n_words / 4 + kDotThreads - 1) / kDotThreads;
-    if (grid > need) grid = need;
-    if (grid < 1) grid = 1;
-    if (grid > kDotMaxCtas) grid = kDotMaxCtas;
-    if (aligned(a, 16) && aligned(b, 16))
-        dot_kernel<MODE, true, 1><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket, partial,
-                                                                          n_words);
-    else
-        dot_kernel<MODE, false, 1><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket,
-                                                                           partial, n_words);
-    return launch_status();
+    return dot_launch_any<MODE>(a, b, out, ticket, partial, n_words, kDotMaxCtas, dev, s);
 }
 
 // ---------------------------------------------------- dot without allocation --
@@ -585,18 +724,9 @@ static int dot_static_launch(const uint32_t* a, const uint32_t* b, float* out, l
     if (cudaMemsetAsync(scratch, 0, 16, s) != cudaSuccess) return FEATHER_ERR_LAUNCH;
     unsigned int* ticket = reinterpret_cast<unsigned int*>(scratch);
     float* partial = reinterpret_cast<float*>(scratch + kStaticDotPartialOffset);
-    long long grid = (long long)dev.sm_count * 6;
-    const long long need = (n_words / 4 + kDotThreads - 1) / kDotThreads;
-    if (grid > need) grid = need;
-    if (grid < 1) grid = 1;
-    if (grid > kStaticDotSlots) grid = kStaticDotSlots;
-    if (aligned(a, 16) && aligned(b, 16))
-        dot_kernel<MODE, true, 1><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket, partial,
-                                                                          n_words);
-    else
-        dot_kernel<MODE, false, 1><<<(unsigned)grid, kDotThreads, 0, s>>>(a, b, out, ticket,
-                                                                           partial, n_words);
-    return launch_status();
+    // the same kernel and grid as feather_dot_fp8 (a B200's grid stays below the
+    // slot count), hence the same bits
+    return dot_launch_any<MODE>(a, b, out, ticket, partial, n_words, kStaticDotSlots, dev, s);
 }
 
 }  // namespace feather
@@ -940,6 +1070,92 @@ int feather_set_wait_limit_ms(int milliseconds) {
     return cudaMemcpyToSymbol(g_wait_limit_ns, &ns, sizeof(ns)) == cudaSuccess ? FEATHER_OK
                                                                                 : FEATHER_ERR_LAUNCH;
 }
+
+// ------------------------------------------------------- GEMV chain ----------
+// Plan buffer in device memory: [ticket + one counter per op, padded to 16 bytes | ops].
+static inline int64_t chain_counter_bytes(int64_t n_ops) { return ((n_ops + 1) * 4 + 15) / 16 * 16; }
+
+int64_t feather_gemv_chain_plan_bytes(int32_t n_ops) {
+    if (n_ops <= 0) return 0;
+    return chain_counter_bytes(n_ops) + (int64_t)n_ops * (int64_t)sizeof(ChainOp);
+}
+
+int feather_gemv_chain_plan(const feather_chain_op* ops, int32_t n_ops, void* plan, int64_t plan_bytes,
+                            void* stream) {
+    static_assert(sizeof(feather_chain_op) == sizeof(ChainOp), "public and device op records match");
+    if (!ops || n_ops <= 0 || !plan) return FEATHER_ERR_BAD_ARG;
+    if (plan_bytes < feather_gemv_chain_plan_bytes(n_ops)) return FEATHER_ERR_WORKSPACE;
+    if (!aligned(plan, 16)) return FEATHER_ERR_MISALIGNED;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    const int grid = dev->sm_count;   // the launch's grid: the row split is planned for it
+    std::unique_ptr<ChainOp[]> host(new (std::nothrow) ChainOp[n_ops]);
+    if (!host) return FEATHER_ERR_LAUNCH;
+    for (int i = 0; i < n_ops; ++i) {
+        const feather_chain_op& o = ops[i];
+        if (o.M <= 0 || o.N <= 0 || (o.N & 15) || !o.m || !o.v || !o.out) return FEATHER_ERR_BAD_ARG;
+        if (o.N > kChainTile) return FEATHER_ERR_TOO_LARGE;
+        if ((o.mode != FEATHER_MODE_E5M2 && o.mode != FEATHER_MODE_E4M3) ||
+            (o.out_mode != -1 && o.out_mode != FEATHER_MODE_E5M2 && o.out_mode != FEATHER_MODE_E4M3))
+            return FEATHER_ERR_MODE;
+        if (o.wait_op < -1 || o.wait_op >= i) return FEATHER_ERR_BAD_ARG;   // only EARLIER ops
+        if (!aligned(o.m, 16) || !aligned(o.v, 16) || !aligned(o.out, 4)) return FEATHER_ERR_MISALIGNED;
+        ChainOp& d = host[i];
+        d.m = static_cast<const unsigned char*>(static_cast<const void*>(o.m));
+        d.v = o.v;
+        d.out = o.out;
+        d.M = o.M;
+        d.N = o.N;
+        const int mode = o.mode == FEATHER_MODE_E5M2 ? kE5M2 : kE4M3;
+        const int out_sel = o.out_mode < 0 ? 0 : 1 + (o.out_mode == FEATHER_MODE_E5M2 ? kE5M2 : kE4M3);
+        d.flags = mode | (out_sel << 1);
+        d.wait_op = o.wait_op;
+        d.rows_q = o.M / grid;
+        d.rot = (int)(((long long)i * kChainRotate) % grid);
+    }
+    for (int i = 0; i < n_ops; ++i)
+        if (host[i].wait_op >= 0) host[host[i].wait_op].flags |= 8;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    char* base = static_cast<char*>(plan);
+    const int64_t cb = chain_counter_bytes(n_ops);
+    if (cudaMemsetAsync(base, 0, (size_t)cb, s) != cudaSuccess ||
+        cudaMemcpyAsync(base + cb, host.get(), sizeof(ChainOp) * (size_t)n_ops, cudaMemcpyHostToDevice, s) !=
+            cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess)   // the host copy of the table is released on return
+        return FEATHER_ERR_LAUNCH;
+    return FEATHER_OK;
+}
+
+int feather_gemv_chain_fp8(const void* plan, int32_t n_ops, uint32_t flags, void* stream) {
+    if (flags & ~(uint32_t)FEATHER_GEMV_STATIC_MATRIX) return FEATHER_ERR_BAD_ARG;
+    if (!plan || n_ops <= 0) return FEATHER_ERR_BAD_ARG;
+    if (!aligned(plan, 16)) return FEATHER_ERR_MISALIGNED;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    unsigned int* status = nullptr;
+    if (int st = status_word(&status)) return st;
+    const bool early = (flags & FEATHER_GEMV_STATIC_MATRIX) != 0;
+    auto kernel = early ? gemv_chain_kernel<true> : gemv_chain_kernel<false>;
+    static std::atomic<unsigned long long> configured[2];
+    if (int st = ensure_smem(kernel, kChainSmemBytes, configured[early ? 1 : 0])) return st;
+    char* base = static_cast<char*>(const_cast<void*>(plan));
+    unsigned int* done = reinterpret_cast<unsigned int*>(base);
+    const ChainOp* ops = reinterpret_cast<const ChainOp*>(base + chain_counter_bytes(n_ops));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)dev->sm_count);   // one CTA per SM: resident at once
+    cfg.blockDim = dim3(kChainThreads);
+    cfg.dynamicSmemBytes = kChainSmemBytes;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ops, (int)n_ops, done, status);
+    return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
+}
+
+int feather_set_tuning(const char* spec) { return apply_tuning(spec); }
 
 int feather_device_status(void* stream) {
     unsigned int* status = nullptr;

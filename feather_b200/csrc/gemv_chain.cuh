@@ -1,0 +1,371 @@
+// gemv_chain_kernel: a whole table of packed-FP8 GEMVs in ONE persistent launch.
+//
+//   for every op i of the table:  out_i[r] = sum_j decode(m_i[r, j]) * decode(v_i[j])
+//
+// Batch-1 decoding runs a chain of small GEMVs (a TinyLlama-shaped token is 155
+// of them, 0.5 .. 65 MB each).  Launched one by one they are bound by launch
+// and prologue latency, not by HBM: every kernel starts with an empty pipeline
+// and ends by draining it.  Here the grid (one CTA per SM) walks the table and
+// the stream of matrix bytes never stops at an op boundary:
+//
+//   * the producer warp walks (op, task, segment) and keeps a ring of
+//     kChainStages shared-memory stages full with cp.async.bulk; a stage holds
+//     up to 16 rows x 2 KiB of one op; it runs ahead across op boundaries as far
+//     as the ring allows (weights do not depend on earlier ops);
+//   * 16 consumer warps each OWN one row of a stage for all its columns (no
+//     CTA-wide reduction; the arithmetic and its order are those of
+//     gemv_rows_kernel / gemv_ring_kernel, so every op's result has the bits
+//     of the single-op entry point);
+//   * the vector warp stages the NEXT op's vector (decoded once to FP16 pairs,
+//     two buffers) while the consumers still work on the current op; ops that
+//     share a vector (q/k/v, gate/up) stage it once;
+//   * an op may name an earlier op it depends on (`wait_op`: its vector is that
+//     op's packed output).  CTAs that finish their rows of an op count
+//     themselves in done[op] (release); the vector warp of a dependent op polls
+//     that counter (acquire, bounded) before it reads the vector with L2 loads.
+//     The matrix stream is not held up by such a wait until the ring is full;
+//   * results are FP32 sums or, with out_mode >= 0, FP8 codes of the sums (the
+//     packer's rounding) stored one byte per row -- the packed vector the next
+//     op consumes.
+//
+// Rows of op i are dealt to the CTAs in contiguous blocks, rotated by the op
+// index so that the extra row of an uneven split does not always hit the same CTAs.
+// The grid must be resident at once when ops depend on each other (checked by
+// the host with the occupancy API).  Every wait is bounded (status word).
+#pragma once
+#include "gemv_ring.cuh"
+
+namespace feather {
+
+// One GEMV of the table as the kernel reads it (built by feather_gemv_chain_plan
+// from the public feather_chain_op records; same size, 48 bytes).
+struct ChainOp {
+    const unsigned char* m;   // packed matrix, M rows of N bytes, 16-byte aligned rows
+    const uint32_t* v;        // packed vector, N / 4 words, 16-byte aligned
+    void* out;                // M floats, or ceil(M / 4) packed words when there is an output format
+    int M, N;                 // N a multiple of 16, at most kChainTile
+    int flags;                // bit 0: decode of m and v (kE5M2 / kE4M3); bits 1-2: 0 = FP32 sums,
+                              // 1 + format = the sums encoded to that format; bit 3: a later op waits
+                              // for this one
+    int wait_op;              // -1, or the index of an EARLIER op that writes v
+    int rows_q;               // M / grid: every CTA's share, the first M % grid CTAs hold one more
+    int rot;                  // (op index * kChainRotate) % grid: where the row blocks start
+    __host__ __device__ int mode() const { return flags & 1; }
+    __host__ __device__ int out_mode() const { return ((flags >> 1) & 3) - 1; }
+    __host__ __device__ bool signal() const { return (flags & 8) != 0; }
+};
+static_assert(kE5M2 == 0 && kE4M3 == 1, "mode fits one bit");
+static_assert(sizeof(ChainOp) == 48, "the table layout is part of the ABI");
+
+constexpr int kChainCW = 16;                    // consumer warps = rows per stage
+constexpr int kChainCL = 4;                     // 16-byte chunks per lane, row and stage
+constexpr int kChainStages = 6;
+constexpr int kChainTile = 8192;                // longest row / vector, in codes
+constexpr int kChainSegChunks = kChainCL * 32;  // 128 chunks = 2 KiB of a row per stage
+constexpr int kChainSegBytes = kChainSegChunks * 16;
+constexpr int kChainStageBytes = kChainCW * kChainSegBytes;       // 32 KiB
+constexpr int kChainVecBytes = kChainTile * 2;                    // one FP16 vector buffer
+constexpr int kChainBarriers = 2 * kChainStages + 4;              // full, empty, vec_full[2], vec_empty[2]
+constexpr int kChainSmemBytes = 2 * kChainVecBytes + kChainStages * kChainStageBytes +
+                                kChainBarriers * 8 + 8 * 4;       // + 8 per-op arrival counters
+constexpr int kChainThreads = (kChainCW + 2) * 32;
+constexpr int kChainRotate = 61;                // row blocks move by this many CTAs per op
+
+struct ChainGeom {
+    int row_begin, row_end, n_tasks, n16, n_seg;
+};
+__device__ __forceinline__ ChainGeom chain_geom(const ChainOp& d) {
+    ChainGeom g;
+    int b = (int)blockIdx.x + d.rot;
+    if (b >= (int)gridDim.x) b -= (int)gridDim.x;
+    const int rem = d.M - d.rows_q * (int)gridDim.x;
+    g.row_begin = b * d.rows_q + min(b, rem);
+    g.row_end = g.row_begin + d.rows_q + (b < rem ? 1 : 0);
+    g.n_tasks = (g.row_end - g.row_begin + kChainCW - 1) / kChainCW;
+    g.n16 = d.N >> 4;
+    g.n_seg = (g.n16 + kChainSegChunks - 1) / kChainSegChunks;
+    return g;
+}
+__device__ __forceinline__ ChainOp chain_load_op(const ChainOp* ops, int op, int n_ops) {
+    // three 16-byte loads; past the end the last op is read again (unused)
+    const uint4* p = reinterpret_cast<const uint4*>(ops + (op < n_ops ? op : n_ops - 1));
+    union { uint4 q[3]; ChainOp d; } u;
+    u.q[0] = __ldg(p);
+    u.q[1] = __ldg(p + 1);
+    u.q[2] = __ldg(p + 2);
+    return u.d;
+}
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ld_l2(const uint4* p) {
+    uint4 r;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+    return r;
+}
+
+// One stage of one row: `chunks` 16-byte chunks (at most kChainSegChunks) of the
+// row at `st` against the vector chunks at `vs`.
+template <int MODE>
+__device__ __forceinline__ void chain_row_stage(const uint4* st, const uint4* vs, int chunks, int lane,
+                                                float (&acc)[4]) {
+    if (chunks == kChainSegChunks) {
+#pragma unroll
+        for (int c = 0; c < kChainCL; ++c)
+            fma_chunk<MODE>(st[c * 32], vs[(c * 2) * 32], vs[(c * 2 + 1) * 32], acc);
+    } else {
+#pragma unroll 1
+        for (int c = 0; c < kChainCL; ++c)
+            if (c * 32 + lane < chunks)
+                fma_chunk<MODE>(st[c * 32], vs[(c * 2) * 32], vs[(c * 2 + 1) * 32], acc);
+    }
+}
+
+// done[0] is the CTA ticket of the launch, done[1 + i] the number of CTAs that
+// have finished op i.  All are zero between launches (the last CTA resets them).
+// EARLY: the caller promises that nothing in flight writes the matrices or the
+// table, so the producer starts before the stream-order wait.
+template <bool EARLY>
+__global__ void __launch_bounds__(kChainThreads, 1)
+gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __restrict__ done,
+                  unsigned int* __restrict__ status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint4* vec = reinterpret_cast<uint4*>(smem);                    // two buffers of kChainTile / 8 uint4
+    unsigned char* ring = smem + 2 * kChainVecBytes;
+    const uint32_t ring_s = smem_u32(ring);
+    unsigned char* bar_mem = ring + kChainStages * kChainStageBytes;
+    const uint32_t bars = smem_u32(bar_mem);
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (kChainStages + s); };
+    auto vec_full = [&](int b) { return bars + 8u * (2 * kChainStages + b); };
+    auto vec_empty = [&](int b) { return bars + 8u * (2 * kChainStages + 2 + b); };
+    unsigned int* op_cnt = reinterpret_cast<unsigned int*>(bar_mem + 8 * kChainBarriers);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kChainStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), kChainCW);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(vec_full(b), 1);
+            mbar_init(vec_empty(b), kChainCW);
+        }
+        for (int i = 0; i < 8; ++i) op_cnt[i] = 0u;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (!EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    if (warp == kChainCW) {
+        // ------------------------------------------------------- producer --
+        int s = 0;
+        uint32_t round = 0;
+        bool alive = true;
+        ChainOp next = chain_load_op(ops, 0, n_ops);
+        for (int op = 0; op < n_ops && alive; ++op) {
+            const ChainOp d = next;
+            next = chain_load_op(ops, op + 1, n_ops);
+            const ChainGeom g = chain_geom(d);
+            const size_t row_bytes = (size_t)d.N;
+            for (int task = 0; task < g.n_tasks && alive; ++task) {
+                const int row0 = g.row_begin + task * kChainCW;
+                const int rows = min(kChainCW, g.row_end - row0);
+                for (int seg = 0; seg < g.n_seg; ++seg) {
+                    if (round > 0 && !mbar_wait(empty_bar(s), (round & 1u) ^ 1u, status)) {
+                        alive = false;
+                        break;
+                    }
+                    const int chunks = min(kChainSegChunks, g.n16 - seg * kChainSegChunks);
+                    const uint32_t bytes = (uint32_t)chunks * 16u;
+                    if (lane == 0) mbar_arrive_expect_tx(full_bar(s), bytes * (uint32_t)rows);
+                    if (lane < rows)
+                        bulk_load(ring_s + s * kChainStageBytes + lane * kChainSegBytes,
+                                  d.m + (size_t)(row0 + lane) * row_bytes + (size_t)seg * kChainSegBytes,
+                                  bytes, full_bar(s));
+                    if (++s == kChainStages) { s = 0; ++round; }
+                }
+            }
+        }
+        if (!alive) {
+            const unsigned long long t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < 1000000ull) {}   // let the copies in flight land
+        }
+    } else if (warp == kChainCW + 1) {
+        // ---------------------------------------------------- vector warp --
+        if (EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");  // vectors and counters
+        int vec_idx = -1;
+        const uint32_t* staged_v = nullptr;
+        int staged_n = -1, staged_mode = -1;
+        bool alive = true;
+        ChainOp next = chain_load_op(ops, 0, n_ops);
+        for (int op = 0; op < n_ops && alive; ++op) {
+            const ChainOp d = next;
+            next = chain_load_op(ops, op + 1, n_ops);
+            const ChainGeom g = chain_geom(d);
+            if (g.n_tasks == 0) continue;
+            if (d.v == staged_v && d.N == staged_n && d.mode() == staged_mode && d.wait_op < 0) continue;
+            staged_v = d.v; staged_n = d.N; staged_mode = d.mode();
+            ++vec_idx;
+            const int b = vec_idx & 1;
+            if (vec_idx >= 2 && !mbar_wait(vec_empty(b), (uint32_t)((vec_idx >> 1) - 1) & 1u, status)) break;
+            if (d.wait_op >= 0) {
+                // the vector is op wait_op's output: all CTAs that hold rows of it must be done
+                const ChainOp w = chain_load_op(ops, d.wait_op, n_ops);
+                const unsigned int target = (unsigned int)min((int)gridDim.x, w.M);
+                const unsigned int* flag = done + 1 + d.wait_op;
+                if (ld_acquire_gpu(flag) < target) {
+                    const unsigned long long t0 = global_timer_ns();
+                    while (ld_acquire_gpu(flag) < target) {
+                        if (global_timer_ns() - t0 > kWaitLimitNs) {
+                            atomicOr(status, 4u);   // an op this one depends on did not finish in time
+                            alive = false;
+                            break;
+                        }
+                    }
+                }
+                if (!alive) break;
+            }
+            // chunk c (16 codes) -> uint4 (c / 32 * 2 + k) * 32 + c % 32, k = 0, 1: the FP16
+            // pairs of its first and second eight codes (the layout fma_chunk reads)
+            uint4* dst = vec + b * (kChainTile / 8);
+            const uint4* src = reinterpret_cast<const uint4*>(d.v);
+            const int fill = g.n_seg * kChainSegChunks;
+            constexpr int kBatch = 8;
+            for (int c0 = lane; c0 < fill; c0 += 32 * kBatch) {
+                uint4 raw[kBatch];
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    const int c = c0 + 32 * u;
+                    raw[u] = c < g.n16 ? ld_l2(src + c) : make_uint4(0, 0, 0, 0);  // past N: code 0 = +0.0
+                }
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    const int c = c0 + 32 * u;
+                    if (c < fill) {
+                        uint4 lo, hi;
+                        if (d.mode() == kE5M2) {
+                            decode_word_h2<kE5M2>(raw[u].x, lo.x, lo.y);
+                            decode_word_h2<kE5M2>(raw[u].y, lo.z, lo.w);
+                            decode_word_h2<kE5M2>(raw[u].z, hi.x, hi.y);
+                            decode_word_h2<kE5M2>(raw[u].w, hi.z, hi.w);
+                        } else {
+                            decode_word_h2<kE4M3>(raw[u].x, lo.x, lo.y);
+                            decode_word_h2<kE4M3>(raw[u].y, lo.z, lo.w);
+                            decode_word_h2<kE4M3>(raw[u].z, hi.x, hi.y);
+                            decode_word_h2<kE4M3>(raw[u].w, hi.z, hi.w);
+                        }
+                        dst[((c >> 5) * 2) * 32 + (c & 31)] = lo;
+                        dst[((c >> 5) * 2 + 1) * 32 + (c & 31)] = hi;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(vec_full(b));
+        }
+    } else {
+        // ------------------------------------------------------ consumers --
+        if (EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");  // before any output is written
+        int s = 0;
+        uint32_t phase = 0;
+        int vec_idx = -1, sig_idx = 0;
+        const uint32_t* staged_v = nullptr;
+        int staged_n = -1, staged_mode = -1;
+        bool alive = true;
+        const uint4* const ring_lane = reinterpret_cast<const uint4*>(ring) + lane;
+        ChainOp next = chain_load_op(ops, 0, n_ops);
+        for (int op = 0; op < n_ops && alive; ++op) {
+            const ChainOp d = next;
+            next = chain_load_op(ops, op + 1, n_ops);
+            const ChainGeom g = chain_geom(d);
+            if (g.n_tasks == 0) continue;
+            if (!(d.v == staged_v && d.N == staged_n && d.mode() == staged_mode && d.wait_op < 0)) {
+                staged_v = d.v; staged_n = d.N; staged_mode = d.mode();
+                if (vec_idx >= 0) {   // done with the previous vector
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(vec_empty(vec_idx & 1));
+                }
+                ++vec_idx;
+                if (!mbar_wait(vec_full(vec_idx & 1), (uint32_t)(vec_idx >> 1) & 1u, status)) break;
+            }
+            const uint4* vbase = vec + (vec_idx & 1) * (kChainTile / 8) + lane;
+            for (int task = 0; task < g.n_tasks && alive; ++task) {
+                // Row `slot` of the task belongs to warp (slot + shift) % 16, the shift moving
+                // with op and task: a short task (14 of 16 rows, 2 rows of a 256-row matrix)
+                // then idles different warps -- and different schedulers -- each time, and
+                // because the warps run up to a ring's depth apart the load evens out.
+                const int slot = (warp - (5 * op + 3 * task)) & (kChainCW - 1);
+                const int row = g.row_begin + task * kChainCW + slot;
+                const bool has_row = row < g.row_end;   // warp-uniform
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int seg = 0; seg < g.n_seg; ++seg) {
+                    if (!mbar_wait(full_bar(s), phase, status)) {
+                        alive = false;
+                        break;
+                    }
+                    if (has_row) {
+                        const uint4* st = ring_lane + (s * kChainCW + slot) * kChainSegChunks;
+                        const uint4* vs = vbase + (seg * kChainCL * 2) * 32;
+                        const int chunks = min(kChainSegChunks, g.n16 - seg * kChainSegChunks);
+                        if (d.mode() == kE5M2) chain_row_stage<kE5M2>(st, vs, chunks, lane, acc);
+                        else chain_row_stage<kE4M3>(st, vs, chunks, lane, acc);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty_bar(s));
+                    if (++s == kChainStages) { s = 0; phase ^= 1u; }
+                }
+                if (!alive) break;
+                if (has_row) {
+                    float sums[1] = {(acc[0] + acc[1]) + (acc[2] + acc[3])};
+                    warp_reduce_rows<1>(sums, lane);
+                    if (lane == 0) {
+                        const int out_mode = d.out_mode();
+                        if (out_mode < 0) {
+                            reinterpret_cast<float*>(d.out)[row] = sums[0];
+                        } else {
+                            // one code per row, byte r of the packed output; the row that ends the
+                            // matrix also writes the zero codes that pad the last word
+                            unsigned char* codes = reinterpret_cast<unsigned char*>(d.out);
+                            codes[row] = (unsigned char)(out_mode == kE5M2 ? encode_f32<kE5M2>(sums[0])
+                                                                             : encode_f32<kE4M3>(sums[0]));
+                            if (row == d.M - 1)
+                                for (int i = d.M; i & 3; ++i) codes[i] = 0;
+                        }
+                    }
+                }
+            }
+            if (!alive) break;
+            if (d.signal()) {
+                // This warp's rows of the op are written.  The warps count themselves in with a
+                // release at CTA scope; the last one, having seen them all, issues the one
+                // GPU-scope fence (which thereby covers every warp's rows) and counts the CTA
+                // in done[op].
+                __threadfence_block();
+                __syncwarp();
+                if (lane == 0) {
+                    unsigned int* cnt = op_cnt + (sig_idx & 7);
+                    if (atomicAdd(cnt, 1u) == kChainCW - 1) {
+                        *cnt = 0u;
+                        __threadfence();
+                        atomicAdd(done + 1 + op, 1u);
+                    }
+                }
+            }
+            ++sig_idx;
+        }
+    }
+    // ---- every role ends here: the last CTA of the launch zeroes the counters ----
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(done, 1u) == gridDim.x - 1) {
+            for (int i = 0; i <= n_ops; ++i) done[i] = 0u;
+        }
+    }
+}
+
+}  // namespace feather

@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(kRowsThreads)
 gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
                  float* __restrict__ out, int M, int n16, int out_code,
                  const __grid_constant__ std::conditional_t<ALLREDUCE, AllReduceArgs, NoAllReduce> ar,
-                 unsigned int* __restrict__ status) {
+                 unsigned int* __restrict__ status, int pre) {
     extern __shared__ __align__(16) unsigned char rows_smem[];
     uint4* vec = reinterpret_cast<uint4*>(rows_smem);
     constexpr int kWarps = kRowsThreads / 32;
@@ -88,6 +88,19 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
         }
     };
     if (EARLY) issue(rows, active, 0);
+    else if (pre && active && (lane & 7) == 0) {
+        // without the promise: ask L2 for the lines of the first batch (one
+        // request per 128-byte line).  A prefetch moves data from HBM into L2,
+        // where every write to this GPU's memory lands too, so it cannot make
+        // the loads after the wait see stale bytes.
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = u * 32 + lane;
+#pragma unroll
+            for (int r = 0; r < RW; ++r)
+                if (c < n16) asm volatile("prefetch.global.L2 [%0];" ::"l"(rows[r] + c));
+        }
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (!EARLY) issue(rows, active, 0);
     __shared__ float ar_part[kGroupRows];  // a CTA's row sums, for the all-reduce / packed output

@@ -183,14 +183,13 @@ template <int MODE, int CW, int RW, int CL, int STAGES, int TILE, int CTAS, bool
 __global__ void __launch_bounds__((CW + 2) * 32, CTAS)
 gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict__ v,
                  float* __restrict__ out, int M, int n16, unsigned int* __restrict__ status,
-                 const __grid_constant__ ShardArgs sh = ShardArgs{}) {
+                 int pre_bytes, const __grid_constant__ ShardArgs sh = ShardArgs{}) {
     using G = RingGeometry<CW, RW, CL, STAGES, TILE>;
     // Programmatic dependent launch: let the next kernel of the stream be
-    // scheduled onto SMs as they free up, and wait for everything before this
-    // kernel (in stream order) to have completed and become visible before any
-    // global memory is touched.  Without the launch attribute both are no-ops.
+    // scheduled onto SMs as they free up.  Everything up to the stream-order
+    // wait below touches no global memory, so it runs under the tail of the
+    // kernel before this one.  Without the launch attribute both are no-ops.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (!EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");
     extern __shared__ __align__(128) unsigned char smem[];
     uint4* vec = reinterpret_cast<uint4*>(smem);
     unsigned char* ring = smem + G::kVecBytes;
@@ -233,7 +232,22 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
         *warps_done = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (!EARLY && warp == CW && pre_bytes > 0) {
+        // Ahead of the stream-order wait the producer asks L2 for the first
+        // `pre_bytes` of this CTA's rows.  A prefetch only moves lines from HBM
+        // into L2, the point where all writes to this GPU's memory meet, so it
+        // is harmless even when the kernel before this one is still writing
+        // the matrix: the copies issued after the wait read what L2 then holds.
+        // CTAs of a kernel launched back to back land on SMs as the previous
+        // kernel's CTAs retire, and these requests fill the HBM time its tail
+        // leaves idle.
+        const int chunks_p0 = min(piece_chunks, n16);
+        const int pre_rows = min(row_end - row_begin, (pre_bytes + chunks_p0 * 16 - 1) / (chunks_p0 * 16));
+        for (int r = lane; r < pre_rows; r += 32)
+            bulk_prefetch_l2(m + (size_t)(row_begin + r) * row_bytes, (uint32_t)chunks_p0 * 16u);
+    }
     __syncthreads();
+    if (!EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (n_tasks == 0 && !FUSED) return;  // a fused rank needs every CTA at the final ticket
 
     if (warp == CW + 1) {

@@ -314,6 +314,75 @@ int feather_device_status(void* stream);
 int feather_set_wait_limit_ms(int milliseconds);
 
 /*
+ * A table of GEMVs in ONE persistent launch (batch-1 decoding: one token of a
+ * model is a chain of small GEMVs that, launched one by one, are bound by
+ * launch and pipeline-fill latency instead of HBM).  No counterpart in the
+ * reference, where every GEMV is its own launch of feather/routines/gemv.py:136
+ * / :187; every op computes what feather_gemv_fp8 (or, with out_mode >= 0,
+ * feather_gemv_fp8_packed) computes for the same operands, bit for bit.
+ *
+ * feather_chain_op describes one GEMV:
+ *   m, v, out  as for feather_gemv_fp8; m and v 16-byte aligned; out holds M
+ *              floats (out_mode = -1) or ceil(M / 4) packed words of the sums
+ *              encoded to out_mode (FEATHER_MODE_E5M2 / _E4M3), padding codes 0
+ *   M, N       N a multiple of 16, at most 8192 (FEATHER_ERR_TOO_LARGE beyond)
+ *   mode       decode of m and v
+ *   wait_op    -1, or the index of an EARLIER op of the table whose output is
+ *              this op's vector: v is read only after that op has finished on
+ *              every SM.  Ops without it may run in any overlap; an op must
+ *              not read what another op of the same launch writes unless it
+ *              names that op here.
+ *
+ * feather_gemv_chain_plan validates a HOST array of ops and writes the device
+ * table (and the zeroed completion counters) into `plan`, a device buffer of
+ * at least feather_gemv_chain_plan_bytes(n_ops) bytes, 16-byte aligned, owned
+ * by the caller; it synchronises `stream`, so the host array may be freed on
+ * return.  feather_gemv_chain_fp8 enqueues the launch; the same plan can be
+ * launched again and again (also from a captured CUDA graph), but not by two
+ * launches that overlap on the GPU.  FEATHER_GEMV_STATIC_MATRIX promises that
+ * no work in flight writes the matrices or the plan.  Device-side waits are
+ * bounded (feather_set_wait_limit_ms, feather_device_status).
+ */
+typedef struct feather_chain_op {
+    const uint32_t* m;
+    const uint32_t* v;
+    void* out;
+    int32_t M, N;
+    int32_t mode;
+    int32_t out_mode;
+    int32_t wait_op;
+    int32_t reserved;   /* set to 0 */
+} feather_chain_op;
+
+int64_t feather_gemv_chain_plan_bytes(int32_t n_ops);
+int feather_gemv_chain_plan(const feather_chain_op* ops, int32_t n_ops, void* plan, int64_t plan_bytes,
+                            void* stream);
+int feather_gemv_chain_fp8(const void* plan, int32_t n_ops, uint32_t flags, void* stream);
+
+/*
+ * Kernel-variant knobs for A/B runs in benchmarks; results do not depend on
+ * them.  No counterpart in the reference, whose only tunables are the
+ * BLOCK_SIZE constants in its launch wrappers (feather/routines/gemv.py:178,
+ * :229, feather/routines/dot.py:256).  `spec` is "key=value[,key=value...]":
+ *   ring_pre_kb=K       KiB of each CTA's first rows that the large-matrix GEMV
+ *                       kernel asks L2 for ahead of its stream-order wait, E5M2
+ *                       (0 .. 16384, default 128; 0 = none)
+ *   ring_pre_kb_e4m3=K  the same for E4M3 (-1 = by matrix size, the default)
+ *   rows_pre=0|1        the same for the first batch of the small-matrix kernel
+ *   dot_ring=0..3       0: the register-load dot kernel only; 1, 2, 3: long
+ *                       operands take the bulk-copy ring kernel with stages of
+ *                       32, 64 or 16 KiB
+ *   dot_pre_kb=K        as ring_pre_kb, for the dot ring kernel
+ *   dot_unroll=1|2|4    16-byte loads per operand a dot thread keeps in flight
+ *   dot_ctas_per_sm=C   dot grid in CTAs per SM (1 .. 16)
+ * The environment variable FEATHER_KERNEL, if set, is applied once with the
+ * same syntax when the library first touches a device.  Process-wide, takes
+ * effect for later launches.  FEATHER_ERR_BAD_ARG for an unknown key or value;
+ * keys before the offending one have been applied.
+ */
+int feather_set_tuning(const char* spec);
+
+/*
  * *out = sum_i decode(a[i]) * decode(b[i]) over 4 * n_words codes.
  * Replaces feather/routines/dot.py:220-260 (dot_fp8_e5m2_acc_fp32_gpu) and its
  * kernel dot.py:144-192.  The reference adds per-block sums with a float

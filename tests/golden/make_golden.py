@@ -139,7 +139,29 @@ def make_attention() -> None:
     print("attention", os.path.getsize(os.path.join(HERE, "attention.npz")), "bytes")
 
 
+def make_dot() -> None:
+    """dot through the reference kernel (E5M2 is the only FP8 dot it has)."""
+    d = {}
+    d["doc"] = run_dot(ref_pack(np.array([2, 0, -3, 1], dtype=np.float16), "E5M2"),
+                       ref_pack(np.array([-1, 0, -3, 1], dtype=np.float16), "E5M2"))  # dot.py:244-251
+    # bench_dot.py:15 has n = 10 000, 500 000 and 1 500 000; 1027 adds a ragged length
+    for n, seed in ((10_000, 31), (500_000, 32), (1027, 33), (1_500_000, 34)):
+        rng = np.random.default_rng(seed)
+        x1 = rng.standard_normal(n).astype(np.float16)
+        x2 = rng.standard_normal(n).astype(np.float16)
+        a, bb = ref_pack(x1, "E5M2"), ref_pack(x2, "E5M2")
+        if n <= 20_000:  # larger inputs are regenerated from the seed by the tests
+            d[f"n{n}_a"], d[f"n{n}_b"] = a, bb
+        d[f"n{n}_wordsum"] = np.array([a.astype(np.uint64).sum(), bb.astype(np.uint64).sum()],
+                                      dtype=np.uint64)
+        d[f"n{n}_out"] = run_dot(a, bb)
+        d[f"n{n}_seed"] = np.array(seed, dtype=np.int64)
+    np.savez_compressed(os.path.join(HERE, "dot.npz"), **d)
+
+
 def main() -> None:
+    if sys.argv[1:] == ["dot"]:  # only the dot fixture (the others are unchanged)
+        return make_dot()
     if sys.argv[1:] == ["relu"]:  # only the ReLU fixture (the others are unchanged)
         return make_relu()
     if sys.argv[1:] == ["attention"]:
@@ -216,22 +238,7 @@ def main() -> None:
     g["rawbits_m"], g["rawbits_v"] = mw, vw
     np.savez_compressed(os.path.join(HERE, "gemv.npz"), **g)
 
-    # 4. dot through the reference kernel (E5M2 is the only FP8 dot it has)
-    d = {}
-    d["doc"] = run_dot(ref_pack(np.array([2, 0, -3, 1], dtype=np.float16), "E5M2"),
-                       ref_pack(np.array([-1, 0, -3, 1], dtype=np.float16), "E5M2"))  # dot.py:244-251
-    for n, seed in ((10_000, 31), (500_000, 32), (1027, 33)):  # bench_dot.py:15
-        rng = np.random.default_rng(seed)
-        x1 = rng.standard_normal(n).astype(np.float16)
-        x2 = rng.standard_normal(n).astype(np.float16)
-        a, bb = ref_pack(x1, "E5M2"), ref_pack(x2, "E5M2")
-        if n <= 20_000:  # larger inputs are regenerated from the seed by the tests
-            d[f"n{n}_a"], d[f"n{n}_b"] = a, bb
-        d[f"n{n}_wordsum"] = np.array([a.astype(np.uint64).sum(), bb.astype(np.uint64).sum()],
-                                      dtype=np.uint64)
-        d[f"n{n}_out"] = run_dot(a, bb)
-        d[f"n{n}_seed"] = np.array(seed, dtype=np.int64)
-    np.savez_compressed(os.path.join(HERE, "dot.npz"), **d)
+    make_dot()
     for f in ("encode", "decode", "gemv", "dot"):
         print(f, os.path.getsize(os.path.join(HERE, f + ".npz")), "bytes")
 

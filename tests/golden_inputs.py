@@ -9,7 +9,7 @@ import numpy as np
 GEMV_CASES = {"n01_33x2052": ((33, 2052), 21), "n01_16x8192": ((16, 8192), 22),
               "n01_7x12": ((7, 12), 23), "int_16x4096": ((16, 4096), 24),
               "c3_24x4100": ((24, 4100), 25)}
-DOT_CASES = ((10_000, 31), (500_000, 32), (1027, 33))
+DOT_CASES = ((10_000, 31), (500_000, 32), (1027, 33), (1_500_000, 34))  # bench_dot.py:15 + a ragged length
 
 
 def sample_f32(kind: str, n: int, seed: int) -> np.ndarray:

@@ -291,10 +291,11 @@ def test_readme_surface_and_mode_tag(fb):
 
 @pytest.mark.parametrize("mode", MODES)
 def test_gemv_bench_gemv_integer_inputs_exact(fb, mode):
-    """feather/benchmark/bench_gemv.py:48-93: integer-valued inputs in [-3, 2]
-    are exact in both formats, so the result equals torch.mv exactly."""
+    """feather/benchmark/bench_gemv.py:14-15, 48-93: integer-valued inputs in
+    [-3, 2] are exact in both formats, so the result equals torch.mv exactly;
+    every (M, N) combination of the reference's grid."""
     torch.manual_seed(4)
-    for M, N in ((4096, 4096), (8192, 4096), (4096, 16384)):
+    for M, N in ((m, n) for m in (4096, 8192, 16384) for n in (4096, 8192, 16384)):
         a = torch.randint(-3, 3, (M, N), device="cuda").to(torch.float16)
         b = torch.randint(-3, 3, (N,), device="cuda").to(torch.float16)
         y = fb.gemv_fp8_acc_fp32_gpu(fb.pack_fp8_tensor(a, mode), fb.pack_fp8_tensor(b, mode),
@@ -413,6 +414,127 @@ def test_gemv_chain_driver_runs(fb):
     c.token()
     torch.cuda.synchronize()
     assert len(c.ops) == 8 and all(torch.isfinite(o).all() for _, _, _, o in c.ops)
+
+
+# ------------------------------------------------- one launch for a table of GEMVs --
+def _chain_operands(fb, shapes, seed):
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    ops = []
+    for (M, N), mode in shapes:
+        A = torch.randn(M, N, device="cuda", generator=gen) * (1.0 if mode == "E5M2" else 0.05)
+        v = torch.randn(N, device="cuda", generator=gen)
+        ops.append({"m": fb.pack_fp8_tensor(A, mode), "v": fb.pack_fp8_tensor(v, mode),
+                    "shape": (M, N), "mode": mode})
+    return ops
+
+
+def test_gemv_chain_kernel_each_op_has_the_bits_of_the_single_call(fb):
+    """Independent ops of mixed shape and format (ragged N, M below the SM
+    count, M not a multiple of 4, shared vectors), FP32 and packed outputs."""
+    from feather_b200.chain import PersistentGemvChain
+    shapes = [((37, 2064), "E4M3"), ((2048, 2048), "E4M3"), ((256, 2048), "E5M2"), ((100, 5632), "E4M3"),
+              ((5632, 2048), "E5M2"), ((3, 16), "E4M3"), ((2046, 8192), "E5M2"), ((1, 4096), "E4M3"),
+              ((4737, 1040), "E4M3")]
+    ops = _chain_operands(fb, shapes, 50)
+    ops[2]["v"], ops[2]["mode"] = ops[1]["v"], "E4M3"      # two consecutive ops share a vector
+    ops[2]["m"] = fb.pack_fp8_tensor(torch.randn(256, 2048, device="cuda") * 0.05, "E4M3")
+    for i in (1, 3, 4, 8):
+        ops[i]["out_mode"] = "E4M3" if i != 4 else "E5M2"
+    chain = PersistentGemvChain(ops, static_matrix=False)
+    for rep in range(3):                                    # the plan is reusable
+        for o in chain.outs:
+            o.view(torch.int32).fill_(-1) if o.dtype != torch.float32 else o.fill_(float("nan"))
+        chain.token()
+        fb.device_status()
+        for op, got in zip(ops, chain.outs):
+            if op.get("out_mode") is None:
+                want = fb.gemv_fp8_acc_fp32_gpu(op["m"], op["v"], op["shape"], op["mode"])
+            else:
+                want = fb.gemv_fp8_ret_packed_gpu(op["m"], op["v"], op["shape"], op["mode"],
+                                                  out_mode=op["out_mode"])
+            assert torch.equal(got.view(torch.int32), want.view(torch.int32)), op["shape"]
+
+
+@pytest.mark.parametrize("static_matrix", [False, True])
+def test_gemv_chain_kernel_dependent_ops_and_graph_replay(fb, static_matrix):
+    """A real dependency chain: every op's vector is the packed output of the op
+    before it.  Equal, bit for bit, to the same GEMVs issued one by one."""
+    from feather_b200.chain import PersistentGemvChain
+    dims = [2048, 5632, 2048, 256, 2048, 8192, 1040, 2048]
+    gen = torch.Generator(device="cuda").manual_seed(51)
+    x = fb.pack_fp8_tensor(torch.randn(dims[0], device="cuda", generator=gen), "E4M3")
+    ops, v = [], x
+    for i in range(len(dims) - 1):
+        W = torch.randn(dims[i + 1], dims[i], device="cuda", generator=gen) / dims[i] ** 0.5
+        out = torch.zeros((dims[i + 1] + 3) // 4, dtype=torch.int32, device="cuda").view(torch.uint32)
+        ops.append({"m": fb.pack_fp8_tensor(W, "E4M3"), "v": v, "shape": (dims[i + 1], dims[i]),
+                    "out": out, "out_mode": "E4M3", "wait_op": i - 1})
+        v = out
+    ops.append({"m": ops[-1]["m"], "v": ops[-2]["out"], "shape": ops[-1]["shape"], "wait_op": len(ops) - 2})
+    chain = PersistentGemvChain(ops, "E4M3", static_matrix=static_matrix)
+    want, v = [], x
+    for op in ops[:-1]:
+        v = fb.gemv_fp8_ret_packed_gpu(op["m"], v, op["shape"], "E4M3")
+        want.append(v.clone())
+    want.append(fb.gemv_fp8_acc_fp32_gpu(ops[-1]["m"], want[-2], ops[-1]["shape"], "E4M3"))
+
+    def check():
+        fb.device_status()
+        for got, w in zip(chain.outs, want):
+            assert torch.equal(got.view(torch.int32), w.view(torch.int32))
+            got.view(torch.int32).zero_()
+    for _ in range(3):
+        chain.token()
+        check()
+    stream, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        chain.token()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            chain.token()
+            chain.token()                                    # two launches back to back in one graph
+    check()
+    for _ in range(3):
+        graph.replay()
+        check()
+
+
+def test_gemv_chain_kernel_config5_token_equals_the_155_launches(fb):
+    from feather_b200 import chain
+    c = chain.GemvChain(layers=2)
+    c.token()
+    p = chain.PersistentGemvChain.from_chain(c)
+    want = [o.clone() for _, _, _, o in c.ops]
+    for _, _, _, o in c.ops:
+        o.fill_(float("nan"))
+    p.token()
+    fb.device_status()
+    assert len(p.outs) == 15
+    for got, w in zip(p.outs, want):
+        assert torch.equal(got, w)
+    # the dependent form (every op re-encodes, inputs come from earlier outputs) runs too
+    d = chain.PersistentGemvChain.from_chain(chain.GemvChain(layers=2), dependent=True)
+    d.token()
+    fb.device_status()
+    assert all(int(o.view(torch.int32).abs().sum()) != 0 for o in d.outs)
+
+
+def test_gemv_chain_kernel_rejects(fb):
+    from feather_b200.chain import PersistentGemvChain
+    ok = _chain_operands(fb, [((64, 2048), "E4M3")], 52)[0]
+    with pytest.raises(ValueError):      # rows longer than the kernel's vector buffers
+        PersistentGemvChain(_chain_operands(fb, [((8, 8208), "E4M3")], 53))
+    with pytest.raises(ValueError):      # rows that are not whole 16-byte chunks
+        PersistentGemvChain(_chain_operands(fb, [((8, 2052), "E4M3")], 54))
+    with pytest.raises(ValueError):      # an op may only wait for an earlier op
+        PersistentGemvChain([dict(ok, wait_op=0)])
+    with pytest.raises(ValueError):
+        PersistentGemvChain([])
+    with pytest.raises(NotImplementedError):
+        PersistentGemvChain([dict(ok, mode="E3M4")])
+    lib = fb._lib.load()
+    assert lib.feather_gemv_chain_plan_bytes(0) == 0
+    assert lib.feather_gemv_chain_fp8(None, 1, 0, None) == -1
 
 
 # --------------------------------------------------------------------- dot --

@@ -214,3 +214,28 @@ def test_attention_matches_reference_kernel(golden, seq, d):
         s = dec(q) @ dec(k).T / np.sqrt(d)
         p = np.exp(s - s.max(axis=1, keepdims=True))
         assert O.normalised_error(got, (p / p.sum(axis=1, keepdims=True)) @ dec(v)) < 1e-3
+
+
+def test_reference_cpu_path_worker_agrees_with_the_oracle(c_oracle):
+    """The reference's CPU leg that the benchmark times (its packer + a torch
+    decode with the GPU kernels' bit semantics + torch.mv, run by
+    baseline/reference_worker.py) computes what the oracle computes."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import torch
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if not os.path.isdir(os.path.join(root, "baseline", "_ref", "feather", "routines")):
+        pytest.skip("baseline/_ref is not installed (baseline/install_reference.sh)")
+    res = subprocess.run([sys.executable, os.path.join(root, "baseline", "reference_worker.py"), "cpu",
+                          "--M", "256", "--N", "512"], capture_output=True, text=True, timeout=600)
+    line = [l for l in res.stdout.splitlines() if l.startswith("REFERENCE_WORKER ")][0]
+    got = json.loads(line[len("REFERENCE_WORKER "):])
+    assert "unavailable" not in got, got
+    torch.manual_seed(0)
+    A = torch.randn(256, 512).half().numpy()
+    v = torch.randn(512).half().numpy()
+    for mode in ("E5M2", "E4M3"):
+        y = c_oracle.gemv(c_oracle.pack(A, mode), c_oracle.pack(v, mode), (256, 512), mode, acc="f64")
+        assert abs(got[mode]["checksum"] - float(np.abs(y).sum())) < 1e-4 * float(np.abs(y).sum())

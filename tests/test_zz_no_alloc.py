@@ -6,10 +6,12 @@ memory arena, a loop that cannot afford the allocator's device-wide
 synchronisation -- so they cannot provide the workspace feather_dot_fp8 asks
 for.  This entry point keeps its scratch in a fixed array inside the library.
 The test drives it through the C ABI and holds it to the workspace-taking
-entry point's answer: two calls in a row on different data (the second call
-meets whatever the first left in the shared array), both FP8 modes, plus the
-size limit.  The file name sorts last so that a failure here cannot hide any
-other test from a run that stops at the first failure.
+entry point's answer bit for bit (both run the same kernel on the same grid)
+and to the CPU oracle's float64 sum within the dot tests' tolerance: two calls
+in a row on different data (the second call meets whatever the first left in
+the shared array), both FP8 modes, plus the size limit.  The file name sorts
+last so that a failure here cannot hide any other test from a run that stops
+at the first failure.
 """
 import numpy as np
 import pytest
@@ -36,13 +38,14 @@ def _operands(n_words: int, seed: int):
 
 
 @pytest.mark.parametrize("mode", [0, 1])
-def test_static_dot_matches_workspace_dot_twice_in_a_row(lib, mode):
+def test_static_dot_matches_workspace_dot_twice_in_a_row(lib, mode, c_oracle):
     from oracle import feather_oracle as O
     ws = torch.zeros(int(lib.feather_dot_workspace_bytes(0)), dtype=torch.uint8, device="cuda")
     out_ref = torch.zeros((), dtype=torch.float32, device="cuda")
     out_new = torch.full((), float("nan"), dtype=torch.float32, device="cuda")
-    # first a large call (many CTAs fill the scratch), then a small one on
-    # other data that must not see the leftovers, then an odd, unaligned length
+    # first a large call (long enough for the bulk-copy ring kernel: every CTA
+    # fills its scratch slot), then a small one on other data that must not see
+    # the leftovers, then an odd, unaligned length
     for n_words, seed, off in (((1 << 22) + 5, 1, 0), (4099, 2, 0), (70001, 3, 1)):
         a, b, ad, bd = _operands(n_words + off, seed)
         a, b, ad, bd = a[off:], b[off:], ad[off:], bd[off:]
@@ -53,7 +56,9 @@ def test_static_dot_matches_workspace_dot_twice_in_a_row(lib, mode):
         torch.cuda.synchronize()
         name = "E5M2" if mode == 0 else "E4M3"
         scale = float(np.abs(O.unpack(a, name).astype(np.float64) * O.unpack(b, name)).sum())
-        assert abs(out_new.item() - out_ref.item()) / scale < TOL
+        assert out_new.item() == out_ref.item()   # same kernel, same grid: same bits
+        want = float(c_oracle.dot(a, b, name, acc="f64"))
+        assert abs(out_new.item() - want) / scale < TOL
         # and once more on the same data: same bits as its own previous answer
         first = out_new.item()
         assert lib.feather_dot_fp8_static(ad.data_ptr(), bd.data_ptr(), out_new.data_ptr(),
