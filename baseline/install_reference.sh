@@ -3,7 +3,7 @@
 # so that its own Triton kernels and packer can be run beside this library on a
 # GPU box (tests/test_reference_gpu.py, bench.py's reference legs).
 #
-#   baseline/install_reference.sh [/path/to/reference/checkout]
+#   baseline/install_reference.sh /path/to/reference/checkout
 #
 # The reference's pyproject lists only the top-level package, and its
 # sub-packages feather/packers and feather/routines have no __init__.py, so a
@@ -12,7 +12,7 @@
 # file of the reference is changed.  baseline/_ref/ is git-ignored: nothing of
 # the reference enters this repository's history.
 set -euo pipefail
-SRC="${1:-/root/reference}"
+SRC="${1:?usage: install_reference.sh <reference checkout>}"
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 DST="$HERE/_ref"
 TMP="$(mktemp -d /tmp/feather_ref_src.XXXXXX)"

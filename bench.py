@@ -36,10 +36,11 @@ METRIC = "packed_fp8_gemv_hbm_gbps"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes per launch of gemv_ring_kernel<E5M2> at 16384 x 16384 from an ncu
-# capture: dram__bytes_read.sum 268 475 136 + dram__bytes_write.sum 3 669 248
-# (profiles/gemv_ring_e5m2_16384x16384.md).
+# DRAM bytes of ONE launch of gemv_ring_kernel<E5M2> at 16384 x 16384 as ncu
+# counted them (dram__bytes_read.sum + dram__bytes_write.sum of a single
+# captured launch, clocks not locked): 268 475 136 read + 3 669 248 written.
 NCU_TRAFFIC_BYTES_16384 = 272144384
+REPEAT_BLOCKS = 8  # further blocks of K steps timed after the official one, for median / min
 
 
 def gemv_bytes(M: int, N: int) -> int:
@@ -66,25 +67,29 @@ while True:
     t = time.time()
     print(t, nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM),
           nv.nvmlDeviceGetCurrentClocksEventReasons(h), flush=True)
-    time.sleep(0.002)
+    time.sleep(0.0005)
 """
 
 
 class ClockSampler:
     """SM clock and throttle reasons while the timed region runs.
 
-    NVML is polled (read-only queries, every 2 ms) by a CHILD process: polling
-    from a thread of the benchmark process contends with its kernel launches for
-    the driver's locks, which at 8 GPUs slowed the timed region by 25 %.  The
-    child is started before the warm-up; samples are kept if their wall-clock
-    time falls inside the timed region."""
+    NVML is polled (read-only queries, as fast as they return) by a CHILD
+    process: polling from a thread of the benchmark process contends with its
+    kernel launches for the driver's locks, which at 8 GPUs slowed the timed
+    region by 25 %.  The child is started before the warm-up.  The official
+    region of K steps can be shorter than one NVML query (20 x 40 us), so the
+    sampler also knows an EXTENDED window: the official region plus the
+    repeat blocks of the same step that follow it back to back.  The summary
+    uses the samples inside the official region when there are at least three,
+    else those of the extended window, and says which."""
 
     REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40,
                "sw_thermal_slowdown": 0x20, "hw_power_brake_slowdown": 0x80,
                "applications_clocks_setting": 0x2}
 
     def __init__(self, index: int):
-        self.proc, self.t0, self.t1 = None, None, None
+        self.proc, self.t0, self.t1, self.t2 = None, None, None, None
         if index < 0:
             return
         try:
@@ -101,20 +106,26 @@ class ClockSampler:
 
     def __exit__(self, *exc):
         self.t1 = time.time()
+
+    def stop(self):
+        """End of the extended window (call after the repeat blocks)."""
+        self.t2 = time.time()
         if self.proc is not None:
-            time.sleep(0.005)  # one more sample after the region, for very short regions
+            time.sleep(0.004)  # let the sample in flight be written
             self.proc.terminate()
 
     def summary(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
+        if self.t2 is None:
+            self.stop()
         try:
             text, _ = self.proc.communicate(timeout=10)
         except Exception:
             self.proc.kill()
             return out
-        inside, nearest, reasons = [], None, 0
+        official, extended = [], []
         for line in [self.first] + text.splitlines():
             f = line.split()
             if len(f) == 2 and f[0] == "max":
@@ -122,17 +133,20 @@ class ClockSampler:
             elif len(f) == 3:
                 t, mhz, r = float(f[0]), int(f[1]), int(f[2])
                 if self.t0 <= t <= self.t1:
-                    inside.append(mhz)
-                    reasons |= r
-                elif t > self.t1 and nearest is None:
-                    nearest = (mhz, r)
-        if not inside and nearest is not None:  # region shorter than one polling period
-            inside, reasons = [nearest[0]], nearest[1]
-            out["note"] = "timed region shorter than the polling period: first sample after it"
-        if inside:
-            inside.sort()
-            out["sm_mhz"] = inside[len(inside) // 2]
-            out["samples"] = len(inside)
+                    official.append((mhz, r))
+                if self.t0 <= t <= self.t2:
+                    extended.append((mhz, r))
+        use, out["window"] = (official, "official K steps") if len(official) >= 3 else (
+            extended, "official K steps + the repeat blocks right behind them")
+        if use:
+            mhz = sorted(m for m, _ in use)
+            reasons = 0
+            for _, r in use:
+                reasons |= r
+            out["sm_mhz"] = mhz[len(mhz) // 2]
+            out["sm_mhz_min"] = mhz[0]
+            out["samples"] = len(use)
+            out["samples_in_official_region"] = len(official)
             out["reasons"] = sorted(k for k, bit in self.REASONS.items() if reasons & bit)
         return out
 
@@ -228,6 +242,23 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def reference_worker(*argv, timeout: int = 900) -> dict:
+    """Run baseline/reference_worker.py (the reference's own code, installed
+    unmodified under baseline/_ref) in a process of its own; its JSON result, or
+    {"unavailable": why}."""
+    import subprocess
+    worker = os.path.join(ROOT, "baseline", "reference_worker.py")
+    try:
+        res = subprocess.run([sys.executable, worker, *argv], capture_output=True, text=True,
+                             timeout=timeout, cwd=os.path.join(ROOT, "baseline"))
+        for ln in res.stdout.splitlines():
+            if ln.startswith("REFERENCE_WORKER "):
+                return json.loads(ln[len("REFERENCE_WORKER "):])
+        return {"unavailable": f"worker exit code {res.returncode}: {res.stderr[-300:]}"}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": repr(e)[:300]}
+
+
 # ------------------------------------------------------------------ GPU arm --
 def time_calls(torch, fn, n_iter: int, warmup: int) -> float:
     """Average milliseconds per call with CUDA events on the current stream."""
@@ -241,6 +272,48 @@ def time_calls(torch, fn, n_iter: int, warmup: int) -> float:
     end.record()
     torch.cuda.synchronize()
     return start.elapsed_time(end) / n_iter
+
+
+def check_sharded(torch, dist, fb, op, op_nccl, m_local, vw, M, N, mode, rank, world, dev) -> dict:
+    """Correctness of the row-sharded operators on every rank: the fused
+    exchange (waiting and split-phase) against the NCCL all-gather, bit for bit
+    (rows never interact), and 1024 sampled rows PER RANK of the gathered
+    result against the oracle's float64 GEMV of the same packed rows."""
+    import numpy as np
+
+    from oracle import c_oracle as C
+    C.build()
+    rows = M // world
+    y_nccl = op_nccl(vw).clone()
+    same_wait = same_split = True
+    if op.fused:
+        for _ in range(3):   # both buffers, several epochs
+            same_wait &= bool(torch.equal(op(vw), y_nccl))
+        for _ in range(3):
+            y = op(vw, wait=False)
+            op.wait()
+            same_split &= bool(torch.equal(y, y_nccl))
+        fb.device_status()
+    n_sample = min(1024, rows)
+    idx = np.sort(np.random.default_rng(100 + rank).choice(rows, n_sample, replace=False))
+    idx_t = torch.from_numpy(idx).to(dev)
+    sub = m_local.view(torch.int32).view(rows, N // 4)[idx_t].contiguous().cpu().numpy().view(np.uint32)
+    v_host = vw.view(torch.int32).cpu().numpy().view(np.uint32)
+    ref = C.gemv(sub.reshape(-1), v_host, (n_sample, N), mode, acc="f64")
+    ref_t = torch.from_numpy(np.asarray(ref, dtype=np.float64)).to(dev)
+    all_ref = [torch.empty_like(ref_t) for _ in range(world)]
+    all_idx = [torch.empty_like(idx_t) for _ in range(world)]
+    dist.all_gather(all_ref, ref_t)
+    dist.all_gather(all_idx, idx_t)
+    want = torch.cat(all_ref)
+    where = torch.cat([all_idx[r] + r * rows for r in range(world)])
+    got = (op(vw) if op.fused else y_nccl)[where].double()
+    err = float(((got - want).abs().max() / want.abs().max()).item())
+    t = torch.tensor([err, -float(same_wait), -float(same_split)], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"rows_checked_per_rank": world * n_sample, "max_norm_err_vs_oracle_f64": float(t[0].item()),
+            "fused_equals_nccl": bool(t[1].item() == -1.0), "split_phase_equals_nccl": bool(t[2].item() == -1.0),
+            "tolerance": 1e-5}
 
 
 def run_ours(args) -> None:
@@ -293,6 +366,9 @@ def run_ours(args) -> None:
         def step():
             fb.gemv_fp8_acc_fp32_gpu(mats[state["i"] % n_buf], vw, (M, N), mode, out=out)
             state["i"] += 1
+
+        def finish():
+            pass
         l2_note = f"{n_buf} distinct 256 MiB packed matrices rotated (each larger than L2)"
     else:
         M = N = 65536
@@ -305,9 +381,15 @@ def run_ours(args) -> None:
         step_bytes = gemv_bytes(M, N)
 
         def step():
-            op(vw)
+            # split-phase: the call ends when this rank's rows and epoch are on their way; the
+            # arrival of the peers' slices is awaited once, after the last step (finish()),
+            # still inside the timed region, and by every later call before it overwrites a buffer
+            op(vw, wait=False)
+        finish = op.wait
         l2_note = f"per-rank block {rows * N >> 20} MiB, larger than L2"
-        extra["exchange"] = ("fused into the GEMV kernel (peer stores over NVLink)" if op.fused
+        extra["exchange"] = ("fused into the GEMV kernel (peer stores over NVLink), split-phase: the K "
+                             "steps are enqueued back to back, the wait for the last step's slices is "
+                             "inside the timed region" if op.fused
                              else "NCCL all-gather after the local GEMV")
 
     # ---- the timed region: W warm-up steps, then exactly K steps -----------
@@ -315,6 +397,7 @@ def run_ours(args) -> None:
     clocks = ClockSampler(physical_gpu_index(local_rank) if rank == 0 else -1)
     for _ in range(W):
         step()
+    finish()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if world > 1:
         dist.barrier()
@@ -323,17 +406,34 @@ def run_ours(args) -> None:
         start.record()
         for _ in range(K):
             step()
+        finish()
         end.record()
         torch.cuda.synchronize()
+    ms_total = start.elapsed_time(end)
+    # the same K steps again, REPEAT_BLOCKS times, each block timed on its own: the spread
+    # over blocks shows whether the official block (often under a millisecond) was typical
+    block_us = [ms_total * 1e3 / K]
+    for _ in range(REPEAT_BLOCKS):
+        s_ev, e_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_ev.record()
+        for _ in range(K):
+            step()
+        finish()
+        e_ev.record()
+        torch.cuda.synchronize()
+        block_us.append(s_ev.elapsed_time(e_ev) * 1e3 / K)
+    clocks.stop()
     if world > 1:
         dist.barrier()
-    ms_total = start.elapsed_time(end)
-    if world > 1:
-        t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms_total] + block_us, device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
+        ms_total, block_us = float(t[0].item()), [float(x) for x in t[1:].tolist()]
     ms_per_step = ms_total / K
     value = step_bytes / (ms_per_step * 1e-3) / 1e9
+    ordered = sorted(block_us)
+    blocks = {"blocks": len(block_us), "steps_per_block": K, "official_us": round(block_us[0], 3),
+              "median_us": round(ordered[len(ordered) // 2], 3), "min_us": round(ordered[0], 3),
+              "max_us": round(ordered[-1], 3)}
 
     # ---- kernel-only duration for the roofline (local GEMV kernel) ---------
     if world == 1:
@@ -343,25 +443,57 @@ def run_ours(args) -> None:
     else:
         kern_ms = time_calls(torch, lambda: op.local(vw), max(20, K), 5)
         kern_bytes = gemv_bytes(M // world, N)
-        if op.fused:  # the same step with the separate NCCL all-gather, for comparison
-            op_nccl = RowShardedGemv(m_local, (M, N), mode, fused=False)
-            ms_nccl = time_calls(torch, lambda: op_nccl(vw), max(20, K), 5)
-            t = torch.tensor([ms_nccl], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            extra["same_step_with_nccl_all_gather_us"] = round(float(t.item()) * 1e3, 3)
+        parity = {}
+        op_nccl = RowShardedGemv(m_local, (M, N), mode, fused=False)
+        if op.fused:
+            def rank_max(ms: float) -> float:
+                t = torch.tensor([ms], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                return round(float(t.item()) * 1e3, 3)
+            # the same step (a) waiting for all slices at the end of every call, (b) with the
+            # separate NCCL all-gather
+            extra["fused_waiting_in_every_call_us"] = rank_max(time_calls(torch, lambda: op(vw), max(20, K), 5))
+            extra["same_step_with_nccl_all_gather_us"] = rank_max(
+                time_calls(torch, lambda: op_nccl(vw), max(20, K), 5))
+            # where a waiting call's tail goes: GPU timer of the rank's last CTA
+            op.record_stamps(True)
+            lat, skew = [], []
+            for _ in range(10):
+                op(vw)
+                st = op.stamps()
+                lat.append((st[1] - st[0]) * 1e-3)
+                skew.append((st[2] - st[1]) * 1e-3)
+            op.record_stamps(False)
+            t = torch.tensor([sorted(lat)[5], sorted(skew)[5]], device=dev, dtype=torch.float64)
+            tmax, tmin = t.clone(), t.clone()
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
+            extra["exchange_tail_us"] = {
+                "rows_pushed_to_epoch_published": {"max_over_ranks": round(float(tmax[0]), 2),
+                                                   "min_over_ranks": round(float(tmin[0]), 2)},
+                "epoch_published_to_all_epochs_seen": {"max_over_ranks": round(float(tmax[1]), 2),
+                                                       "min_over_ranks": round(float(tmin[1]), 2)},
+                "note": "median of 10 waiting calls per rank; the first is fence + flag stores, the "
+                        "second the wait for the slowest rank"}
         extra["local_gemv_kernel_us"] = round(kern_ms * 1e3, 3)
+        # ---- correctness of what was timed (outside the timed region) ------
+        parity.update(check_sharded(torch, dist, fb, op, op_nccl, m_local, vw, M, N, mode, rank, world, dev))
         try:  # TinyLlama-shaped GEMV chain, tensor-parallel over the ranks (NCCL all-reduce)
             from feather_b200 import chain
-            extra["tinyllama_gemv_chain_tensor_parallel"] = chain.measure_tp(tokens=20)
+            extra["tinyllama_gemv_chain_tensor_parallel"] = chain.measure_tp(tokens=20, check=True)
         except Exception as e:  # noqa: BLE001 - must not sink the headline
             extra["tinyllama_gemv_chain_tensor_parallel"] = {"error": repr(e)}
         try:  # the same with the all-reduce inside the column-sharded GEMV kernels
             extra["tinyllama_gemv_chain_tensor_parallel_fused_allreduce"] = chain.measure_tp(
-                tokens=20, fused_allreduce=True)
+                tokens=20, fused_allreduce=True, check=True)
             extra["tinyllama_gemv_chain_tensor_parallel_fused_allreduce_merged"] = chain.measure_tp(
-                tokens=20, fused_allreduce=True, merge_projections=True)
+                tokens=20, fused_allreduce=True, merge_projections=True, check=True)
         except Exception as e:  # noqa: BLE001
             extra["tinyllama_gemv_chain_tensor_parallel_fused_allreduce"] = {"error": repr(e)}
+        parity["tp_chain_max_norm_err"] = {
+            k.replace("tinyllama_gemv_chain_tensor_parallel", "tp"): v.get("max_norm_err_vs_single_gpu_chain")
+            for k, v in extra.items() if k.startswith("tinyllama_gemv_chain_tensor_parallel")}
+        extra["parity"] = parity
         kern_name = "gemv_ring_kernel<E5M2> (per-rank block)"
     achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": kern_name, "achieved": round(achieved, 1),
@@ -491,8 +623,17 @@ def run_ours(args) -> None:
                 tokens=20, use_graph=True, reencode="fused")
             extra["tinyllama_gemv_chain_1gpu_reencode_separate_launch"] = chain.measure(
                 tokens=20, use_graph=True, reencode="separate")
+            # the whole token as ONE persistent launch (feather_gemv_chain_fp8): the same
+            # independent GEMVs; with q/k/v and gate/up merged; and as a true dependency chain
+            # (every op re-encodes its result, the next op of matching length reads it)
+            extra["tinyllama_gemv_chain_1gpu_one_launch"] = chain.measure(
+                tokens=30, use_graph=True, persistent="independent")
+            extra["tinyllama_gemv_chain_1gpu_one_launch_merged_qkv_gateup"] = chain.measure(
+                tokens=30, use_graph=True, persistent="independent", merge_projections=True)
+            extra["tinyllama_gemv_chain_1gpu_one_launch_dependent_reencode"] = chain.measure(
+                tokens=30, use_graph=True, persistent="dependent")
         except Exception as e:  # noqa: BLE001 - the extra section must not sink the headline
-            extra["tinyllama_gemv_chain_1gpu"] = {"error": repr(e)}
+            extra["tinyllama_gemv_chain_error"] = {"error": repr(e)}
         # dot on two 2^26-element E5M2 vectors: reuse the packed matrices as operands
         n_words = 1 << 24
         ops = [(mats[i][:n_words], mats[i][n_words:2 * n_words]) for i in range(n_buf)]
@@ -540,6 +681,28 @@ def run_ours(args) -> None:
             "us_per_call": round(ms_e * 1e3, 3), "GB/s": round(3 * M * N / ms_e / 1e6, 1),
             "frac_of_peak": round(3 * M * N / ms_e / 1e6 / peak, 4)}
         del src
+        # the row-sharded workload (65536 x 65536, 4 GiB packed) on this ONE GPU: the
+        # single-GPU point of the strong-scaling curve
+        try:
+            del mats, ops
+            torch.cuda.empty_cache()
+            Mb = Nb = 65536
+            big = make_packed(Mb, Nb, 5, mode)
+            gen.manual_seed(5)
+            vb = fb.pack_fp8_tensor(torch.randn(Nb, device=dev, generator=gen, dtype=torch.float16), mode)
+            ob = torch.empty(Mb, dtype=torch.float32, device=dev)
+            ms_b = time_calls(torch, lambda: fb.gemv_fp8_acc_fp32_gpu(big, vb, (Mb, Nb), mode, out=ob), 20, 3)
+            bb = gemv_bytes(Mb, Nb)
+            extra["gemv_e5m2_65536x65536_1gpu"] = {
+                "us_per_call": round(ms_b * 1e3, 2), "GB/s": round(bb / ms_b / 1e6, 1),
+                "frac_of_peak": round(bb / ms_b / 1e6 / peak, 4),
+                "note": "the N > 1 workload on one GPU: strong-scaling efficiency at N GPUs = this "
+                        "time / (N x the N-GPU ms_per_step)"}
+            del big, vb, ob
+            torch.cuda.empty_cache()
+        except Exception as e:  # noqa: BLE001
+            extra["gemv_e5m2_65536x65536_1gpu"] = {"error": repr(e)}
+        fb.device_status()
 
     if world > 1:
         op.close()  # unmap the peers' buffers (a collective: every rank calls it)
@@ -553,6 +716,20 @@ def run_ours(args) -> None:
         gbps, threads, sample, _ = cpu_gemv_gbps(M, N, mode, budget_s=12.0)
         cpu = {"value": round(gbps, 3), "unit": UNIT, "cores": threads, "kind": "port",
                "sample": sample}
+        # the reference's OWN code beside it (a process of its own, baseline/reference_worker.py):
+        # its Triton kernels on this GPU, and its packer + torch CPU decode + torch.mv on the host
+        torch.cuda.empty_cache()
+        extra["reference_triton_same_gpu"] = reference_worker("time", "--iters", "200")
+        ref_cpu = reference_worker("cpu", "--M", "4096", "--N", "4096")
+        if "unavailable" not in ref_cpu:
+            e5 = ref_cpu["E5M2"]
+            ref_cpu = {"value": e5["decode_mv_GB/s"], "unit": UNIT, "cores": ref_cpu["threads"],
+                       "kind": "reference",
+                       "sample": "4096 x 4096 (configuration 1): the reference packer "
+                                 "(feather/packers/fp8.py:260-281), then a torch-CPU decode with the "
+                                 "kernels' bit semantics + FP32 torch.mv; value = E5M2 decode+mv",
+                       "detail": ref_cpu}
+        extra["cpu_baseline_reference"] = ref_cpu
     line = {
         "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": round(ms_per_step, 6), "higher_is_better": True,
@@ -561,7 +738,7 @@ def run_ours(args) -> None:
         "config": {"workload": workload, "M": M, "N": N, "mode": mode,
                    "bytes_per_step": step_bytes, "l2": l2_note,
                    "parallelism": f"rows/{world}" if world > 1 else "1 GPU"},
-        "us_per_call": round(ms_per_step * 1e3, 3),
+        "us_per_call": round(ms_per_step * 1e3, 3), "us_per_call_blocks": blocks,
         "frac_of_nominal_8TBs": round(value / world / NOMINAL_HBM_GBS, 4),
         "roofline": roofline, "e2e": e2e, "gpu_launches": K,
         "clocks": clocks.summary(), "extra": extra,
@@ -571,6 +748,12 @@ def run_ours(args) -> None:
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+        par = extra.get("parity", {})
+        errs = [par.get("max_norm_err_vs_oracle_f64", 0.0)] + [
+            e for e in par.get("tp_chain_max_norm_err", {}).values() if e is not None]
+        if not (par.get("fused_equals_nccl", True) and par.get("split_phase_equals_nccl", True)
+                and all(e < 1e-5 for e in errs)):
+            raise SystemExit("parity check of the multi-GPU run failed: " + json.dumps(par))
 
 
 def main() -> None:

@@ -1,6 +1,6 @@
 """Small launch driver for profiling one kernel of the path under ncu.
 
-    python -m feather_b200.ncu_driver --op gemv --mode E5M2 --M 16384 --N 16384
+    python benchmark/ncu/profile_kernels.py --op gemv --mode E5M2 --M 16384 --N 16384
 
 Modelled on the reference's feather/benchmark/ncu/profile_gemv.py (a warm-up
 call, the measured calls, a synchronize).  Operands are random finite FP8 codes
@@ -10,10 +10,13 @@ its data in L2.  Prints one line per op with the CUDA-event time.
 from __future__ import annotations
 
 import argparse
+import os
+import sys
 
 import torch
 
-import feather_b200 as fb
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+import feather_b200 as fb  # noqa: E402
 
 
 def _codes(n_words: int, seed: int) -> torch.Tensor:

@@ -9,7 +9,9 @@ import ctypes
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libfeather_b200.so")
+# FEATHER_DEBUG_BOUNDS=1 selects the bounds-checking build (python -m feather_b200.csrc.build --debug-bounds)
+LIB_PATH = os.path.join(_PKG, "libfeather_b200_debug.so" if os.environ.get("FEATHER_DEBUG_BOUNDS") == "1"
+                        else "libfeather_b200.so")
 
 MODE_IDS = {"E5M2": 0, "E4M3": 1}
 SRC_F16, SRC_F32 = 0, 1
@@ -19,6 +21,7 @@ DECODE_KERNEL, DECODE_IEEE = 0, 1
 _vp, _i32, _i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
 SYMBOLS = {
     "feather_version": (_i32, []),
+    "feather_debug_bounds": (_i32, []),
     "feather_strerror": (ctypes.c_char_p, [_i32]),
     "feather_encode_fp8": (_i32, [_vp, _i32, _vp, _i64, _i32, _vp]),
     "feather_decode_fp8": (_i32, [_vp, _vp, _i64, _i32, _i32, _vp]),
@@ -31,6 +34,9 @@ SYMBOLS = {
     "feather_gemv_fp8_sharded": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp, _vp, _i32, _i32,
                                         ctypes.c_uint32, _vp]),
     "feather_gemv_fp8_sharded_supported": (_i32, [_i64, _i64]),
+    "feather_gemv_fp8_sharded_ex": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp, _vp, _i32, _i32,
+                                           ctypes.c_uint32, ctypes.c_uint32, _vp, _vp]),
+    "feather_gemv_fp8_sharded_wait": (_i32, [_vp, _i32, _i32, ctypes.c_uint32, _vp, _vp]),
     "feather_gemv_fp8_allreduce": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _i64, _vp, _i32, _i32,
                                           _vp]),
     "feather_enable_peer_access": (_i32, [_i32]),
@@ -111,6 +117,8 @@ def check(status: int) -> None:
     msg = load().feather_strerror(status).decode()
     if status in (-1, -2, -6, -8):
         raise ValueError(f"libfeather_b200: {msg} (status {status})")
+    if status == -9:
+        raise FeatherError(status, msg)
     if status == -7:
         raise FeatherError(status, msg + " (a device-side wait timed out; results are undefined)")
     if status == -3:

@@ -268,12 +268,38 @@ class TensorParallelChain:
             self.ctx.close()
 
 
+def check_tp(tp: "TensorParallelChain", single: "GemvChain") -> float:
+    """Largest error of a tensor-parallel token against the single-GPU chain
+    built from the same seed, normalised per op by the largest reference value:
+    row-split ops against their slice of the single-GPU result, column-split
+    ops (after the all-reduce) against the whole of it.  Max over the ranks."""
+    import torch.distributed as dist
+    tp.token()
+    single.token()
+    torch.cuda.synchronize()
+    worst = 0.0
+    for (kind, _, _, shape, out_tp), (_, _, _, out_1) in zip(tp.ops, single.ops):
+        ref = out_1 if kind in ("cols", "fused") else out_1[tp.rank * shape[0]:(tp.rank + 1) * shape[0]]
+        scale = float(out_1.abs().max().item()) or 1.0
+        worst = max(worst, float((out_tp.double() - ref.double()).abs().max().item()) / scale)
+    t = torch.tensor([worst], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=tp.group)
+    return float(t.item())
+
+
 def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", group=None,
-               fused_allreduce: bool = False, merge_projections: bool = False) -> dict:
-    """Tokens per second of the tensor-parallel chain (call on every rank)."""
+               fused_allreduce: bool = False, merge_projections: bool = False,
+               check: bool = False) -> dict:
+    """Tokens per second of the tensor-parallel chain (call on every rank).
+    ``check``: also compare one token with the single-GPU chain (check_tp)."""
     import torch.distributed as dist
     chain = TensorParallelChain(mode, group=group, fused_allreduce=fused_allreduce,
                                 merge_projections=merge_projections)
+    err = None
+    if check:
+        single = GemvChain(mode, merge_projections=merge_projections)
+        err = check_tp(chain, single)
+        del single
     # First token with a short wait limit: if the ranks cannot reach each other the
     # fused all-reduce gives up quickly and the status check raises here, instead of
     # every later call waiting out the default limit.
@@ -319,7 +345,8 @@ def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", gro
             "gemvs_per_token_per_rank": len(chain.ops),
             "all_reduces_per_token": sum(1 for o in chain.ops if o[0] in ("cols", "fused")),
             "fused_allreduce": chain.fused_allreduce, "merged_projections": merge_projections,
-            "world": chain.world, "cuda_graph": graphed, "mode": mode}
+            "world": chain.world, "cuda_graph": graphed, "mode": mode,
+            "max_norm_err_vs_single_gpu_chain": err}
 
 
 def measure(tokens: int = 50, use_graph: bool = True, mode: str = "E4M3",

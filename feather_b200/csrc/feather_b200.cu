@@ -41,8 +41,8 @@ struct Tuning {
     std::atomic<int> rows_pre{1};
     std::atomic<int> dot_unroll{4};
     std::atomic<int> dot_ctas_per_sm{6};
-    std::atomic<int> dot_ring{1};
-    std::atomic<int> dot_pre_kb{128};
+    std::atomic<int> dot_ring{2};
+    std::atomic<int> dot_pre_kb{64};
     std::atomic<int> ring_pre_kb_e4m3{-1};
 };
 static Tuning g_tune;
@@ -268,10 +268,7 @@ static int encode_launch(const void* src, uint32_t* dst, long long n, cudaStream
     return launch_status();
 }
 
-// Sticky status word raised by a kernel whose bounded wait gave up
-// (gemv_ring.cuh).  Read and cleared by feather_device_status().
-__device__ unsigned int g_wait_status;
-
+// g_wait_status (gemv_common.cuh): the sticky status word of the device.
 static int status_word(unsigned int** ptr) {
     static std::atomic<unsigned int*> cached[64];
     int dev = 0;
@@ -332,7 +329,7 @@ static int gemv_ring_launch(const uint32_t* m, const uint32_t* v, float* out, lo
     if (grid > max_useful) grid = max_useful;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(G::kThreads);
+    cfg.blockDim = dim3(FUSED ? G::kThreadsFused : G::kThreads);
     cfg.dynamicSmemBytes = G::kSmemBytes;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
@@ -735,7 +732,15 @@ using namespace feather;
 
 extern "C" {
 
-int feather_version(void) { return 200; /* 0.2.0: + packed-output, multi-vector and all-reduce GEMV, ReLU, attention */ }
+int feather_version(void) { return 300; /* 0.3.0: + GEMV chain in one launch, split-phase sharded GEMV, ring dot */ }
+
+int feather_debug_bounds(void) {
+#ifdef FEATHER_DEBUG_BOUNDS
+    return 1;
+#else
+    return 0;
+#endif
+}
 
 const char* feather_strerror(int status) {
     switch (status) {
@@ -747,6 +752,7 @@ const char* feather_strerror(int status) {
         case FEATHER_ERR_LAUNCH: return "CUDA reported an error at launch";
         case FEATHER_ERR_WORKSPACE: return "workspace is missing or too small";
         case FEATHER_ERR_TIMEOUT: return "a bounded device-side wait gave up";
+        case FEATHER_ERR_BOUNDS: return "debug build: a kernel formed an index outside its buffer (access skipped)";
         case FEATHER_ERR_TOO_LARGE: return "size exceeds what this entry point covers (built-in scratch, inbox, resident grid or model dimension)";
         default: return "unknown feather status";
     }
@@ -989,13 +995,22 @@ int feather_gemv_fp8_sharded(const uint32_t* m_local, const uint32_t* v, int64_t
                              int64_t N, int mode, float* const* peer_out,
                              uint32_t* const* peer_flags, int rank, int world, uint32_t epoch,
                              void* stream) {
+    return feather_gemv_fp8_sharded_ex(m_local, v, rows_local, N, mode, peer_out, peer_flags, rank, world,
+                                       epoch, 0u, nullptr, stream);
+}
+
+int feather_gemv_fp8_sharded_ex(const uint32_t* m_local, const uint32_t* v, int64_t rows_local,
+                                int64_t N, int mode, float* const* peer_out,
+                                uint32_t* const* peer_flags, int rank, int world, uint32_t epoch,
+                                uint32_t flags, uint64_t* stamps, void* stream) {
+    if (flags & ~(uint32_t)(FEATHER_GEMV_STATIC_MATRIX | FEATHER_SHARDED_NO_WAIT)) return FEATHER_ERR_BAD_ARG;
     if (rows_local <= 0 || N <= 0 || (N & 3) || rows_local > 0x7FFFFFFF || !peer_out || !peer_flags ||
         world < 1 || world > kMaxShardRanks || rank < 0 || rank >= world || epoch == 0 || !m_local || !v)
         return FEATHER_ERR_BAD_ARG;
     if (mode != FEATHER_MODE_E5M2 && mode != FEATHER_MODE_E4M3) return FEATHER_ERR_MODE;
     const DeviceInfo* dev;
     if (int st = device_info(&dev)) return st;
-    if (!aligned(v, 4)) return FEATHER_ERR_MISALIGNED;
+    if (!aligned(v, 4) || !aligned(stamps, 8)) return FEATHER_ERR_MISALIGNED;
     if (!ring_eligible(m_local, rows_local, N, *dev)) return FEATHER_ERR_BAD_ARG;
     ShardArgs sh = {};
     for (int p = 0; p < world; ++p) {
@@ -1008,6 +1023,8 @@ int feather_gemv_fp8_sharded(const uint32_t* m_local, const uint32_t* v, int64_t
     sh.rank = rank;
     sh.world = world;
     sh.epoch = epoch;
+    sh.no_wait = (flags & FEATHER_SHARDED_NO_WAIT) ? 1 : 0;
+    sh.stamps = reinterpret_cast<unsigned long long*>(stamps);
     {   // rows per CTA as the kernel will split them (grid = min(SMs, tasks))
         long long grid = dev->sm_count;
         const long long tasks = (rows_local + kRingCW * kRingRW - 1) / (kRingCW * kRingRW);
@@ -1016,9 +1033,38 @@ int feather_gemv_fp8_sharded(const uint32_t* m_local, const uint32_t* v, int64_t
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     float* mine = peer_out[rank] + sh.row_offset;
-    return mode == FEATHER_MODE_E5M2
-               ? gemv_ring_launch<kE5M2, true>(m_local, v, mine, rows_local, N, *dev, s, sh)
-               : gemv_ring_launch<kE4M3, true>(m_local, v, mine, rows_local, N, *dev, s, sh);
+    const bool early = (flags & FEATHER_GEMV_STATIC_MATRIX) != 0;
+    if (mode == FEATHER_MODE_E5M2)
+        return early ? gemv_ring_launch<kE5M2, true, true>(m_local, v, mine, rows_local, N, *dev, s, sh)
+                     : gemv_ring_launch<kE5M2, true>(m_local, v, mine, rows_local, N, *dev, s, sh);
+    return early ? gemv_ring_launch<kE4M3, true, true>(m_local, v, mine, rows_local, N, *dev, s, sh)
+                 : gemv_ring_launch<kE4M3, true>(m_local, v, mine, rows_local, N, *dev, s, sh);
+}
+
+int feather_gemv_fp8_sharded_wait(uint32_t* const* peer_flags, int rank, int world, uint32_t epoch,
+                                  uint64_t* stamps, void* stream) {
+    if (!peer_flags || world < 1 || world > kMaxShardRanks || rank < 0 || rank >= world || epoch == 0 ||
+        !peer_flags[rank])
+        return FEATHER_ERR_BAD_ARG;
+    if (!aligned(peer_flags[rank], 4) || !aligned(stamps, 8)) return FEATHER_ERR_MISALIGNED;
+    const DeviceInfo* dev;
+    if (int st = device_info(&dev)) return st;
+    unsigned int* status = nullptr;
+    if (int st = status_word(&status)) return st;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, shard_wait_kernel,
+                                             static_cast<const unsigned int*>(peer_flags[rank]), world,
+                                             (unsigned int)epoch, status,
+                                             reinterpret_cast<unsigned long long*>(stamps));
+    return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
 }
 
 int feather_gemv_fp8_allreduce(const uint32_t* m_local, const uint32_t* v_local, float* result,
@@ -1167,7 +1213,7 @@ int feather_device_status(void* stream) {
         return FEATHER_ERR_LAUNCH;
     if (host == 0) return FEATHER_OK;
     if (cudaMemsetAsync(status, 0, sizeof(host), s) != cudaSuccess) return FEATHER_ERR_LAUNCH;
-    return FEATHER_ERR_TIMEOUT;
+    return (host & 0x100u) ? FEATHER_ERR_BOUNDS : FEATHER_ERR_TIMEOUT;
 }
 
 int64_t feather_dot_workspace_bytes(int64_t n_words) {

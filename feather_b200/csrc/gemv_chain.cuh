@@ -183,7 +183,7 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
                     const int chunks = min(kChainSegChunks, g.n16 - seg * kChainSegChunks);
                     const uint32_t bytes = (uint32_t)chunks * 16u;
                     if (lane == 0) mbar_arrive_expect_tx(full_bar(s), bytes * (uint32_t)rows);
-                    if (lane < rows)
+                    if (lane < rows && bounds_ok(row0 + lane < d.M && (size_t)seg * kChainSegBytes + bytes <= row_bytes))
                         bulk_load(ring_s + s * kChainStageBytes + lane * kChainSegBytes,
                                   d.m + (size_t)(row0 + lane) * row_bytes + (size_t)seg * kChainSegBytes,
                                   bytes, full_bar(s));
@@ -322,7 +322,7 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
                 if (has_row) {
                     float sums[1] = {(acc[0] + acc[1]) + (acc[2] + acc[3])};
                     warp_reduce_rows<1>(sums, lane);
-                    if (lane == 0) {
+                    if (lane == 0 && bounds_ok(row >= 0 && row < d.M)) {
                         const int out_mode = d.out_mode();
                         if (out_mode < 0) {
                             reinterpret_cast<float*>(d.out)[row] = sums[0];

@@ -85,6 +85,25 @@ __device__ __forceinline__ void warp_reduce_rows(float (&v)[RW], int lane) {
 __device__ unsigned long long g_wait_limit_ns = 2000000000ull;
 #define kWaitLimitNs g_wait_limit_ns
 
+// Sticky status word: bit 0 / 1 / 2 raised by a bounded wait that gave up
+// (ring stage / peer rank / chain dependency), bit 8 by a bounds guard of a
+// -DFEATHER_DEBUG_BOUNDS build.  Read and cleared by feather_device_status().
+__device__ unsigned int g_wait_status;
+
+// Debug builds (-DFEATHER_DEBUG_BOUNDS, the stand-in for a memory checker):
+// every global-memory index the GEMV kernels form is checked against its
+// buffer; a bad one raises bit 8 of the status word and the access is skipped.
+// Release builds compile the guard away.
+__device__ __forceinline__ bool bounds_ok(bool ok) {
+#ifdef FEATHER_DEBUG_BOUNDS
+    if (!ok) atomicOr(&g_wait_status, 0x100u);
+    return ok;
+#else
+    (void)ok;
+    return true;
+#endif
+}
+
 __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

@@ -84,7 +84,8 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
             const int c = c0 + u * 32 + lane;
 #pragma unroll
             for (int r = 0; r < RW; ++r)
-                buf[u][r] = (on && c < n16) ? ldg_stream(rp[r] + c) : make_uint4(0, 0, 0, 0);
+                buf[u][r] = (on && c < n16 && bounds_ok(rp[r] + c >= m && rp[r] + c < m + (size_t)M * n16))
+                                ? ldg_stream(rp[r] + c) : make_uint4(0, 0, 0, 0);
         }
     };
     if (EARLY) issue(rows, active, 0);
@@ -123,7 +124,7 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
             if ((lane & (32 / RW - 1)) == 0) {
                 const int row = row0 + lane / (32 / RW);
                 if (ALLREDUCE || out_code >= 0) ar_part[warp * RW + lane / (32 / RW)] = row < M ? sums[0] : 0.f;
-                else if (row < M) out[row] = sums[0];
+                else if (row < M && bounds_ok(row >= 0)) out[row] = sums[0];
             }
         } else if (ALLREDUCE || out_code >= 0) {
             if (lane < RW) ar_part[warp * RW + lane] = 0.f;
@@ -141,7 +142,8 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
                     const uint32_t c = out_code == kE5M2 ? encode_f32<kE5M2>(x) : encode_f32<kE4M3>(x);
                     word |= (live ? c : 0u) << (8 * i);
                 }
-                reinterpret_cast<uint32_t*>(out)[cta_row0 / 4 + threadIdx.x] = word;
+                if (bounds_ok(cta_row0 / 4 + (int)threadIdx.x < (M + 3) / 4))
+                    reinterpret_cast<uint32_t*>(out)[cta_row0 / 4 + threadIdx.x] = word;
             }
             __syncthreads();  // ar_part is free for the next row group
         }
@@ -156,7 +158,8 @@ gemv_rows_kernel(const uint4* __restrict__ m, const uint32_t* __restrict__ v,
         const int w_valid = tile_chunks * 4, w_fill = ((tile_chunks + 31) / 32) * 128;
         for (int wl = threadIdx.x; wl < w_fill; wl += kRowsThreads) {
             uint32_t lo, hi;
-            decode_word_h2<MODE>(wl < w_valid ? __ldg(v + t0 * 4 + wl) : 0u, lo, hi);
+            decode_word_h2<MODE>(wl < w_valid && bounds_ok(t0 * 4 + wl < n16 * 4) ? __ldg(v + t0 * 4 + wl) : 0u,
+                                 lo, hi);
             const int chunk = wl >> 2, k = wl & 3;
             vec2[(((chunk >> 5) * 2 + (k >> 1)) * 32 + (chunk & 31)) * 2 + (k & 1)] = make_uint2(lo, hi);
         }
@@ -292,6 +295,7 @@ gemv_general_kernel(const uint32_t* __restrict__ m, const uint32_t* __restrict__
         const uint32_t* mr = m + (size_t)row * n_words;
         float2 a0 = make_float2(0.f, 0.f), a1 = a0;
         for (int w = lane; w < n_words; w += 32) {
+            if (!bounds_ok(row >= 0 && row < M && w < n_words)) break;
             float2 mlo, mhi, vlo, vhi;
             decode_word<MODE>(__ldg(mr + w), mlo, mhi);
             decode_word<MODE>(__ldg(v + w), vlo, vhi);

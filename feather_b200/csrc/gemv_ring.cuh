@@ -101,9 +101,14 @@ struct ShardArgs {
     long long row_offset;                // first global row of this rank's block
     int rank, world;
     unsigned int epoch;                  // this call's number, increasing by one per call
-    int staged;                          // 1: every CTA owns <= kShardStageRows rows and pushes them
-                                         //    to the peers as ONE coalesced block when it is done;
+    int staged;                          // 1: every CTA owns <= kShardStageRows rows; a dedicated warp
+                                         //    pushes each task's rows to the peers, coalesced, as soon
+                                         //    as the task is done;
                                          // 0: each row is stored to the peers as it finishes
+    int no_wait;                         // 1: the kernel ends once its rows and its epoch are on their
+                                         //    way; the caller waits for the peers' epochs separately
+    unsigned long long* stamps;          // optional (may be null): %globaltimer of the rank's last CTA
+                                         //    [0] rows pushed, [1] epoch published, [2] all epochs seen
 };
 template <int CW, int RW, int CL, int STAGES, int TILE>
 struct RingGeometry {
@@ -116,9 +121,11 @@ struct RingGeometry {
     static constexpr int kVecBytes = TILE * 2;         // FP16 vector region (one tile or two halves)
     // mbarriers: full[STAGES], empty[STAGES], start, vec_full[2], vec_empty[2]; then one counter word
     static constexpr int kBarriers = 2 * STAGES + 5;
+    static constexpr int kMaxTasks = 64;               // per-task arrival counters of a fused launch
     static constexpr int kSmemBytes = kVecBytes + STAGES * kStageBytes + (kBarriers + 1) * 8 +
-                                      kShardStageRows * 4;
+                                      kShardStageRows * 4 + kMaxTasks * 4;
     static constexpr int kThreads = (CW + 2) * 32;     // consumers, producer warp, vector warp
+    static constexpr int kThreadsFused = (CW + 3) * 32;  // + the exchange warp of a row-sharded launch
     static_assert(kHalfChunks % kSegChunks == 0, "a vector half holds whole segments");
 };
 
@@ -139,7 +146,7 @@ __device__ __forceinline__ void stage_vector(uint4* dst, const uint32_t* __restr
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
             const int wl = w0 + b * n_threads;
-            raw[b] = wl < w_valid ? __ldg(v + wl) : 0u;  // beyond N: code 0 = +0.0
+            raw[b] = wl < w_valid && bounds_ok(wl >= 0) ? __ldg(v + wl) : 0u;  // beyond N: code 0 = +0.0
         }
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
@@ -169,10 +176,20 @@ __device__ __forceinline__ void stage_vector(uint4* dst, const uint32_t* __restr
 // FUSED: the kernel is one rank of a row-sharded GEMV.  Finished rows are
 // stored straight into EVERY rank's output buffer (plain stores to peer-mapped
 // memory over NVLink), so the gather of the output slices happens inside the
-// GEMV instead of in a separate collective.  When the last CTA of the rank is
-// done it publishes the call's epoch in every rank's flag block and then waits
-// (bounded) until all ranks have published theirs here: when the kernel ends,
-// this rank's buffer holds the full result.
+// GEMV instead of in a separate collective.  An extra warp does the exchange:
+// it waits (shared-memory counters) for each task's rows, pushes them to all
+// ranks as coalesced 64-byte runs while the consumers go on with the next
+// task, and at the end takes the rank's CTA ticket.  The last CTA of the rank
+// publishes the call's epoch in every rank's flag block.  Before the first
+// push of call e the exchange warp makes sure every peer has delivered call
+// e - 1: a peer that has delivered e - 1 has been launched for it, so the
+// result of call e - 2 in the buffer about to be overwritten (two buffers
+// alternate by epoch parity) is no longer wanted -- a result is valid until the
+// rank's next call.  Then either the last CTA waits (bounded) until all ranks'
+// epochs have arrived here, so that the buffer holds the full result when the
+// kernel ends, or (sh.no_wait) it returns and the caller waits separately
+// (shard_wait_kernel) before it reads the result: the exchange latency and the
+// skew between ranks then overlap the next call instead of ending every call.
 // EARLY: the caller promises that nothing earlier in the stream writes the
 // MATRIX (static weights).  The producer warp then starts streaming matrix
 // bytes before the stream-order wait, so a kernel that was launched early
@@ -180,7 +197,7 @@ __device__ __forceinline__ void stage_vector(uint4* dst, const uint32_t* __restr
 // drains; the vector is read and the output written only after the wait.
 template <int MODE, int CW, int RW, int CL, int STAGES, int TILE, int CTAS, bool PREFETCH,
           bool FUSED = false, bool EARLY = false>
-__global__ void __launch_bounds__((CW + 2) * 32, CTAS)
+__global__ void __launch_bounds__((CW + 2 + (FUSED ? 1 : 0)) * 32, CTAS)
 gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict__ v,
                  float* __restrict__ out, int M, int n16, unsigned int* __restrict__ status,
                  int pre_bytes, const __grid_constant__ ShardArgs sh = ShardArgs{}) {
@@ -203,6 +220,7 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
     auto vec_empty = [&](int b) { return bars + 8u * (2 * STAGES + 3 + b); };
     unsigned int* warps_done = reinterpret_cast<unsigned int*>(bar_mem + 8 * G::kBarriers);
     float* staged_rows = reinterpret_cast<float*>(bar_mem + 8 * (G::kBarriers + 1));
+    unsigned int* task_cnt = reinterpret_cast<unsigned int*>(staged_rows + kShardStageRows);
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row_begin = (int)(((long long)M * blockIdx.x) / gridDim.x);
@@ -230,6 +248,8 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
             mbar_init(vec_empty(b), CW);   // one arrive per consumer warp
         }
         *warps_done = 0u;
+        if (FUSED)
+            for (int t = 0; t < G::kMaxTasks; ++t) task_cnt[t] = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (!EARLY && warp == CW && pre_bytes > 0) {
@@ -249,6 +269,102 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
     __syncthreads();
     if (!EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (n_tasks == 0 && !FUSED) return;  // a fused rank needs every CTA at the final ticket
+
+    if (FUSED && warp == CW + 2) {
+        // -------------------------------------------------- exchange warp --
+        if (EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");  // it writes the outputs
+        unsigned int* my_flags = sh.flags[sh.rank];
+        if (sh.staged && n_tasks > 0) {
+            // every peer must have delivered the call before this one (see above)
+            if (lane < sh.world) {
+                const unsigned int need = sh.epoch - 1u;
+                if ((int)(ld_relaxed_sys(my_flags + lane) - need) < 0) {
+                    const unsigned long long t0 = global_timer_ns();
+                    while ((int)(ld_relaxed_sys(my_flags + lane) - need) < 0) {
+                        if (global_timer_ns() - t0 > kWaitLimitNs) {
+                            atomicOr(status, 2u);  // rank `lane` never delivered the previous call
+                            break;
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            bool alive = true;
+            for (int task = 0; task < n_tasks && alive; ++task) {
+                const int t_row0 = task * task_rows;                       // CTA-local
+                const int t_rows = min(task_rows, row_end - row_begin - t_row0);
+                // the consumers count every finished row of the task in task_cnt[task]
+                const volatile unsigned int* cnt = task_cnt + task;
+                if (*cnt < (unsigned int)t_rows) {
+                    const unsigned long long t0 = global_timer_ns();
+                    while (*cnt < (unsigned int)t_rows) {
+                        __nanosleep(64);
+                        if (global_timer_ns() - t0 > kWaitLimitNs) {
+                            atomicOr(status, 1u);
+                            alive = false;
+                            break;
+                        }
+                    }
+                }
+                __threadfence_block();   // the rows counted above are visible to this warp
+                if (!alive) break;
+                // two ranks per pass: lanes 0-15 and 16-31 each store one 64-byte run
+                const int i = lane & 15;
+                for (int k = 0; k < sh.world; k += 2) {
+                    const int kk = k + (lane >> 4);
+                    if (kk < sh.world && i < t_rows && bounds_ok(row_begin + t_row0 + i < M)) {
+                        const int p = (sh.rank + kk) % sh.world;  // own buffer first, then round the ring
+                        sh.out[p][sh.row_offset + row_begin + t_row0 + i] = staged_rows[t_row0 + i];
+                    }
+                }
+            }
+        }
+        // All rows of this CTA are on their way (staged mode) or were stored by the consumers:
+        // wait for the consumers' count in the other mode, then take the rank's ticket.
+        if (!sh.staged) {
+            const volatile unsigned int* cnt = warps_done;
+            const unsigned long long t0 = global_timer_ns();
+            while (*cnt < (unsigned int)CW) {
+                __nanosleep(64);
+                if (global_timer_ns() - t0 > kWaitLimitNs) {
+                    atomicOr(status, 1u);
+                    break;
+                }
+            }
+        }
+        __syncwarp();
+        __threadfence_system();  // the pushed rows are visible everywhere before the ticket
+        unsigned int ticket = 0;
+        if (lane == 0) ticket = atomicAdd(my_flags + kShardTicketWord, 1u);
+        ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
+        if (ticket == gridDim.x - 1) {
+            // last CTA of this rank: lane q tells rank q "my slice is with you"
+            if (lane == 0) {
+                my_flags[kShardTicketWord] = 0u;  // ready for the next call
+                if (sh.stamps) sh.stamps[0] = global_timer_ns();
+            }
+            __threadfence_system();
+            if (lane < sh.world) st_relaxed_sys(sh.flags[lane] + sh.rank, sh.epoch);
+            if (lane == 0 && sh.stamps) sh.stamps[1] = global_timer_ns();
+            if (!sh.no_wait) {
+                // ... and waits for rank q's slice here -- all peers in parallel
+                if (lane < sh.world) {
+                    const unsigned long long t0 = global_timer_ns();
+                    // wrap-safe "flag has reached this epoch"
+                    while ((int)(ld_relaxed_sys(my_flags + lane) - sh.epoch) < 0) {
+                        if (global_timer_ns() - t0 > kWaitLimitNs) {
+                            atomicOr(status, 2u);  // rank `lane`'s slice did not arrive in time
+                            break;
+                        }
+                    }
+                }
+                __syncwarp();
+                __threadfence_system();  // the peers' rows are visible to whatever runs next
+                if (lane == 0 && sh.stamps) sh.stamps[2] = global_timer_ns();
+            }
+        }
+        return;
+    }
 
     if (warp == CW + 1) {
         // ---------------------------------------------------- vector warp --
@@ -296,8 +412,9 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
                     if (lane == 0) mbar_arrive_expect_tx(full_bar(s), bytes * (uint32_t)valid_rows);
                     const size_t col = ((size_t)piece * piece_chunks + (size_t)seg * G::kSegChunks) * 16;
                     for (int r = lane; r < valid_rows; r += 32)
-                        bulk_load(ring_s + s * G::kStageBytes + r * G::kSegBytes,
-                                  m + (size_t)(row0 + r) * row_bytes + col, bytes, full_bar(s));
+                        if (bounds_ok(row0 + r < M && col + bytes <= row_bytes && r < G::kTaskRows))
+                            bulk_load(ring_s + s * G::kStageBytes + r * G::kSegBytes,
+                                      m + (size_t)(row0 + r) * row_bytes + col, bytes, full_bar(s));
                     if (++s == STAGES) { s = 0; ++round; }
                 }
             }
@@ -396,10 +513,12 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
                         if (smem_acc) staged_rows[row - row_begin] = total;
                         else partial[row] = total;  // the same lane owns the row in every piece
                     } else if (!FUSED) {
-                        out[row] = total;
+                        if (bounds_ok(row >= 0 && row < M)) out[row] = total;
                     } else if (sh.staged) {
-                        // the CTA's rows are pushed once, coalesced, when the CTA is done
+                        // the exchange warp pushes the task's rows once all of them are here
                         staged_rows[row - row_begin] = total;
+                        __threadfence_block();
+                        atomicAdd(task_cnt + task, 1u);
                     } else {
                         for (int p = 0; p < sh.world; ++p) sh.out[p][sh.row_offset + row] = total;
                         __threadfence_system();  // before this warp reports itself finished
@@ -413,52 +532,34 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
             if (lane == 0) mbar_arrive(vec_empty(piece & 1));  // this warp is done with the piece
         }
     }
-    if (FUSED) {
-        // This warp's rows are finished.  The last consumer warp of the CTA
-        // delivers the CTA's block to every rank, then the last CTA of the rank
-        // signals the peers and waits for their signals.
-        __threadfence_block();
+    if (FUSED && !sh.staged) {
+        // rows went to the peers one by one: tell the exchange warp this warp is done
         __syncwarp();
-        unsigned int arrived = 0;
-        if (lane == 0) arrived = atomicAdd(warps_done, 1u);
-        arrived = __shfl_sync(0xFFFFFFFFu, arrived, 0);
-        if (arrived == CW - 1) {
-            __threadfence_block();
-            if (sh.staged) {
-                const int n_rows = row_end - row_begin;
-                for (int k = 0; k < sh.world; ++k) {
-                    const int p = (sh.rank + k) % sh.world;  // own buffer first, then round the ring
-                    float* dst = sh.out[p] + sh.row_offset + row_begin;
-                    for (int i = lane; i < n_rows; i += 32) dst[i] = staged_rows[i];
-                }
-            }
-            __threadfence_system();  // the pushed rows are visible everywhere before the ticket
-            __syncwarp();
-            unsigned int* my_flags = sh.flags[sh.rank];
-            unsigned int ticket = 0;
-            if (lane == 0) ticket = atomicAdd(my_flags + kShardTicketWord, 1u);
-            ticket = __shfl_sync(0xFFFFFFFFu, ticket, 0);
-            if (ticket == gridDim.x - 1) {
-                // last CTA of this rank: lane q tells rank q "my slice is with you"
-                // and waits for rank q's slice here -- all peers in parallel
-                if (lane == 0) my_flags[kShardTicketWord] = 0u;  // ready for the next call
-                __threadfence_system();
-                if (lane < sh.world) {
-                    st_relaxed_sys(sh.flags[lane] + sh.rank, sh.epoch);
-                    const unsigned long long t0 = global_timer_ns();
-                    // wrap-safe "flag has reached this epoch"
-                    while ((int)(ld_relaxed_sys(my_flags + lane) - sh.epoch) < 0) {
-                        if (global_timer_ns() - t0 > kWaitLimitNs) {
-                            atomicOr(status, 2u);  // rank `lane`'s slice did not arrive in time
-                            break;
-                        }
-                    }
-                }
-                __syncwarp();
-                __threadfence_system();  // the peers' rows are visible to whatever runs next
+        if (lane == 0) atomicAdd(warps_done, 1u);
+    }
+}
+
+// Second half of a split-phase row-sharded call (sh.no_wait): returns once every
+// rank's epoch has reached `epoch` in this rank's flag block, i.e. once all
+// slices of that call sit in this rank's output buffer.  One warp; bounded.
+__global__ void __launch_bounds__(32)
+shard_wait_kernel(const unsigned int* __restrict__ my_flags, int world, unsigned int epoch,
+                  unsigned int* __restrict__ status, unsigned long long* __restrict__ stamps) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int lane = threadIdx.x;
+    if (lane < world) {
+        const unsigned long long t0 = global_timer_ns();
+        while ((int)(ld_relaxed_sys(my_flags + lane) - epoch) < 0) {
+            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                atomicOr(status, 2u);
+                break;
             }
         }
     }
+    __syncwarp();
+    __threadfence_system();
+    if (lane == 0 && stamps) stamps[2] = global_timer_ns();
 }
 
 }  // namespace feather

@@ -20,10 +20,13 @@ Two exchange paths:
   all-gather.
 * ``fused=True`` (default on GPUs when the shape allows it): the GEMV kernel
   itself stores every finished row into all ranks' output buffers through
-  peer-mapped memory (``feather_gemv_fp8_sharded``), so the exchange overlaps
-  the streaming of the matrix and costs one NVLink round trip at the end
-  instead of a collective launch.  The buffers are shared between the ranks'
-  processes with CUDA IPC (torch's own tensor sharing).
+  peer-mapped memory (``feather_gemv_fp8_sharded_ex``), so the exchange
+  overlaps the streaming of the matrix and there is no collective launch.
+  ``op(v)`` returns when all slices have arrived; ``op(v, wait=False)`` ends
+  the call as soon as this rank's rows are on their way and ``op.wait()``
+  completes it later, so that the exchange latency and the skew between the
+  ranks overlap whatever is enqueued in between (the next call, for one).  The
+  buffers are shared between the ranks' processes with CUDA IPC.
 
 One process per GPU over ``torch.distributed`` (NCCL on GPUs).  The local
 compute is injectable so that the partition / gather plumbing can be tested
@@ -150,13 +153,20 @@ class RowShardedGemv:
         NCCL all-gather, None = fused when the operands are on GPUs, the world
         has more than one rank and the kernel supports the shape.
 
-    The result of ``op(v)`` is the object's own buffer.  In fused mode two
-    buffers alternate, so a result stays valid until the call after the next.
+    static_matrix : promise that nothing in flight writes ``m_local`` (fused
+        mode: the kernel starts streaming before its stream-order wait).
+
+    The result of ``op(v)`` is the object's own buffer and stays valid until
+    the next call on THIS rank is enqueued.  (In fused mode two buffers
+    alternate, and a peer writes call k+2 into the buffer of call k only after
+    every rank has delivered call k+1 -- which a rank does only once it has
+    been launched for call k+1.)
     """
 
     def __init__(self, m_local: torch.Tensor, m_shape, mode: str = "E5M2",
                  group: Optional[dist.ProcessGroup] = None,
-                 local_gemv: Optional[Callable] = None, fused: Optional[bool] = None):
+                 local_gemv: Optional[Callable] = None, fused: Optional[bool] = None,
+                 static_matrix: bool = False):
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed is not initialised")
         self.group = group
@@ -173,6 +183,8 @@ class RowShardedGemv:
                              f"{self.rows}x{self.N} needs {need}")
         self.m_local = m_local
         self.mode = mode
+        self.static_matrix = bool(static_matrix)
+        self._pending = 0   # epoch of a fused call whose arrival wait has not been enqueued yet
         custom_compute = local_gemv is not None
         if local_gemv is None:
             from .routines.gemv import gemv_fp8_acc_fp32_gpu
@@ -227,7 +239,9 @@ class RowShardedGemv:
             self._flag_ptrs = arr(*[b + 4 * 2 * self.M for b in base])
             self._views = [self._shared[: self.M], self._shared[self.M: 2 * self.M]]
             self._lib, self._check = lib, _lib.check
-            self._fn = lib.feather_gemv_fp8_sharded
+            self._fn = lib.feather_gemv_fp8_sharded_ex
+            self._wait_fn = lib.feather_gemv_fp8_sharded_wait
+            self._stamps = None
             self._m_ptr = self.m_local.data_ptr()
             self._n_words = self.N // 4
             self._dev, self._dev_index = dev, dev.index
@@ -250,7 +264,7 @@ class RowShardedGemv:
             self._mapped = []
             self.fused = False
 
-    def _call_fused(self, v_packed: torch.Tensor) -> torch.Tensor:
+    def _call_fused(self, v_packed: torch.Tensor, wait: bool) -> torch.Tensor:
         # hot path: everything that does not change between calls was prepared in
         # _setup_fused; operands may be PackedFP8 subclasses, so metadata reads
         # skip the Python-level __torch_function__ dispatch
@@ -263,14 +277,39 @@ class RowShardedGemv:
         idx = self._dev_index
         if torch.cuda.current_device() != idx:
             with torch.cuda.device(idx):
-                return self._launch_fused(v_ptr, k, idx)
-        return self._launch_fused(v_ptr, k, idx)
+                return self._launch_fused(v_ptr, k, idx, wait)
+        return self._launch_fused(v_ptr, k, idx, wait)
 
-    def _launch_fused(self, v_ptr: int, k: int, idx: int) -> torch.Tensor:
+    def _launch_fused(self, v_ptr: int, k: int, idx: int, wait: bool) -> torch.Tensor:
+        flags = (1 if self.static_matrix else 0) | (0 if wait else 2)
+        stamps = None if self._stamps is None else self._stamps.data_ptr()
         self._check(self._fn(self._m_ptr, v_ptr, self.rows, self.N, self._mode_id,
                              self._out_ptrs[k], self._flag_ptrs, self.rank, self.world_size,
-                             (self._epoch & 0xFFFFFFFF) or 1, self._stream_ptr(idx)))
+                             (self._epoch & 0xFFFFFFFF) or 1, flags, stamps, self._stream_ptr(idx)))
+        self._pending = 0 if wait else self._epoch
         return self._views[k]
+
+    def wait(self) -> None:
+        """Complete a call made with ``wait=False``: enqueue, on the current
+        stream, the wait for all ranks' slices of the latest call.  Until then
+        only this rank's own rows of the returned buffer are defined."""
+        if not self.fused or not self._pending:
+            return
+        idx = self._dev_index
+        with torch.cuda.device(idx):
+            stamps = None if self._stamps is None else self._stamps.data_ptr()
+            self._check(self._wait_fn(self._flag_ptrs, self.rank, self.world_size,
+                                      (self._pending & 0xFFFFFFFF) or 1, stamps, self._stream_ptr(idx)))
+        self._pending = 0
+
+    def record_stamps(self, on: bool = True) -> None:
+        """Have the kernels record the GPU timer of this rank's last CTA (rows
+        pushed, epoch published, all epochs seen) into ``self.stamps()``."""
+        self._stamps = (torch.zeros(3, dtype=torch.int64, device=self.m_local.device) if on else None)
+
+    def stamps(self):
+        torch.cuda.synchronize(self.m_local.device)
+        return None if self._stamps is None else [int(x) for x in self._stamps.tolist()]
 
     def _check_agreement(self) -> None:
         """Every rank must describe the same global problem."""
@@ -289,11 +328,12 @@ class RowShardedGemv:
         self._local_gemv(self.m_local, v_packed, (self.rows, self.N), self.mode, out=mine)
         return mine
 
-    def __call__(self, v_packed: torch.Tensor) -> torch.Tensor:
+    def __call__(self, v_packed: torch.Tensor, wait: bool = True) -> torch.Tensor:
         """Full ``(M,)`` FP32 result on every rank.  The returned tensor is the
-        object's own buffer and is overwritten by the next call."""
+        object's own buffer and is valid until this rank's next call.
+        ``wait=False`` (fused mode): see ``wait()``."""
         if self.fused:
-            return self._call_fused(v_packed)
+            return self._call_fused(v_packed, wait)
         mine = self.local(v_packed)
         if self.world_size > 1:
             # in place: rank r's slice already sits at offset r * rows

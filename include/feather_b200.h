@@ -35,6 +35,7 @@ typedef enum feather_status {
     FEATHER_ERR_LAUNCH = -5,      /* CUDA reported a launch error               */
     FEATHER_ERR_WORKSPACE = -6,   /* workspace missing or too small             */
     FEATHER_ERR_TIMEOUT = -7,     /* a bounded device-side wait gave up         */
+    FEATHER_ERR_BOUNDS = -9,      /* -DFEATHER_DEBUG_BOUNDS build: an index left its buffer */
     FEATHER_ERR_TOO_LARGE = -8    /* beyond what the entry point covers: built-in scratch, inbox, resident grid, model dimension */
 } feather_status;
 
@@ -47,6 +48,12 @@ typedef enum feather_status {
 
 /* Library version: major * 10000 + minor * 100 + patch. */
 int feather_version(void);
+
+/* 1 if the library was built with -DFEATHER_DEBUG_BOUNDS (every global-memory
+ * index of the GEMV kernels checked on the device, violations reported by
+ * feather_device_status() as FEATHER_ERR_BOUNDS), else 0.  No counterpart in
+ * the reference. */
+int feather_debug_bounds(void);
 
 /* Static, NUL-terminated description of a feather_status value. */
 const char* feather_strerror(int status);
@@ -210,7 +217,11 @@ int64_t feather_gemv_fp8_packed_workspace_bytes(int64_t M, int64_t N);
  *   epoch       1 for the first call, +1 for every later call, equal on all
  *               ranks.  Use two output buffers alternately (even / odd epoch):
  *               a fast rank may start writing call k+1 while a slow rank's
- *               consumer still reads call k.  Because the epoch is a launch
+ *               consumer still reads call k.  A rank stores call k+2 into the
+ *               peers' buffers only once every peer has delivered call k+1,
+ *               i.e. has been launched for it: the result of call k is valid
+ *               until THIS rank's call k+1 is enqueued, not longer.  Because
+ *               the epoch is a launch
  *               argument, a captured CUDA graph of this call must not be
  *               replayed (the second replay would find its epoch already
  *               published and not wait); launch it from the stream.
@@ -223,6 +234,35 @@ int feather_gemv_fp8_sharded(const uint32_t* m_local, const uint32_t* v, int64_t
                              uint32_t* const* peer_flags, int rank, int world, uint32_t epoch,
                              void* stream);
 int feather_gemv_fp8_sharded_supported(int64_t rows_local, int64_t N);
+
+/*
+ * feather_gemv_fp8_sharded with options.  No reference counterpart, as above.
+ *   flags   FEATHER_GEMV_STATIC_MATRIX  as feather_gemv_fp8_ex.
+ *           FEATHER_SHARDED_NO_WAIT     split-phase completion: the kernel ends
+ *             once this rank's rows and its epoch are on their way to the
+ *             peers; it does NOT wait for the peers' slices.  The caller runs
+ *             feather_gemv_fp8_sharded_wait(..., epoch, ...) on the same stream
+ *             before anything reads the result.  Exchange latency and the skew
+ *             between ranks then overlap the next call (or whatever else the
+ *             stream holds) instead of ending every call.  Results stay valid
+ *             until this rank's next sharded call is enqueued, as above.
+ *   stamps  NULL, or 3 device uint64 (8-byte aligned) that receive the GPU's
+ *           nanosecond timer from the rank's last CTA: [0] all rows pushed,
+ *           [1] epoch published, [2] all ranks' epochs seen (written by the
+ *           kernel without NO_WAIT, else by feather_gemv_fp8_sharded_wait).
+ *           For measuring how a step's time splits into fence / flag latency
+ *           and waiting for the slowest rank.
+ * feather_gemv_fp8_sharded_wait enqueues a one-warp kernel that returns when
+ * every rank's epoch in peer_flags[rank] has reached `epoch` (bounded like the
+ * other waits; see feather_device_status).
+ */
+#define FEATHER_SHARDED_NO_WAIT 2u
+int feather_gemv_fp8_sharded_ex(const uint32_t* m_local, const uint32_t* v, int64_t rows_local,
+                                int64_t N, int mode, float* const* peer_out,
+                                uint32_t* const* peer_flags, int rank, int world, uint32_t epoch,
+                                uint32_t flags, uint64_t* stamps, void* stream);
+int feather_gemv_fp8_sharded_wait(uint32_t* const* peer_flags, int rank, int world, uint32_t epoch,
+                                  uint64_t* stamps, void* stream);
 
 /*
  * One rank of a COLUMN-sharded GEMV with the all-reduce of the partial results

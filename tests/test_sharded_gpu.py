@@ -1,5 +1,5 @@
-"""Row-sharded GEMV on real GPUs (NCCL).  World size 1 always runs; world size
-2 runs when the box has two GPUs."""
+"""Row-sharded GEMV on real GPUs (NCCL).  World size 1 always runs; world
+sizes 2, 4 and 8 run when the box has that many GPUs."""
 import os
 import socket
 import sys
@@ -35,7 +35,7 @@ def _worker(rank: int, world: int, port: int, q):
         from feather_b200.sharded import RowShardedGemv, local_words
         from oracle import c_oracle as C
         from oracle import feather_oracle as O
-        M, N, mode = 9472, 8192, "E4M3"   # 4736 rows per rank at world 2: the ring kernel
+        M, N, mode = 4736 * world, 8192, "E4M3"   # 4736 rows per rank: the ring kernel
         gen = torch.Generator(device="cuda").manual_seed(77)  # same data on every rank
         A = torch.randn(M, N, device="cuda", generator=gen, dtype=torch.float16)
         v = torch.randn(N, device="cuda", generator=gen, dtype=torch.float16)
@@ -53,6 +53,26 @@ def _worker(rank: int, world: int, port: int, q):
                 # rows never interact, so the sharded result has the single-GPU bits
                 ok_bits &= bool(torch.equal(y, y_single))
                 ok_err &= O.normalised_error(y.cpu().numpy(), ref) < 1e-5
+            if op.fused:
+                # split-phase: calls that do not wait for the peers' slices, back to back, then
+                # one wait; each result is checked after the wait that completes it
+                for it in range(5):
+                    y = op(vw, wait=False)
+                    if it % 2 == 0:
+                        op.wait()
+                        ok_bits &= bool(torch.equal(y, y_single))
+                op.wait()
+                ok_bits &= bool(torch.equal(y, y_single))
+                # a different vector through the same buffers: no stale rows survive
+                v2 = fb.pack_fp8_tensor(torch.randn(N, device="cuda", generator=gen, dtype=torch.float16), mode)
+                y2 = op(v2, wait=False)
+                op.wait()
+                ok_bits &= bool(torch.equal(y2, fb.gemv_fp8_acc_fp32_gpu(mw, v2, (M, N), mode)))
+                # the static-matrix variant
+                op_s = RowShardedGemv(local_words(mw, (M, N), world, rank), (M, N), mode, fused=True,
+                                      static_matrix=True)
+                ok_bits &= bool(torch.equal(op_s(vw), y_single))
+                op_s.close()
             fb.device_status()
         # tensor-parallel GEMV chain (one layer + lm_head) against the single-GPU chain
         from feather_b200 import chain
@@ -133,7 +153,7 @@ def _run(world: int):
         procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
         for p in procs:
             p.start()
-        out = [q.get(timeout=180) for _ in range(world)]
+        out = [q.get(timeout=420) for _ in range(world)]
         for p in procs:
             p.join(timeout=60)
         if any(o[1] == "init failed" for o in out) and attempt < 2:
@@ -147,7 +167,8 @@ def test_row_sharded_world_1():
     assert _run(1) == [(0, True, True)]
 
 
-def test_row_sharded_world_2():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    assert _run(2) == [(0, True, True), (1, True, True)]
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_row_sharded_world_n(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    assert _run(world) == [(r, True, True) for r in range(world)]
