@@ -490,6 +490,13 @@ def run_ours(args) -> None:
                 tokens=20, fused_allreduce=True, merge_projections=True, check=True)
         except Exception as e:  # noqa: BLE001
             extra["tinyllama_gemv_chain_tensor_parallel_fused_allreduce"] = {"error": repr(e)}
+        try:  # each rank's whole token as ONE launch, the all-reduces inside it
+            extra["tinyllama_gemv_chain_tensor_parallel_one_launch"] = chain.measure_tp(
+                tokens=30, persistent=True, check=True)
+            extra["tinyllama_gemv_chain_tensor_parallel_one_launch_merged"] = chain.measure_tp(
+                tokens=30, persistent=True, merge_projections=True, check=True)
+        except Exception as e:  # noqa: BLE001
+            extra["tinyllama_gemv_chain_tensor_parallel_one_launch"] = {"error": repr(e)}
         parity["tp_chain_max_norm_err"] = {
             k.replace("tinyllama_gemv_chain_tensor_parallel", "tp"): v.get("max_norm_err_vs_single_gpu_chain")
             for k, v in extra.items() if k.startswith("tinyllama_gemv_chain_tensor_parallel")}

@@ -28,8 +28,9 @@ def _codes(n_words: int, seed: int) -> torch.Tensor:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", choices=("gemv", "dot", "encode", "decode", "relu", "multi", "packed", "attention"),
-                    default="gemv")
+    ap.add_argument("--op", choices=("gemv", "dot", "encode", "decode", "relu", "multi", "packed", "attention",
+                                     "chain"), default="gemv")
+    ap.add_argument("--layers", type=int, default=1, help="layers of the TinyLlama-shaped chain for --op chain")
     ap.add_argument("--batch", type=int, default=8, help="vectors per call for --op multi")
     ap.add_argument("--mode", choices=("E5M2", "E4M3"), default="E5M2")
     ap.add_argument("--M", type=int, default=16384)
@@ -38,7 +39,16 @@ def main() -> None:
     a = ap.parse_args()
     M, N = a.M, a.N
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if a.op == "gemv":
+    if a.op == "chain":
+        # the TinyLlama-shaped GEMV chain (a.layers layers + lm_head) as ONE launch; two weight
+        # sets alternate so that a launch never finds its weights in L2
+        from feather_b200 import chain
+        chains = [chain.PersistentGemvChain.from_chain(chain.GemvChain(a.mode, seed=6 + i, layers=a.layers))
+                  for i in range(2)]
+        call = lambda i: chains[i % 2].token()
+        nbytes = a.layers * sum(m * n for _, m, n in chain.LAYER_SHAPES) + chain.VOCAB * chain.HIDDEN
+        M, N = a.layers, 0
+    elif a.op == "gemv":
         mats = [_codes(M * N // 4, s) for s in (1, 2)]
         v = _codes(N // 4, 3)
         out = torch.empty(M, dtype=torch.float32, device="cuda")

@@ -49,6 +49,9 @@ SYMBOLS = {
     "feather_gemv_chain_plan_bytes": (_i64, [_i32]),
     "feather_gemv_chain_plan": (_i32, [_vp, _i32, _vp, _i64, _vp]),
     "feather_gemv_chain_fp8": (_i32, [_vp, _i32, ctypes.c_uint32, _vp]),
+    "feather_gemv_chain_inbox_floats": (_i64, [_i32, _i32, _i32]),
+    "feather_gemv_chain_fp8_tp": (_i32, [_vp, _i32, ctypes.c_uint32, _i32, _i32, _vp, _i64, _vp, _i32, _i32,
+                                         _vp]),
     "feather_gemv_fp8_ex": (_i32, [_vp, _vp, _vp, _i64, _i64, _i32, ctypes.c_uint32, _vp]),
     "feather_dot_fp8": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _vp]),
     "feather_dot_workspace_bytes": (_i64, [_i64]),
@@ -62,7 +65,7 @@ class ChainOp(ctypes.Structure):
     """feather_chain_op of include/feather_b200.h."""
     _fields_ = [("m", _vp), ("v", _vp), ("out", _vp), ("M", ctypes.c_int32), ("N", ctypes.c_int32),
                 ("mode", ctypes.c_int32), ("out_mode", ctypes.c_int32), ("wait_op", ctypes.c_int32),
-                ("reserved", ctypes.c_int32)]
+                ("allreduce", ctypes.c_int32)]
 
 
 _lib = None

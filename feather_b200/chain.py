@@ -103,9 +103,15 @@ class PersistentGemvChain:
     bit for bit ``gemv_fp8_ret_packed_gpu``) and ``wait_op`` (index of the
     earlier op that writes ``v``).  Missing outputs are allocated.  Every op's
     result has the bits of the single-op call on the same operands.
+
+    Tensor-parallel use (one process per GPU): ops with ``allreduce=True`` are
+    column-sharded -- ``m`` is this rank's column block, ``shape`` its LOCAL
+    (M, N/W), ``v`` the matching slice -- and their outputs are the sums over
+    the ranks, exchanged inside the kernel through ``ctx``, a
+    ``sharded.PeerAllReduce`` created with ``n_ops`` = the number of such ops.
     """
 
-    def __init__(self, ops, mode: str = "E4M3", static_matrix: bool = True):
+    def __init__(self, ops, mode: str = "E4M3", static_matrix: bool = True, ctx=None):
         import ctypes
         from ._lib import ChainOp
         from .packers.fp8 import as_words
@@ -144,8 +150,19 @@ class PersistentGemvChain:
             t.mode = fb._lib.mode_id(op.get("mode", mode))
             t.out_mode = -1 if out_mode is None else fb._lib.mode_id(out_mode)
             t.wait_op = int(op.get("wait_op", -1))
-            t.reserved = 0
+            t.allreduce = 1 if op.get("allreduce") else 0
         self.n_ops, self.device = len(ops), device
+        self.ctx = ctx
+        ar_rows = [int(op["shape"][0]) for op in ops if op.get("allreduce")]
+        self.n_allreduce, self.max_allreduce_rows = len(ar_rows), max(ar_rows, default=0)
+        if ar_rows:
+            if ctx is None:
+                raise ValueError("ops with allreduce=True need ctx=PeerAllReduce(max_rows, n_ops=...)")
+            need = int(self.lib.feather_gemv_chain_inbox_floats(self.n_allreduce, self.max_allreduce_rows,
+                                                                ctx.world_size))
+            if ctx.inbox_floats < need or ctx.device != device:
+                raise ValueError(f"the all-reduce context is too small ({ctx.inbox_floats} < {need} floats) "
+                                 "or lives on another device")
         nbytes = int(self.lib.feather_gemv_chain_plan_bytes(self.n_ops))
         self.plan = torch.empty(nbytes, dtype=torch.uint8, device=device)
         with torch.cuda.device(device):
@@ -156,9 +173,16 @@ class PersistentGemvChain:
     def token(self) -> None:
         idx = self.device.index
         with torch.cuda.device(idx):
-            fb._lib.check(self.lib.feather_gemv_chain_fp8(self.plan.data_ptr(), self.n_ops,
-                                                          1 if self.static_matrix else 0,
-                                                          fb._lib.current_stream_ptr(idx)))
+            if self.ctx is None:
+                fb._lib.check(self.lib.feather_gemv_chain_fp8(self.plan.data_ptr(), self.n_ops,
+                                                              1 if self.static_matrix else 0,
+                                                              fb._lib.current_stream_ptr(idx)))
+            else:
+                c = self.ctx
+                fb._lib.check(self.lib.feather_gemv_chain_fp8_tp(
+                    self.plan.data_ptr(), self.n_ops, 1 if self.static_matrix else 0, self.n_allreduce,
+                    self.max_allreduce_rows, c.inbox_ptrs, c.inbox_floats, c.flag_ptrs, c.rank,
+                    c.world_size, fb._lib.current_stream_ptr(idx)))
 
     __call__ = token
 
@@ -204,7 +228,9 @@ class TensorParallelChain:
 
     def __init__(self, mode: str = "E4M3", seed: int = 6, group=None, layers: int = LAYERS,
                  static_matrix: bool = True, fused_allreduce: bool = False,
-                 merge_projections: bool = False):
+                 merge_projections: bool = False, persistent: bool = False):
+        """``persistent``: the rank's whole token is ONE launch
+        (PersistentGemvChain) with the all-reduces of o and down inside it."""
         import torch.distributed as dist
         from .sharded import ColumnShardedGemv, PeerAllReduce
         self.dist, self.group = dist, group
@@ -213,8 +239,11 @@ class TensorParallelChain:
         device = torch.device("cuda", torch.cuda.current_device())
         gen = torch.Generator(device=device).manual_seed(seed)
         self.mode, self.static_matrix = mode, static_matrix
-        self.fused_allreduce = bool(fused_allreduce) and self.world > 1
-        self.ctx = PeerAllReduce(HIDDEN, device, group) if self.fused_allreduce else None
+        self.persistent = bool(persistent)
+        self.fused_allreduce = (bool(fused_allreduce) or self.persistent) and self.world > 1
+        self.ctx = None
+        if self.fused_allreduce:
+            self.ctx = PeerAllReduce(HIDDEN, device, group, n_ops=2 * layers if self.persistent else 1)
         self.ops = []  # (kind, packed weight shard, packed activation (slice), (rows, cols), out)
         acts = {}
         for n in (HIDDEN, INTER):
@@ -231,7 +260,9 @@ class TensorParallelChain:
                 act = acts[n][r * cols // 4:(r + 1) * cols // 4]
                 packed = fb.pack_fp8_tensor(shard, mode)
                 out = torch.empty(m, dtype=torch.float32, device=device)
-                if self.fused_allreduce:
+                if self.persistent:
+                    self.ops.append(("fused" if self.world > 1 else "cols", packed, act, (m, cols), out))
+                elif self.fused_allreduce:
                     self.ops.append(("fused", ColumnShardedGemv(packed, (m, cols), mode, self.ctx, out=out),
                                      act, (m, cols), out))
                 else:
@@ -252,9 +283,16 @@ class TensorParallelChain:
             for name, m, n in shapes:
                 add(name, m, n)
         add("lm_head", VOCAB, HIDDEN)
+        self.pchain = None
+        if self.persistent:
+            self.pchain = PersistentGemvChain(
+                [{"m": w, "v": a, "shape": shape, "out": out, "allreduce": kind == "fused"}
+                 for kind, w, a, shape, out in self.ops], mode, static_matrix, ctx=self.ctx)
         torch.cuda.synchronize()
 
     def token(self) -> None:
+        if self.pchain is not None:
+            return self.pchain.token()
         for kind, w, a, shape, out in self.ops:
             if kind == "fused":
                 w(a)
@@ -289,12 +327,12 @@ def check_tp(tp: "TensorParallelChain", single: "GemvChain") -> float:
 
 def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", group=None,
                fused_allreduce: bool = False, merge_projections: bool = False,
-               check: bool = False) -> dict:
+               check: bool = False, persistent: bool = False) -> dict:
     """Tokens per second of the tensor-parallel chain (call on every rank).
     ``check``: also compare one token with the single-GPU chain (check_tp)."""
     import torch.distributed as dist
     chain = TensorParallelChain(mode, group=group, fused_allreduce=fused_allreduce,
-                                merge_projections=merge_projections)
+                                merge_projections=merge_projections, persistent=persistent)
     err = None
     if check:
         single = GemvChain(mode, merge_projections=merge_projections)
@@ -343,6 +381,7 @@ def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", gro
     chain.close()
     return {"tokens_per_s": round(1e3 / ms, 1), "us_per_token": round(ms * 1e3, 1),
             "gemvs_per_token_per_rank": len(chain.ops),
+            "launches_per_token_per_rank": 1 if persistent else len(chain.ops),
             "all_reduces_per_token": sum(1 for o in chain.ops if o[0] in ("cols", "fused")),
             "fused_allreduce": chain.fused_allreduce, "merged_projections": merge_projections,
             "world": chain.world, "cuda_graph": graphed, "mode": mode,

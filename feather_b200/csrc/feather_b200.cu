@@ -1137,6 +1137,7 @@ int feather_gemv_chain_plan(const feather_chain_op* ops, int32_t n_ops, void* pl
     const int grid = dev->sm_count;   // the launch's grid: the row split is planned for it
     std::unique_ptr<ChainOp[]> host(new (std::nothrow) ChainOp[n_ops]);
     if (!host) return FEATHER_ERR_LAUNCH;
+    int n_ar = 0;   // all-reduced ops so far: an op's inbox region is its index among them
     for (int i = 0; i < n_ops; ++i) {
         const feather_chain_op& o = ops[i];
         if (o.M <= 0 || o.N <= 0 || (o.N & 15) || !o.m || !o.v || !o.out) return FEATHER_ERR_BAD_ARG;
@@ -1154,7 +1155,8 @@ int feather_gemv_chain_plan(const feather_chain_op* ops, int32_t n_ops, void* pl
         d.N = o.N;
         const int mode = o.mode == FEATHER_MODE_E5M2 ? kE5M2 : kE4M3;
         const int out_sel = o.out_mode < 0 ? 0 : 1 + (o.out_mode == FEATHER_MODE_E5M2 ? kE5M2 : kE4M3);
-        d.flags = mode | (out_sel << 1);
+        if (o.allreduce != 0 && o.allreduce != 1) return FEATHER_ERR_BAD_ARG;
+        d.flags = mode | (out_sel << 1) | (o.allreduce ? (++n_ar) << 4 : 0);
         d.wait_op = o.wait_op;
         d.rows_q = o.M / grid;
         d.rot = (int)(((long long)i * kChainRotate) % grid);
@@ -1172,7 +1174,8 @@ int feather_gemv_chain_plan(const feather_chain_op* ops, int32_t n_ops, void* pl
     return FEATHER_OK;
 }
 
-int feather_gemv_chain_fp8(const void* plan, int32_t n_ops, uint32_t flags, void* stream) {
+static int chain_launch(const void* plan, int32_t n_ops, uint32_t flags, const ChainArArgs& ar,
+                        void* stream) {
     if (flags & ~(uint32_t)FEATHER_GEMV_STATIC_MATRIX) return FEATHER_ERR_BAD_ARG;
     if (!plan || n_ops <= 0) return FEATHER_ERR_BAD_ARG;
     if (!aligned(plan, 16)) return FEATHER_ERR_MISALIGNED;
@@ -1197,8 +1200,41 @@ int feather_gemv_chain_fp8(const void* plan, int32_t n_ops, uint32_t flags, void
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ops, (int)n_ops, done, status);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ops, (int)n_ops, done, status, ar);
     return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
+}
+
+int feather_gemv_chain_fp8(const void* plan, int32_t n_ops, uint32_t flags, void* stream) {
+    return chain_launch(plan, n_ops, flags, ChainArArgs{}, stream);
+}
+
+int64_t feather_gemv_chain_inbox_floats(int32_t n_allreduce_ops, int32_t max_allreduce_rows, int world) {
+    if (n_allreduce_ops <= 0 || max_allreduce_rows <= 0 || world < 1) return 0;
+    const int64_t rows_cap = ((int64_t)max_allreduce_rows + 15) / 16 * 16;
+    return 2 /* call parities */ * (int64_t)n_allreduce_ops * world * rows_cap * 2 /* (sum, tag) */;
+}
+
+int feather_gemv_chain_fp8_tp(const void* plan, int32_t n_ops, uint32_t flags, int32_t n_allreduce_ops,
+                              int32_t max_allreduce_rows, float* const* peer_inbox, int64_t inbox_floats,
+                              uint32_t* const* peer_flags, int rank, int world, void* stream) {
+    if (n_allreduce_ops < 0 || max_allreduce_rows < 0 || !peer_inbox || !peer_flags || world < 1 ||
+        world > kMaxArRanks || rank < 0 || rank >= world)
+        return FEATHER_ERR_BAD_ARG;
+    if (n_allreduce_ops > 0 &&
+        inbox_floats < feather_gemv_chain_inbox_floats(n_allreduce_ops, max_allreduce_rows, world))
+        return FEATHER_ERR_TOO_LARGE;
+    ChainArArgs ar = {};
+    for (int p = 0; p < world; ++p) {
+        if (!peer_inbox[p] || !peer_flags[p]) return FEATHER_ERR_BAD_ARG;
+        if (!aligned(peer_inbox[p], 16) || !aligned(peer_flags[p], 4)) return FEATHER_ERR_MISALIGNED;
+        ar.inbox[p] = peer_inbox[p];
+        ar.flags[p] = peer_flags[p];
+    }
+    ar.rank = rank;
+    ar.world = world;
+    ar.n_ar = n_allreduce_ops;
+    ar.rows_cap = (max_allreduce_rows + 15) / 16 * 16;
+    return chain_launch(plan, n_ops, flags, ar, stream);
 }
 
 int feather_set_tuning(const char* spec) { return apply_tuning(spec); }

@@ -26,7 +26,19 @@
 //     The matrix stream is not held up by such a wait until the ring is full;
 //   * results are FP32 sums or, with out_mode >= 0, FP8 codes of the sums (the
 //     packer's rounding) stored one byte per row -- the packed vector the next
-//     op consumes.
+//     op consumes;
+//   * tensor-parallel launches (one per GPU): an op may be COLUMN-sharded, every
+//     rank holding a column block of all rows and the matching slice of the
+//     vector.  Its row sums are partial: the consumer's lanes store (sum, call
+//     number) pairs into every rank's inbox through peer-mapped pointers --
+//     eight bytes that arrive whole, so the data is its own arrival flag -- and
+//     go on with the next row.  A further warp, the reduce warp, polls this
+//     rank's inbox for the pairs of all ranks (bounded), adds them in rank order
+//     and writes the result: the same bits on every rank, no collective launch,
+//     and the NVLink round trip overlaps the streaming of the following ops.
+//     Every all-reduced op of a launch has its own inbox region, and two sets
+//     of regions alternate by the parity of the call number, which lives in
+//     device memory so that a captured graph can be replayed.
 //
 // Rows of op i are dealt to the CTAs in contiguous blocks, rotated by the op
 // index so that the extra row of an uneven split does not always hit the same CTAs.
@@ -46,13 +58,15 @@ struct ChainOp {
     int M, N;                 // N a multiple of 16, at most kChainTile
     int flags;                // bit 0: decode of m and v (kE5M2 / kE4M3); bits 1-2: 0 = FP32 sums,
                               // 1 + format = the sums encoded to that format; bit 3: a later op waits
-                              // for this one
+                              // for this one; bits 4..: 0, or 1 + the op's index among the launch's
+                              // all-reduced (column-sharded) ops
     int wait_op;              // -1, or the index of an EARLIER op that writes v
     int rows_q;               // M / grid: every CTA's share, the first M % grid CTAs hold one more
     int rot;                  // (op index * kChainRotate) % grid: where the row blocks start
     __host__ __device__ int mode() const { return flags & 1; }
     __host__ __device__ int out_mode() const { return ((flags >> 1) & 3) - 1; }
     __host__ __device__ bool signal() const { return (flags & 8) != 0; }
+    __host__ __device__ int ar_index() const { return (flags >> 4) - 1; }
 };
 static_assert(kE5M2 == 0 && kE4M3 == 1, "mode fits one bit");
 static_assert(sizeof(ChainOp) == 48, "the table layout is part of the ABI");
@@ -68,7 +82,44 @@ constexpr int kChainVecBytes = kChainTile * 2;                    // one FP16 ve
 constexpr int kChainBarriers = 2 * kChainStages + 4;              // full, empty, vec_full[2], vec_empty[2]
 constexpr int kChainSmemBytes = 2 * kChainVecBytes + kChainStages * kChainStageBytes +
                                 kChainBarriers * 8 + 8 * 4;       // + 8 per-op arrival counters
-constexpr int kChainThreads = (kChainCW + 2) * 32;
+constexpr int kChainThreads = (kChainCW + 3) * 32;   // consumers, producer, vector warp, reduce warp
+
+// Tensor-parallel launch: where every rank's inbox and flag block live, as mapped
+// into this process (world = 0: a single-GPU launch).  Inbox layout, in 8-byte
+// (sum, call number) pairs: [parity of the call][all-reduced op][source rank][row],
+// `rows_cap` rows per source rank.
+struct ChainArArgs {
+    float* inbox[kMaxArRanks];
+    unsigned int* flags[kMaxArRanks];   // only this rank's own is used (call counter, kArEpochWord)
+    int rank, world;
+    int n_ar;                           // all-reduced ops in the table
+    int rows_cap;                       // rows per (op, source rank) slot
+    __device__ size_t pair_index(unsigned int epoch, int ar, int src, int row) const {
+        return ((((size_t)(epoch & 1u) * n_ar + ar) * world + src) * rows_cap + row);
+    }
+};
+__device__ __forceinline__ void st_volatile_v2(float* p, uint32_t a, uint32_t b) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ uint2 ld_volatile_v2(const float* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+// The code (or float) of one finished row goes to its place in the op's output.
+__device__ __forceinline__ void chain_store_row(const ChainOp& d, int row, float sum) {
+    const int out_mode = d.out_mode();
+    if (out_mode < 0) {
+        reinterpret_cast<float*>(d.out)[row] = sum;
+    } else {
+        // one code per row, byte r of the packed output; the row that ends the matrix also
+        // writes the zero codes that pad the last word
+        unsigned char* codes = reinterpret_cast<unsigned char*>(d.out);
+        codes[row] = (unsigned char)(out_mode == kE5M2 ? encode_f32<kE5M2>(sum) : encode_f32<kE4M3>(sum));
+        if (row == d.M - 1)
+            for (int i = d.M; i & 3; ++i) codes[i] = 0;
+    }
+}
 constexpr int kChainRotate = 61;                // row blocks move by this many CTAs per op
 
 struct ChainGeom {
@@ -131,7 +182,7 @@ __device__ __forceinline__ void chain_row_stage(const uint4* st, const uint4* vs
 template <bool EARLY>
 __global__ void __launch_bounds__(kChainThreads, 1)
 gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __restrict__ done,
-                  unsigned int* __restrict__ status) {
+                  unsigned int* __restrict__ status, const __grid_constant__ ChainArArgs ar) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ __align__(128) unsigned char smem[];
     uint4* vec = reinterpret_cast<uint4*>(smem);                    // two buffers of kChainTile / 8 uint4
@@ -161,7 +212,53 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
     __syncthreads();
     if (!EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    if (warp == kChainCW) {
+    if (warp == kChainCW + 2) {
+        // ---------------------------------------------------- reduce warp --
+        if (ar.world > 0) {
+            if (EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");
+            // this call's number: one more than the calls completed on this rank
+            unsigned int epoch = __ldcg(ar.flags[ar.rank] + kArEpochWord) + 1u;
+            if (epoch == 0u) epoch = 2u;   // 0 is the tag of an untouched inbox; keep the parity
+            bool alive = true;
+            ChainOp next = chain_load_op(ops, 0, n_ops);
+            for (int op = 0; op < n_ops && alive; ++op) {
+                const ChainOp d = next;
+                next = chain_load_op(ops, op + 1, n_ops);
+                const int ai = d.ar_index();
+                if (ai < 0) continue;
+                const ChainGeom g = chain_geom(d);
+                for (int r0 = g.row_begin; r0 < g.row_end && alive; r0 += 32) {
+                    const int row = r0 + lane;
+                    if (row < g.row_end) {
+                        float total = 0.f;
+                        for (int q = 0; q < ar.world; ++q) {   // rank order: the same bits everywhere
+                            const float* src = ar.inbox[ar.rank] + 2 * ar.pair_index(epoch, ai, q, row);
+                            uint2 x = ld_volatile_v2(src);
+                            if (x.y != epoch) {
+                                const unsigned long long t0 = global_timer_ns();
+                                do {
+                                    x = ld_volatile_v2(src);
+                                    if (global_timer_ns() - t0 > kWaitLimitNs) {
+                                        atomicOr(status, 2u);   // rank q's sums did not arrive in time
+                                        alive = false;
+                                        break;
+                                    }
+                                } while (x.y != epoch);
+                            }
+                            total = q == 0 ? __uint_as_float(x.x) : total + __uint_as_float(x.x);
+                        }
+                        if (alive && bounds_ok(row < d.M)) chain_store_row(d, row, total);
+                    }
+                    alive = __all_sync(0xFFFFFFFFu, alive);
+                }
+                if (alive && d.signal() && g.row_end > g.row_begin) {
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) atomicAdd(done + 1 + op, 1u);
+                }
+            }
+        }
+    } else if (warp == kChainCW) {
         // ------------------------------------------------------- producer --
         int s = 0;
         uint32_t round = 0;
@@ -270,6 +367,11 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
     } else {
         // ------------------------------------------------------ consumers --
         if (EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");  // before any output is written
+        unsigned int epoch = 0;
+        if (ar.world > 0) {
+            epoch = __ldcg(ar.flags[ar.rank] + kArEpochWord) + 1u;
+            if (epoch == 0u) epoch = 2u;
+        }
         int s = 0;
         uint32_t phase = 0;
         int vec_idx = -1, sig_idx = 0;
@@ -321,25 +423,21 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
                 if (!alive) break;
                 if (has_row) {
                     float sums[1] = {(acc[0] + acc[1]) + (acc[2] + acc[3])};
-                    warp_reduce_rows<1>(sums, lane);
-                    if (lane == 0 && bounds_ok(row >= 0 && row < d.M)) {
-                        const int out_mode = d.out_mode();
-                        if (out_mode < 0) {
-                            reinterpret_cast<float*>(d.out)[row] = sums[0];
-                        } else {
-                            // one code per row, byte r of the packed output; the row that ends the
-                            // matrix also writes the zero codes that pad the last word
-                            unsigned char* codes = reinterpret_cast<unsigned char*>(d.out);
-                            codes[row] = (unsigned char)(out_mode == kE5M2 ? encode_f32<kE5M2>(sums[0])
-                                                                             : encode_f32<kE4M3>(sums[0]));
-                            if (row == d.M - 1)
-                                for (int i = d.M; i & 3; ++i) codes[i] = 0;
-                        }
+                    warp_reduce_rows<1>(sums, lane);   // every lane holds the row's sum
+                    const int ai = d.ar_index();
+                    if (ai >= 0) {
+                        // partial sum of a column-sharded op: lane q hands it to rank q (this rank
+                        // included), tagged with the call number; the reduce warps do the rest
+                        if (lane < ar.world)
+                            st_volatile_v2(ar.inbox[lane] + 2 * ar.pair_index(epoch, ai, ar.rank, row),
+                                           __float_as_uint(sums[0]), epoch);
+                    } else if (lane == 0 && bounds_ok(row >= 0 && row < d.M)) {
+                        chain_store_row(d, row, sums[0]);
                     }
                 }
             }
             if (!alive) break;
-            if (d.signal()) {
+            if (d.signal() && d.ar_index() < 0) {   // all-reduced ops are signalled by the reduce warp
                 // This warp's rows of the op are written.  The warps count themselves in with a
                 // release at CTA scope; the last one, having seen them all, issues the one
                 // GPU-scope fence (which thereby covers every warp's rows) and counts the CTA
@@ -364,6 +462,12 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
         __threadfence();
         if (atomicAdd(done, 1u) == gridDim.x - 1) {
             for (int i = 0; i <= n_ops; ++i) done[i] = 0u;
+            if (ar.world > 0) {   // the call is complete on this rank: count it
+                unsigned int* my_flags = ar.flags[ar.rank];
+                unsigned int epoch = my_flags[kArEpochWord] + 1u;
+                if (epoch == 0u) epoch = 2u;
+                my_flags[kArEpochWord] = epoch;
+            }
         }
     }
 }

@@ -351,7 +351,10 @@ class PeerAllReduce:
     every rank of ``group``; ``close()`` likewise.
     """
 
-    def __init__(self, max_rows: int, device: Optional[torch.device] = None, group=None):
+    def __init__(self, max_rows: int, device: Optional[torch.device] = None, group=None, n_ops: int = 1):
+        """``n_ops`` > 1 sizes the inbox for a one-launch chain with that many
+        all-reduced ops (``chain.PersistentGemvChain``); such a context serves
+        that chain only."""
         from . import _lib
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed is not initialised")
@@ -364,8 +367,9 @@ class PeerAllReduce:
             self._lib = _lib.load()
             if self.world_size > 16:
                 raise ValueError("the fused all-reduce supports at most 16 ranks")
-            # two halves x world slots x (sum, tag) pairs for max_rows rounded up to 16
-            self.inbox_floats = 2 * self.world_size * 2 * ((self.max_rows + 15) // 16 * 16)
+            # two halves x ops x world slots x (sum, tag) pairs for max_rows rounded up to 16
+            self.n_ops = int(n_ops)
+            self.inbox_floats = 2 * self.n_ops * self.world_size * 2 * ((self.max_rows + 15) // 16 * 16)
             # [inbox | flag block]
             self._shared = torch.zeros(self.inbox_floats + 32, dtype=torch.float32, device=dev)
         except Exception as e:  # noqa: BLE001 - every rank still takes part in the exchange below
@@ -425,10 +429,11 @@ class ColumnShardedGemv:
         self.m_local, self.ctx, self.mode = m_local, ctx, mode
         self._mode_id = _lib.mode_id(mode)
         self._n_words = self.n_local // 4
+        if ctx is None and not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        self.group = ctx.group if ctx is not None else group
+        self._check_agreement()
         if ctx is None:
-            if not dist.is_initialized():
-                raise RuntimeError("torch.distributed is not initialised")
-            self.group = group
             if local_gemv is None:
                 from .routines.gemv import gemv_fp8_acc_fp32_gpu
                 local_gemv = gemv_fp8_acc_fp32_gpu
@@ -448,6 +453,18 @@ class ColumnShardedGemv:
         self._m_ptr, self._out_ptr = words.data_ptr(), self.out.data_ptr()
         self._fn, self._check = ctx._lib.feather_gemv_fp8_allreduce, _lib.check
         self._stream_ptr = _lib.current_stream_ptr
+
+    def _check_agreement(self) -> None:
+        """Every rank must hold a block of the same shape and format: the sums
+        of blocks that differ would be added row by row all the same."""
+        mine = torch.tensor([self.M, self.n_local, self._mode_id], dtype=torch.int64,
+                            device=self.m_local.device)
+        lo, hi = mine.clone(), mine.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=self.group)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=self.group)
+        if not (torch.equal(lo, mine) and torch.equal(hi, mine)):
+            raise ValueError(f"ranks disagree on the local block (M, N/W, mode): min {lo.tolist()} "
+                             f"max {hi.tolist()} mine {mine.tolist()}")
 
     def __call__(self, v_local: torch.Tensor) -> torch.Tensor:
         ctx = self.ctx

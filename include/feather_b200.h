@@ -391,13 +391,43 @@ typedef struct feather_chain_op {
     int32_t mode;
     int32_t out_mode;
     int32_t wait_op;
-    int32_t reserved;   /* set to 0 */
+    int32_t allreduce;  /* 0, or 1 for a column-sharded op of a tensor-parallel launch (below) */
 } feather_chain_op;
 
 int64_t feather_gemv_chain_plan_bytes(int32_t n_ops);
 int feather_gemv_chain_plan(const feather_chain_op* ops, int32_t n_ops, void* plan, int64_t plan_bytes,
                             void* stream);
 int feather_gemv_chain_fp8(const void* plan, int32_t n_ops, uint32_t flags, void* stream);
+
+/*
+ * The chain as one rank of a tensor-parallel group, one launch per GPU and
+ * token.  No counterpart in the reference (single-GPU).  Ops with allreduce = 0
+ * are local (e.g. this rank's ROWS of a projection).  An op with allreduce = 1
+ * is COLUMN-sharded as in feather_gemv_fp8_allreduce: m holds this rank's
+ * column block of all M rows (row stride N / 4 words, N the LOCAL column
+ * count), v the matching slice of the vector; the row sums are partial and the
+ * op's output is their sum over the ranks, added in rank order -- the same
+ * bits on every rank.  The exchange runs inside the kernel through peer-mapped
+ * inboxes ((sum, call number) pairs; no collective launch, no host
+ * synchronisation) and overlaps the streaming of the following ops.
+ *   n_allreduce_ops, max_allreduce_rows   how many ops of the plan have
+ *               allreduce = 1 and their largest M
+ *   peer_inbox  HOST array of `world` device pointers: rank p's inbox, at least
+ *               feather_gemv_chain_inbox_floats(...) floats, 16-byte aligned,
+ *               zero before the first call, as mapped into THIS process
+ *   peer_flags  HOST array of `world` device pointers to the ranks' flag
+ *               blocks (32 words, zero before the first call); this rank's own
+ *               block holds the call counter, so a captured graph of launches
+ *               may be replayed
+ * Every rank launches the same table shape (same ops in the same order).  Waits
+ * for the peers are bounded (feather_set_wait_limit_ms, feather_device_status).
+ * An inbox and flag block serve ONE plan (or plans launched in the same order
+ * on every rank).
+ */
+int64_t feather_gemv_chain_inbox_floats(int32_t n_allreduce_ops, int32_t max_allreduce_rows, int world);
+int feather_gemv_chain_fp8_tp(const void* plan, int32_t n_ops, uint32_t flags, int32_t n_allreduce_ops,
+                              int32_t max_allreduce_rows, float* const* peer_inbox, int64_t inbox_floats,
+                              uint32_t* const* peer_flags, int rank, int world, void* stream);
 
 /*
  * Kernel-variant knobs for A/B runs in benchmarks; results do not depend on

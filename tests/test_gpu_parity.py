@@ -704,6 +704,77 @@ def test_allreduce_gemv_with_hand_fed_peer(fb, mode):
     assert lib.feather_gemv_fp8_allreduce(p, p, p, big, 16, 0, inb, 8 * big * world, flg, 0, world, None) == -8
 
 
+def test_gemv_chain_kernel_allreduce_ops_with_hand_fed_peer(fb):
+    """feather_gemv_chain_fp8_tp as rank 0 of 2, the "peer" being a second inbox
+    on the same GPU that the test fills by hand: a column-sharded op's output is
+    own partial + peer partial (rank order), the own partials land tagged in
+    the peer's inbox, local ops of the same launch are untouched, a dependent op
+    waits for the all-reduced result, and the call counter advances so that the
+    two inbox halves alternate over repeated launches."""
+    from feather_b200._lib import ChainOp
+    lib = fb._lib.load()
+    world, M, n_local = 2, 2048, 704
+    gen = torch.Generator(device="cuda").manual_seed(61)
+    def packed(*shape):
+        return fb.pack_fp8_tensor(torch.randn(*shape, device="cuda", generator=gen) * 0.05, "E4M3")
+    w_ar = [packed(M, n_local), packed(300, 256)]          # two all-reduced ops
+    v_ar = [packed(n_local), packed(256)]
+    w_loc, v_loc = packed(512, 2048), packed(2048)         # a local op in between
+    w_dep = packed(64, M)                                   # reads the first all-reduced result
+    outs = [torch.zeros((M + 3) // 4, dtype=torch.int32, device="cuda"),
+            torch.zeros(512, dtype=torch.float32, device="cuda"),
+            torch.zeros(300, dtype=torch.float32, device="cuda"),
+            torch.zeros(64, dtype=torch.float32, device="cuda")]
+    table = (ChainOp * 4)()
+    def fill(t, m, v, out, Mi, Ni, out_mode=-1, wait=-1, ar=0):
+        t.m, t.v, t.out, t.M, t.N, t.mode, t.out_mode, t.wait_op, t.allreduce = (
+            m.data_ptr(), v.data_ptr(), out.data_ptr(), Mi, Ni, 1, out_mode, wait, ar)
+    fill(table[0], w_ar[0], v_ar[0], outs[0], M, n_local, out_mode=1, ar=1)   # packed E4M3 output
+    fill(table[1], w_loc, v_loc, outs[1], 512, 2048)
+    fill(table[2], w_ar[1], v_ar[1], outs[2], 300, 256, ar=1)
+    fill(table[3], w_dep, outs[0], outs[3], 64, M, wait=0)
+    nbytes = int(lib.feather_gemv_chain_plan_bytes(4))
+    plan = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    assert lib.feather_gemv_chain_plan(ctypes.cast(table, ctypes.c_void_p), 4, plan.data_ptr(), nbytes, None) == 0
+    n_ar, rows_cap = 2, 2048
+    inbox_floats = int(lib.feather_gemv_chain_inbox_floats(n_ar, M, world))
+    assert inbox_floats == 2 * n_ar * world * rows_cap * 2
+    inbox = [torch.zeros(inbox_floats, dtype=torch.float32, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(32, dtype=torch.int32, device="cuda") for _ in range(world)]
+    arr = ctypes.c_void_p * world
+    inb, flg = arr(*[t.data_ptr() for t in inbox]), arr(*[t.data_ptr() for t in flags])
+    own = [fb.gemv_fp8_acc_fp32_gpu(w_ar[0], v_ar[0], (M, n_local), "E4M3"),
+           fb.gemv_fp8_acc_fp32_gpu(w_ar[1], v_ar[1], (300, 256), "E4M3")]
+    local = fb.gemv_fp8_acc_fp32_gpu(w_loc, v_loc, (512, 2048), "E4M3")
+    def region(call, ai, src, rows):   # floats of (parity, op, source rank), `rows` pairs
+        base = 2 * ((((call & 1) * n_ar + ai) * world + src) * rows_cap)
+        return slice(base, base + 2 * rows)
+    for call in range(1, 5):
+        peer = [torch.randn(M, device="cuda", generator=gen), torch.randn(300, device="cuda", generator=gen)]
+        for ai, rows in ((0, M), (1, 300)):   # the peer's partial sums, as rank 1 would have stored them
+            inbox[0][region(call, ai, 1, rows)] = _tagged(peer[ai], call)
+        for o in outs:
+            o.zero_()
+        st = lib.feather_gemv_chain_fp8_tp(plan.data_ptr(), 4, 1 if call % 2 else 0, n_ar, M, inb, inbox_floats,
+                                           flg, 0, world, None)
+        assert st == 0 and lib.feather_device_status(None) == 0
+        total0 = own[0] + peer[0]
+        want0 = fb.pack_fp8_tensor(total0, "E4M3")
+        assert torch.equal(outs[0], want0.view(torch.int32))
+        assert torch.equal(outs[1], local)
+        assert torch.equal(outs[2], own[1] + peer[1])
+        assert torch.equal(outs[3], fb.gemv_fp8_acc_fp32_gpu(w_dep, want0, (64, M), "E4M3"))
+        for ai, rows in ((0, M), (1, 300)):   # own partials, tagged, in the peer's inbox
+            assert torch.equal(inbox[1][region(call, ai, 0, rows)].view(torch.int32),
+                               _tagged(own[ai], call).view(torch.int32))
+        assert int(flags[0][17]) == call
+    # an inbox that is too small is refused before anything is launched
+    assert lib.feather_gemv_chain_fp8_tp(plan.data_ptr(), 4, 0, n_ar, M, inb, inbox_floats - 1, flg, 0, world,
+                                         None) == -8
+    assert lib.feather_gemv_chain_fp8_tp(plan.data_ptr(), 4, 0, n_ar, M, inb, inbox_floats, flg, 2, world,
+                                         None) == -1
+
+
 def test_allreduce_gemv_world_1_and_missing_peer(fb):
     """World size 1 is a plain GEMV.  With a peer that never delivers the wait
     gives up after the limit, the status word reports it and the context stays

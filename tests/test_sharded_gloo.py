@@ -70,6 +70,15 @@ def _worker(rank: int, world: int, port: int, case: str, q):
             ref = O.gemv(mwc.numpy().view(np.uint32), vwc.numpy().view(np.uint32), (Mc, Nc), mode, acc="f64")
             q.put((rank, bool(np.array_equal(y, sum(parts[1:], parts[0]))) and same_block,
                    O.normalised_error(y, ref) < 1e-5))
+        elif case == "columns_disagree":
+            # the ranks pass different row counts for the column split
+            from feather_b200.sharded import ColumnShardedGemv
+            Mc = 24 if rank == 0 else 16
+            try:
+                ColumnShardedGemv(mw[: Mc * 16], (Mc, 64), mode, local_gemv=_oracle_local_gemv)
+                q.put((rank, "no error"))
+            except ValueError as e:
+                q.put((rank, "ValueError" if "disagree" in str(e) else str(e)))
         elif case == "bad_columns":
             from feather_b200.sharded import local_column_words
             try:
@@ -108,6 +117,38 @@ def _run(case: str, world: int = 2):
         p.join(timeout=60)
         assert p.exitcode == 0
     return sorted(out)
+
+
+def _lonely_worker(port: int, q):
+    """Rank 0 of a world of 2 whose peer never starts."""
+    import datetime
+    import time
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    t0 = time.time()
+    try:
+        dist.init_process_group("gloo", rank=0, world_size=2, timeout=datetime.timedelta(seconds=5))
+        q.put(("no error", time.time() - t0))
+        dist.destroy_process_group()
+    except Exception as e:  # noqa: BLE001 - the kind of exception is torch's business
+        q.put((type(e).__name__, time.time() - t0))
+
+
+def test_rank_missing_at_rendezvous_raises_within_the_timeout():
+    """A rank that never joins: the others get an exception after the
+    rendezvous timeout instead of waiting forever (host-side failure; nothing
+    runs on a GPU)."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_lonely_worker, args=(_free_port(), q))
+    p.start()
+    kind, seconds = q.get(timeout=120)
+    p.join(timeout=60)
+    assert kind != "no error" and seconds < 60
+
+
+def test_column_sharded_ranks_that_disagree_raise():
+    assert _run("columns_disagree") == [(0, "ValueError"), (1, "ValueError")]
 
 
 def test_row_sharded_gemv_matches_single_rank():

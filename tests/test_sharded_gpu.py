@@ -87,6 +87,7 @@ def _worker(rank: int, world: int, port: int, q):
         ok_ar = True
         if world > 1:
             ok_ar = _check_fused_allreduce(rank, world, single)
+            ok_ar &= _check_fused_allreduce(rank, world, single, persistent=True)
         q.put((rank, ok_bits and ok_tp and ok_ar and modes == ([False, True] if world > 1 else [False]),
                ok_err))
     except Exception as e:
@@ -95,17 +96,23 @@ def _worker(rank: int, world: int, port: int, q):
         dist.destroy_process_group()
 
 
-def _check_fused_allreduce(rank: int, world: int, single) -> bool:
+def _check_fused_allreduce(rank: int, world: int, single, persistent: bool = False) -> bool:
     """Column-sharded GEMVs with the all-reduce inside the kernel: equal to the
     partial sums added in rank order, the same bits on every rank, close to the
     single-GPU chain, over several calls (both inbox halves) and under CUDA
-    graph replay (the call counter lives on the device)."""
+    graph replay (the call counter lives on the device).  ``persistent``: the
+    rank's whole token as ONE launch, the all-reduces inside it."""
     import feather_b200 as fb
     from feather_b200 import chain
     from oracle import feather_oracle as O
-    tp = chain.TensorParallelChain(layers=1, fused_allreduce=True)
+    tp = chain.TensorParallelChain(layers=1, fused_allreduce=True, persistent=persistent)
     ok = tp.fused_allreduce
     fused = [(op, a, shape, out) for kind, op, a, shape, out in tp.ops if kind == "fused"]
+    if persistent:   # the entries hold the packed shard itself, not an operator object
+        class _Shard:
+            def __init__(self, m):
+                self.m_local = m
+        fused = [(_Shard(op), a, shape, out) for op, a, shape, out in fused]
     refs = [single.ops[i][3] for i, (name, _, _) in enumerate(chain.LAYER_SHAPES) if name in ("o", "down")]
     ok &= len(fused) == len(refs) == 2
     expected = []
@@ -140,6 +147,13 @@ def _check_fused_allreduce(rank: int, world: int, single) -> bool:
     for _ in range(3):
         graph.replay()
         ok &= verify()
+    if persistent:   # the row-split ops of the same launch, against the single-GPU chain
+        tp.token()
+        torch.cuda.synchronize()
+        for (kind, _, _, shape, out_tp), (_, _, _, out_1) in zip(tp.ops, single.ops):
+            if kind == "rows":
+                ok &= O.normalised_error(out_tp.cpu().numpy(),
+                                         out_1[rank * shape[0]:(rank + 1) * shape[0]].cpu().numpy()) < 1e-5
     fb.device_status()
     tp.close()
     return bool(ok)
