@@ -273,7 +273,7 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
                 const int row0 = g.row_begin + task * kChainCW;
                 const int rows = min(kChainCW, g.row_end - row0);
                 for (int seg = 0; seg < g.n_seg; ++seg) {
-                    if (round > 0 && !mbar_wait(empty_bar(s), (round & 1u) ^ 1u, status)) {
+                    if (round > 0 && !mbar_wait_backoff(empty_bar(s), (round & 1u) ^ 1u, status, 20)) {
                         alive = false;
                         break;
                     }
@@ -309,7 +309,7 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
             staged_v = d.v; staged_n = d.N; staged_mode = d.mode();
             ++vec_idx;
             const int b = vec_idx & 1;
-            if (vec_idx >= 2 && !mbar_wait(vec_empty(b), (uint32_t)((vec_idx >> 1) - 1) & 1u, status)) break;
+            if (vec_idx >= 2 && !mbar_wait_backoff(vec_empty(b), (uint32_t)((vec_idx >> 1) - 1) & 1u, status, 100)) break;
             if (d.wait_op >= 0) {
                 // the vector is op wait_op's output: all CTAs that hold rows of it must be done
                 const ChainOp w = chain_load_op(ops, d.wait_op, n_ops);
@@ -392,7 +392,7 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
                     if (lane == 0) mbar_arrive(vec_empty(vec_idx & 1));
                 }
                 ++vec_idx;
-                if (!mbar_wait(vec_full(vec_idx & 1), (uint32_t)(vec_idx >> 1) & 1u, status)) break;
+                if (!mbar_wait_backoff(vec_full(vec_idx & 1), (uint32_t)(vec_idx >> 1) & 1u, status)) break;
             }
             const uint4* vbase = vec + (vec_idx & 1) * (kChainTile / 8) + lane;
             for (int task = 0; task < g.n_tasks && alive; ++task) {
@@ -405,7 +405,7 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
                 const bool has_row = row < g.row_end;   // warp-uniform
                 float acc[4] = {0.f, 0.f, 0.f, 0.f};
                 for (int seg = 0; seg < g.n_seg; ++seg) {
-                    if (!mbar_wait(full_bar(s), phase, status)) {
+                    if (!mbar_wait_backoff(full_bar(s), phase, status)) {
                         alive = false;
                         break;
                     }

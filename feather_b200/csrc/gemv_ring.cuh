@@ -73,6 +73,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
         }
     }
 }
+// The same bounded wait for kernels whose waiting warps would otherwise starve the
+// warps they wait for: a warp that polls an mbarrier in a tight loop takes issue slots,
+// and with 16 consumer warps polling, a producer warp that has real work to do per step
+// (the table walk of the chain kernel) gets a nineteenth of its SM sub-partition's issue
+// bandwidth -- measured as a floor of half a microsecond per GEMV however small.  Here
+// the waiter sleeps a few tens of nanoseconds between looks.
+__device__ __forceinline__ bool mbar_wait_backoff(uint32_t bar, uint32_t parity, unsigned int* status,
+                                                  unsigned int sleep_ns = 40) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 128; ++i) {
+            __nanosleep(sleep_ns);
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        if (global_timer_ns() - t0 > kWaitLimitNs) {
+            atomicOr(status, 1u);
+            return false;
+        }
+    }
+}
 // 1-D bulk copy global -> this CTA's shared memory, completion on `bar`.
 __device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
