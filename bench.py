@@ -402,6 +402,12 @@ def run_ours(args) -> None:
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
+    if world > 1 and op.fused:
+        # The host barrier leaves the ranks tens of microseconds apart, which K = 20 steps of
+        # 90 us would carry as skew.  One more warm-up call that waits for every rank's slices
+        # ends on all GPUs within a few microseconds; the start events are enqueued right
+        # behind it, so the timed regions of the ranks begin together.
+        op(vw)
     with clocks:
         start.record()
         for _ in range(K):

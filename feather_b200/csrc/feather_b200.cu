@@ -1158,7 +1158,7 @@ int feather_gemv_chain_plan(const feather_chain_op* ops, int32_t n_ops, void* pl
         if (o.allreduce != 0 && o.allreduce != 1) return FEATHER_ERR_BAD_ARG;
         d.flags = mode | (out_sel << 1) | (o.allreduce ? (++n_ar) << 4 : 0);
         d.wait_op = o.wait_op;
-        d.rows_q = o.M / grid;
+        d.rows_q = ((o.M + kChainCW - 1) / kChainCW) / grid;
         d.rot = (int)(((long long)i * kChainRotate) % grid);
     }
     for (int i = 0; i < n_ops; ++i)
