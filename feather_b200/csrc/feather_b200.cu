@@ -734,6 +734,17 @@ extern "C" {
 
 int feather_version(void) { return 300; /* 0.3.0: + GEMV chain in one launch, split-phase sharded GEMV, ring dot */ }
 
+#ifdef FEATHER_RING_STAMPS
+// Diagnostic build only: copy the timer stamps of the last 16 gemv_ring_kernel launches
+// (16 x 160 x 8 uint64, see gemv_ring.cuh) to host memory; synchronises the device.
+extern "C" int feather_debug_ring_stamps(void* host_dst) {
+    if (!host_dst) return FEATHER_ERR_BAD_ARG;
+    if (cudaDeviceSynchronize() != cudaSuccess) return FEATHER_ERR_LAUNCH;
+    return cudaMemcpyFromSymbol(host_dst, g_ring_stamps, sizeof(g_ring_stamps)) == cudaSuccess
+               ? FEATHER_OK : FEATHER_ERR_LAUNCH;
+}
+#endif
+
 int feather_debug_bounds(void) {
 #ifdef FEATHER_DEBUG_BOUNDS
     return 1;

@@ -306,10 +306,23 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
                     const int chunks = min(kChainSegChunks, g.n16 - seg * kChainSegChunks);
                     const uint32_t bytes = (uint32_t)chunks * 16u;
                     if (lane == 0) mbar_arrive_expect_tx(full_bar(s), bytes * (uint32_t)rows);
-                    if (lane < rows && bounds_ok(row0 + lane < d.M && (size_t)seg * kChainSegBytes + bytes <= row_bytes))
+                    if (g.n_seg == 1) {
+                        // The rows of a task lie back to back in memory when a row is one segment,
+                        // and the stage keeps them back to back too (row stride = row length).
+                        // The copy engine takes ~50-70 ns per request whatever its size (16 requests
+                        // of 2 KiB cap an SM at ~29 KB/us, below its share of HBM), so the task goes
+                        // as at most four requests of four rows each instead of one per row.
+                        const int r_first = lane * 4, r_count = min(4, rows - r_first);
+                        if (lane < 4 && r_count > 0 && bounds_ok(row0 + r_first + r_count <= d.M))
+                            bulk_load(ring_s + s * kChainStageBytes + (uint32_t)r_first * bytes,
+                                      d.m + (size_t)(row0 + r_first) * row_bytes, (uint32_t)r_count * bytes,
+                                      full_bar(s));
+                    } else if (lane < rows &&
+                               bounds_ok(row0 + lane < d.M && (size_t)seg * kChainSegBytes + bytes <= row_bytes)) {
                         bulk_load(ring_s + s * kChainStageBytes + lane * kChainSegBytes,
                                   d.m + (size_t)(row0 + lane) * row_bytes + (size_t)seg * kChainSegBytes,
                                   bytes, full_bar(s));
+                    }
                     if (++s == kChainStages) { s = 0; ++round; }
                 }
             }
@@ -436,7 +449,9 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
                         break;
                     }
                     if (has_row) {
-                        const uint4* st = ring_lane + (s * kChainCW + slot) * kChainSegChunks;
+                        // a one-segment row sits at slot * (row length) in the stage, see the producer
+                        const uint4* st = ring_lane + s * (kChainCW * kChainSegChunks) +
+                                          slot * (g.n_seg == 1 ? g.n16 : kChainSegChunks);
                         const uint4* vs = vbase + (seg * kChainCL * 2) * 32;
                         const int chunks = min(kChainSegChunks, g.n16 - seg * kChainSegChunks);
                         if (d.mode() == kE5M2) chain_row_stage<kE5M2>(st, vs, chunks, lane, acc);

@@ -112,6 +112,20 @@ __device__ __forceinline__ bool mbar_sync(uint32_t bar, uint32_t& parity, unsign
     return ok;
 }
 
+#ifdef FEATHER_RING_STAMPS
+// Diagnostic build only (-DFEATHER_RING_STAMPS): the GPU's nanosecond timer at six
+// points of every CTA of gemv_ring_kernel, for the 16 most recent launches (the slot is
+// taken from the output address, so give consecutive launches outputs 64 KiB apart):
+// [0] entry, [1] past the stream-order wait, [2] first stage issued, [3] first stage
+// landed, [4] vector staged, [5] last row written.  Read with feather_debug_ring_stamps.
+__device__ unsigned long long g_ring_stamps[16][160][8];
+#define RING_STAMP(out_ptr, i)                                                                         \
+    g_ring_stamps[(reinterpret_cast<uintptr_t>(out_ptr) >> 16) & 15][blockIdx.x < 160 ? blockIdx.x : 159][i] = \
+        global_timer_ns()
+#else
+#define RING_STAMP(out_ptr, i) ((void)0)
+#endif
+
 // Row-sharded multi-GPU launch (FUSED = true): where every rank's output
 // buffer and flag block live.  Pointers are valid on THIS device (peer-mapped).
 constexpr int kMaxShardRanks = 16;
@@ -229,6 +243,7 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
     // wait below touches no global memory, so it runs under the tail of the
     // kernel before this one.  Without the launch attribute both are no-ops.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (threadIdx.x == 0) RING_STAMP(out, 0);
     extern __shared__ __align__(128) unsigned char smem[];
     uint4* vec = reinterpret_cast<uint4*>(smem);
     unsigned char* ring = smem + G::kVecBytes;
@@ -288,8 +303,16 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
         for (int r = lane; r < pre_rows; r += 32)
             bulk_prefetch_l2(m + (size_t)(row_begin + r) * row_bytes, (uint32_t)chunks_p0 * 16u);
     }
+    if (warp == CW + 1 && lane == 0 && pre_bytes > 0) {
+        // The packed vector too: the matrix of the call before has flushed it out of L2 (a
+        // 256 MiB stream through 126 MB), and every CTA is about to read all of it.  The
+        // CTAs share the lines out between them.  Safe ahead of the wait for the same reason.
+        for (int line = blockIdx.x; (size_t)line * 128 < (size_t)n16 * 16; line += gridDim.x)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(v) + (size_t)line * 128));
+    }
     __syncthreads();
     if (!EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) RING_STAMP(out, 1);
     if (n_tasks == 0 && !FUSED) return;  // a fused rank needs every CTA at the final ticket
 
     if (FUSED && warp == CW + 2) {
@@ -408,6 +431,7 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
 
     if (warp == CW) {
         // ------------------------------------------------------- producer --
+        if (lane == 0) RING_STAMP(out, 6);
         int s = 0;               // ring slot of the next stage
         uint32_t round = 0;      // how many times the ring has wrapped
         bool alive = true;
@@ -437,6 +461,7 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
                         if (bounds_ok(row0 + r < M && col + bytes <= row_bytes && r < G::kTaskRows))
                             bulk_load(ring_s + s * G::kStageBytes + r * G::kSegBytes,
                                       m + (size_t)(row0 + r) * row_bytes + col, bytes, full_bar(s));
+                    if (piece == 0 && task == 0 && seg == 0 && lane == 0) RING_STAMP(out, 2);
                     if (++s == STAGES) { s = 0; ++round; }
                 }
             }
@@ -459,9 +484,10 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
     if (!long_rows) {
         // the whole vector, once, by all consumer warps
         const int fill = ((n16 + G::kSegChunks - 1) / G::kSegChunks) * G::kSegChunks;
-        stage_vector<MODE, 4>(vec, v, n16, fill, threadIdx.x, CW * 32);
+        stage_vector<MODE, 8>(vec, v, n16, fill, threadIdx.x, CW * 32);  // 16384 codes: every load of a thread in flight at once
         uint32_t parity = 0;
         alive = mbar_sync(start_bar, parity, status);
+        if (threadIdx.x == 0) RING_STAMP(out, 4);
     }
     // Partial row sums between pieces: in shared memory when the CTA's row block
     // fits there (no global round trip in the loop), else in the output buffer.
@@ -491,6 +517,7 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
                     alive = false;
                     break;
                 }
+                if (threadIdx.x == 0 && piece == 0 && task == 0 && seg == 0) RING_STAMP(out, 3);
                 const uint4* st = ring_lane + s * (G::kStageBytes / 16);
                 const uint4* vs = vbase + (seg * CL * 2) * 32 + lane;
                 if (all_rows && seg < n_full_seg) {
@@ -554,6 +581,7 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
             if (lane == 0) mbar_arrive(vec_empty(piece & 1));  // this warp is done with the piece
         }
     }
+    if (threadIdx.x == 0) RING_STAMP(out, 5);
     if (FUSED && !sh.staged) {
         // rows went to the peers one by one: tell the exchange warp this warp is done
         __syncwarp();
