@@ -303,13 +303,6 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
         for (int r = lane; r < pre_rows; r += 32)
             bulk_prefetch_l2(m + (size_t)(row_begin + r) * row_bytes, (uint32_t)chunks_p0 * 16u);
     }
-    if (warp == CW + 1 && lane == 0 && pre_bytes > 0) {
-        // The packed vector too: the matrix of the call before has flushed it out of L2 (a
-        // 256 MiB stream through 126 MB), and every CTA is about to read all of it.  The
-        // CTAs share the lines out between them.  Safe ahead of the wait for the same reason.
-        for (int line = blockIdx.x; (size_t)line * 128 < (size_t)n16 * 16; line += gridDim.x)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(v) + (size_t)line * 128));
-    }
     __syncthreads();
     if (!EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) RING_STAMP(out, 1);
@@ -484,7 +477,7 @@ gemv_ring_kernel(const unsigned char* __restrict__ m, const uint32_t* __restrict
     if (!long_rows) {
         // the whole vector, once, by all consumer warps
         const int fill = ((n16 + G::kSegChunks - 1) / G::kSegChunks) * G::kSegChunks;
-        stage_vector<MODE, 8>(vec, v, n16, fill, threadIdx.x, CW * 32);  // 16384 codes: every load of a thread in flight at once
+        stage_vector<MODE, 4>(vec, v, n16, fill, threadIdx.x, CW * 32);
         uint32_t parity = 0;
         alive = mbar_sync(start_bar, parity, status);
         if (threadIdx.x == 0) RING_STAMP(out, 4);
