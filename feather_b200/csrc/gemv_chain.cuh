@@ -82,9 +82,11 @@ constexpr int kChainSegBytes = kChainSegChunks * 16;
 constexpr int kChainStageBytes = kChainCW * kChainSegBytes;       // 32 KiB
 constexpr int kChainVecBytes = kChainTile * 2;                    // one FP16 vector buffer
 constexpr int kChainBarriers = 2 * kChainStages + 4;              // full, empty, vec_full[2], vec_empty[2]
+constexpr int kChainArSlots = 8;                 // tasks of an all-reduced op whose partial sums wait in shared memory
 constexpr int kChainSmemBytes = 2 * kChainVecBytes + kChainStages * kChainStageBytes +
                                 kChainBarriers * 8 + 8 * 4 +       // + 8 per-op arrival counters
-                                kChainCachedOps * 48;              // + the table
+                                kChainCachedOps * 48 +             // + the table
+                                kChainArSlots * (kChainCW + 1) * 4;  // + partial sums and their counters
 constexpr int kChainThreads = (kChainCW + 3) * 32;   // consumers, producer, vector warp, reduce warp
 
 // Tensor-parallel launch: where every rank's inbox and flag block live, as mapped
@@ -215,6 +217,8 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
     unsigned int* op_cnt = reinterpret_cast<unsigned int*>(bar_mem + 8 * kChainBarriers);
     uint4* table_w = reinterpret_cast<uint4*>(bar_mem + 8 * kChainBarriers + 8 * 4);
     const uint4* table = table_w;
+    float* ar_stage = reinterpret_cast<float*>(table_w + 3 * kChainCachedOps);          // [slot][row of the task]
+    unsigned int* ar_cnt = reinterpret_cast<unsigned int*>(ar_stage + kChainArSlots * kChainCW);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
     if (threadIdx.x == 0) {
@@ -227,6 +231,7 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
             mbar_init(vec_empty(b), kChainCW);
         }
         for (int i = 0; i < 8; ++i) op_cnt[i] = 0u;
+        for (int i = 0; i < kChainArSlots; ++i) ar_cnt[i] = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (!EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -256,22 +261,36 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
                 for (int r0 = g.row_begin; r0 < g.row_end && alive; r0 += 32) {
                     const int row = r0 + lane;
                     if (row < g.row_end) {
+                        // The ranks' pairs for this row, eight ranks at a time with all eight loads
+                        // in flight (asked for one after the other, every rank costs an L2 round
+                        // trip, and 44 all-reduced ops x 8 ranks of those were most of an 8-GPU
+                        // token); a pair whose tag is not this call's yet is polled on its own.
                         float total = 0.f;
-                        for (int q = 0; q < ar.world; ++q) {   // rank order: the same bits everywhere
-                            const float* src = ar.inbox[ar.rank] + 2 * ar.pair_index(epoch, ai, q, row);
-                            uint2 x = ld_volatile_v2(src);
-                            if (x.y != epoch) {
-                                const unsigned long long t0 = global_timer_ns();
-                                do {
-                                    x = ld_volatile_v2(src);
-                                    if (global_timer_ns() - t0 > kWaitLimitNs) {
-                                        atomicOr(status, 2u);   // rank q's sums did not arrive in time
-                                        alive = false;
-                                        break;
+                        for (int q0 = 0; q0 < ar.world && alive; q0 += 8) {
+                            uint2 x[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                if (q0 + i < ar.world)
+                                    x[i] = ld_volatile_v2(ar.inbox[ar.rank] + 2 * ar.pair_index(epoch, ai, q0 + i, row));
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                if (q0 + i < ar.world) {
+                                    if (x[i].y != epoch) {
+                                        const float* src = ar.inbox[ar.rank] + 2 * ar.pair_index(epoch, ai, q0 + i, row);
+                                        const unsigned long long t0 = global_timer_ns();
+                                        do {
+                                            x[i] = ld_volatile_v2(src);
+                                            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                                                atomicOr(status, 2u);   // that rank's sums did not arrive in time
+                                                alive = false;
+                                                break;
+                                            }
+                                        } while (x[i].y != epoch);
                                     }
-                                } while (x.y != epoch);
+                                    // rank order: the same bits everywhere
+                                    total = q0 + i == 0 ? __uint_as_float(x[i].x) : total + __uint_as_float(x[i].x);
+                                }
                             }
-                            total = q == 0 ? __uint_as_float(x.x) : total + __uint_as_float(x.x);
                         }
                         if (alive && bounds_ok(row < d.M)) chain_store_row(d, row, total);
                     }
@@ -413,7 +432,7 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
         }
         int s = 0;
         uint32_t phase = 0;
-        int vec_idx = -1, sig_idx = 0;
+        int vec_idx = -1, sig_idx = 0, ar_seq = 0;
         const uint32_t* staged_v = nullptr;
         int staged_n = -1, staged_mode = -1;
         bool alive = true;
@@ -467,15 +486,38 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
                     warp_reduce_rows<1>(sums, lane);   // every lane holds the row's sum
                     const int ai = d.ar_index();
                     if (ai >= 0) {
-                        // partial sum of a column-sharded op: lane q hands it to rank q (this rank
-                        // included), tagged with the call number; the reduce warps do the rest
-                        if (lane < ar.world)
-                            st_volatile_v2(ar.inbox[lane] + 2 * ar.pair_index(epoch, ai, ar.rank, row),
-                                           __float_as_uint(sums[0]), epoch);
+                        // Partial sum of a column-sharded op.  The task's (up to) 16 sums meet in
+                        // shared memory and the warp that brings the last one sends them to every
+                        // rank (this one included) as (sum, call number) pairs, 128 contiguous bytes
+                        // per rank in 16-byte stores: one NVLink packet per rank and task instead
+                        // of one per rank and row, which is what the links charge for.  The reduce
+                        // warps do the rest.
+                        const int aslot = ar_seq & (kChainArSlots - 1);
+                        const int row0 = g.row_begin + task * kChainCW;
+                        const int t_rows = min(kChainCW, g.row_end - row0);
+                        if (lane == 0) ar_stage[aslot * kChainCW + slot] = sums[0];
+                        __threadfence_block();
+                        unsigned int before = 0;
+                        if (lane == 0) before = atomicAdd(ar_cnt + aslot, 1u);
+                        before = __shfl_sync(0xFFFFFFFFu, before, 0);
+                        if (before == (unsigned int)t_rows - 1u) {
+                            if (lane == 0) ar_cnt[aslot] = 0u;
+                            __threadfence_block();
+                            const int j = lane & 7;                       // rows 2j, 2j + 1 of the task
+                            const float s0 = 2 * j < t_rows ? ar_stage[aslot * kChainCW + 2 * j] : 0.f;
+                            const float s1 = 2 * j + 1 < t_rows ? ar_stage[aslot * kChainCW + 2 * j + 1] : 0.f;
+                            for (int q0 = 0; q0 < ar.world; q0 += 4) {
+                                const int q = q0 + (lane >> 3);
+                                if (q < ar.world && 2 * j < t_rows)
+                                    st_volatile_v4(ar.inbox[q] + 2 * ar.pair_index(epoch, ai, ar.rank, row0 + 2 * j),
+                                                   make_uint4(__float_as_uint(s0), epoch, __float_as_uint(s1), epoch));
+                            }
+                        }
                     } else if (lane == 0 && bounds_ok(row >= 0 && row < d.M)) {
                         chain_store_row(d, row, sums[0]);
                     }
                 }
+                ++ar_seq;   // every warp counts every task: the shared-memory slot of a task's partial sums
             }
             if (!alive) break;
             if (d.signal() && d.ar_index() < 0) {   // all-reduced ops are signalled by the reduce warp
