@@ -10,8 +10,9 @@
 //
 //   * the producer warp walks (op, task, segment) and keeps a ring of
 //     kChainStages shared-memory stages full with cp.async.bulk; a stage holds
-//     up to 16 rows x 2 KiB of one op; it runs ahead across op boundaries as far
-//     as the ring allows (weights do not depend on earlier ops);
+//     up to 16 rows x 2 KiB of one op (rows of one segment as a few large
+//     copies: the copy engine charges per request); it runs ahead across op
+//     boundaries as far as the ring allows (weights do not depend on earlier ops);
 //   * 16 consumer warps each OWN one row of a stage for all its columns (no
 //     CTA-wide reduction; the arithmetic and its order are those of
 //     gemv_rows_kernel / gemv_ring_kernel, so every op's result has the bits
@@ -29,13 +30,15 @@
 //     op consumes;
 //   * tensor-parallel launches (one per GPU): an op may be COLUMN-sharded, every
 //     rank holding a column block of all rows and the matching slice of the
-//     vector.  Its row sums are partial: the consumer's lanes store (sum, call
-//     number) pairs into every rank's inbox through peer-mapped pointers --
-//     eight bytes that arrive whole, so the data is its own arrival flag -- and
-//     go on with the next row.  A further warp, the reduce warp, polls this
-//     rank's inbox for the pairs of all ranks (bounded), adds them in rank order
-//     and writes the result: the same bits on every rank, no collective launch,
-//     and the NVLink round trip overlaps the streaming of the following ops.
+//     vector.  Its row sums are partial: a task's sums meet in shared memory
+//     and go, as (sum, call number) pairs, into every rank's inbox through
+//     peer-mapped pointers -- eight bytes that arrive whole, so the data is its
+//     own arrival flag, 128 contiguous bytes per rank and task -- and the
+//     consumers go on with the next task.  A further warp, the reduce warp,
+//     reads this rank's inbox for the pairs of all ranks (polling, bounded, what
+//     has not arrived), adds them in rank order and writes the result: the same
+//     bits on every rank, no collective launch, and the NVLink round trip
+//     overlaps the streaming of the following ops.
 //     Every all-reduced op of a launch has its own inbox region, and two sets
 //     of regions alternate by the parity of the call number, which lives in
 //     device memory so that a captured graph can be replayed.
