@@ -637,14 +637,20 @@ def run_ours(args) -> None:
             extra["tinyllama_gemv_chain_1gpu_reencode_separate_launch"] = chain.measure(
                 tokens=20, use_graph=True, reencode="separate")
             # the whole token as ONE persistent launch (feather_gemv_chain_fp8): the same
-            # independent GEMVs; with q/k/v and gate/up merged; and as a true dependency chain
-            # (every op re-encodes its result, the next op of matching length reads it)
+            # independent GEMVs; with q/k/v and gate/up merged; with the model's data flow (every
+            # op re-encodes its result, q/k/v read the previous layer's down output, o reads q's,
+            # gate/up read o's, down reads gate's: four dependent steps per layer); and fully
+            # serial (every op reads the latest output of matching length: 155 dependent steps)
             extra["tinyllama_gemv_chain_1gpu_one_launch"] = chain.measure(
                 tokens=30, use_graph=True, persistent="independent")
             extra["tinyllama_gemv_chain_1gpu_one_launch_merged_qkv_gateup"] = chain.measure(
                 tokens=30, use_graph=True, persistent="independent", merge_projections=True)
-            extra["tinyllama_gemv_chain_1gpu_one_launch_dependent_reencode"] = chain.measure(
-                tokens=30, use_graph=True, persistent="dependent")
+            extra["tinyllama_gemv_chain_1gpu_one_launch_model_dataflow"] = chain.measure(
+                tokens=30, use_graph=True, persistent="model")
+            extra["tinyllama_gemv_chain_1gpu_one_launch_model_dataflow_merged"] = chain.measure(
+                tokens=30, use_graph=True, persistent="model", merge_projections=True)
+            extra["tinyllama_gemv_chain_1gpu_one_launch_serial_dataflow"] = chain.measure(
+                tokens=30, use_graph=True, persistent="serial")
         except Exception as e:  # noqa: BLE001 - the extra section must not sink the headline
             extra["tinyllama_gemv_chain_error"] = {"error": repr(e)}
         # dot on two 2^26-element E5M2 vectors: reuse the packed matrices as operands

@@ -49,14 +49,16 @@ class GemvChain:
         self.static_matrix = static_matrix
         self.reencode = reencode
         self.packed = []  # per op: the packed-output buffer
+        self.names = []   # per op: q, k, v, o, gate, up, down (or qkv, gate_up), lm_head
         self.ops = []  # (packed weights, packed activation, (M, N), out)
         acts = {}
         for n in (HIDDEN, INTER):
             a = torch.randn(n, device=device, generator=gen, dtype=torch.float16)
             acts[n] = fb.pack_fp8_tensor(a, mode)
 
-        def add(m: int, n: int) -> None:
+        def add(m: int, n: int, name: str) -> None:
             w = (0.02 * torch.randn(m, n, device=device, generator=gen)).to(torch.float16)
+            self.names.append(name)
             self.ops.append((fb.pack_fp8_tensor(w, mode), acts[n], (m, n),
                              torch.empty(m, dtype=torch.float32, device=device)))
             self.packed.append(torch.empty((m + 3) // 4, dtype=torch.uint32, device=device))
@@ -67,9 +69,9 @@ class GemvChain:
             ("qkv", HIDDEN + 2 * KV_DIM, HIDDEN), ("o", HIDDEN, HIDDEN),
             ("gate_up", 2 * INTER, HIDDEN), ("down", HIDDEN, INTER))
         for _ in range(layers):
-            for _, m, n in shapes:
-                add(m, n)
-        add(VOCAB, HIDDEN)
+            for name, m, n in shapes:
+                add(m, n, name)
+        add(VOCAB, HIDDEN, "lm_head")
         torch.cuda.synchronize()  # weights are final before any static_matrix GEMV runs
 
     def token(self) -> None:
@@ -120,6 +122,7 @@ class PersistentGemvChain:
         self.lib = fb._lib.load()
         self.static_matrix = static_matrix
         self.outs, self._keep = [], []
+        self.specs = []   # per op: (matrix, vector, (M, N), mode, out_mode) as given
         table = (ChainOp * len(ops))()
         device = None
         for i, op in enumerate(ops):
@@ -144,6 +147,7 @@ class PersistentGemvChain:
                     raise ValueError(f"op {i}: out must hold ceil(M / 4) packed words")
             self.outs.append(out)
             self._keep.append((m, v))
+            self.specs.append((m, v, (M, N), op.get("mode", mode), out_mode))
             t = table[i]
             t.m, t.v, t.out = m.data_ptr(), v.data_ptr(), out.data_ptr()
             t.M, t.N = M, N
@@ -187,20 +191,41 @@ class PersistentGemvChain:
     __call__ = token
 
     @classmethod
-    def from_chain(cls, chain: "GemvChain", dependent: bool = False) -> "PersistentGemvChain":
-        """The ops of a ``GemvChain`` as one launch.  ``dependent=False``: the same
-        independent GEMVs on the chain's fixed activations.  ``dependent=True``: a real
-        dependency chain -- every op writes packed FP8 and every op whose input
-        length matches the latest packed output of that length reads it (and
-        waits for the op that wrote it)."""
-        ops, last = [], {}
-        for i, ((w, a, (m, n), out), words) in enumerate(zip(chain.ops, chain.packed)):
+    def from_chain(cls, chain: "GemvChain", dependent=False) -> "PersistentGemvChain":
+        """The ops of a ``GemvChain`` as one launch.
+
+        ``dependent=False``: the same independent GEMVs on the chain's fixed
+        activations.  ``dependent="model"`` (or True): the data flow of the model
+        whose shapes these are -- every op writes packed FP8; q, k and v read the
+        layer's input (the previous layer's down output), o reads q's output
+        (standing in for the attention output of the same length), gate and up
+        read o's output, down reads gate's, lm_head the last down's; each reader
+        waits for its writer: four dependent steps per layer.  ``dependent="serial"``:
+        every op reads the latest output of matching length, k after q, v after k
+        ...: 155 dependent steps, the worst case."""
+        if dependent is True:
+            dependent = "model"
+        if dependent not in (False, "model", "serial"):
+            raise ValueError("dependent must be False, 'model' or 'serial'")
+        ops, last, src = [], {}, {}
+        reads = {"q": "x", "k": "x", "v": "x", "qkv": "x", "o": "q", "gate": "o", "up": "o",
+                 "gate_up": "o", "down": "gate", "lm_head": "x"}
+        for i, ((w, a, (m, n), out), words, name) in enumerate(zip(chain.ops, chain.packed, chain.names)):
             op = {"m": w, "v": a, "shape": (m, n)}
-            if dependent:
+            if dependent == "serial":
                 op.update(out=words, out_mode=chain.mode)
                 if n in last:
                     op.update(v=last[n][1], wait_op=last[n][0])
                 last[m] = (i, words)
+            elif dependent == "model":
+                op.update(out=words, out_mode=chain.mode)
+                want = reads[name]
+                want = {"q": "qkv", "gate": "gate_up"}.get(want, want) if want not in src else want
+                if want in src:   # the producer's first n codes (merged projections are longer)
+                    op.update(v=src[want][1][: n // 4], wait_op=src[want][0])
+                src[name] = (i, words)
+                if name == "down":
+                    src["x"] = (i, words)
             elif chain.reencode == "fused":
                 op.update(out=words, out_mode=chain.mode)
             else:
@@ -391,12 +416,14 @@ def measure_tp(tokens: int = 30, use_graph: bool = True, mode: str = "E4M3", gro
 def measure(tokens: int = 50, use_graph: bool = True, mode: str = "E4M3",
             merge_projections: bool = False, reencode: str | None = None,
             persistent: str | None = None) -> dict:
-    """``persistent``: None = one launch per GEMV; "independent" / "dependent" =
-    the whole token as one persistent launch (PersistentGemvChain.from_chain)."""
+    """``persistent``: None = one launch per GEMV; "independent", "model" or
+    "serial" = the whole token as one persistent launch with that data flow
+    (PersistentGemvChain.from_chain)."""
     chain = GemvChain(mode, merge_projections=merge_projections, reencode=reencode)
     step = chain.token
     if persistent is not None:
-        step = PersistentGemvChain.from_chain(chain, dependent=persistent == "dependent").token
+        flow = {"independent": False, "dependent": "serial"}.get(persistent, persistent)
+        step = PersistentGemvChain.from_chain(chain, dependent=flow).token
     for _ in range(3):
         step()
     torch.cuda.synchronize()

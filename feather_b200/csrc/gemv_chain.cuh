@@ -19,7 +19,8 @@
 //     of the single-op entry point);
 //   * the vector warp stages the NEXT op's vector (decoded once to FP16 pairs,
 //     two buffers) while the consumers still work on the current op; ops that
-//     share a vector (q/k/v, gate/up) stage it once;
+//     share a vector (q/k/v, gate/up) and wait for the same op, or for none,
+//     stage it once;
 //   * an op may name an earlier op it depends on (`wait_op`: its vector is that
 //     op's packed output).  CTAs that finish their rows of an op count
 //     themselves in done[op] (release); the vector warp of a dependent op polls
@@ -358,7 +359,7 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
         if (EARLY) asm volatile("griddepcontrol.wait;" ::: "memory");  // vectors and counters
         int vec_idx = -1;
         const uint32_t* staged_v = nullptr;
-        int staged_n = -1, staged_mode = -1;
+        int staged_n = -1, staged_mode = -1, staged_wait = -1;   // staged_wait: the op that vector was waited for
         bool alive = true;
         ChainOp next = chain_load_op(ops, table, 0, n_ops);
         for (int op = 0; op < n_ops && alive; ++op) {
@@ -366,8 +367,9 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
             next = chain_load_op(ops, table, op + 1, n_ops);
             const ChainGeom g = chain_geom(d);
             if (g.n_tasks == 0) continue;
-            if (d.v == staged_v && d.N == staged_n && d.mode() == staged_mode && d.wait_op < 0) continue;
-            staged_v = d.v; staged_n = d.N; staged_mode = d.mode();
+            if (d.v == staged_v && d.N == staged_n && d.mode() == staged_mode &&
+                (d.wait_op < 0 || d.wait_op == staged_wait)) continue;
+            staged_v = d.v; staged_n = d.N; staged_mode = d.mode(); staged_wait = d.wait_op;
             ++vec_idx;
             const int b = vec_idx & 1;
             if (vec_idx >= 2 && !mbar_wait_backoff(vec_empty(b), (uint32_t)((vec_idx >> 1) - 1) & 1u, status, 100)) break;
@@ -386,6 +388,7 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
                         }
                     }
                 }
+                alive = __all_sync(0xFFFFFFFFu, alive);   // the lanes leave together
                 if (!alive) break;
             }
             // chunk c (16 codes) -> uint4 (c / 32 * 2 + k) * 32 + c % 32, k = 0, 1: the FP16
@@ -437,7 +440,7 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
         uint32_t phase = 0;
         int vec_idx = -1, sig_idx = 0, ar_seq = 0;
         const uint32_t* staged_v = nullptr;
-        int staged_n = -1, staged_mode = -1;
+        int staged_n = -1, staged_mode = -1, staged_wait = -1;   // staged_wait: the op that vector was waited for
         bool alive = true;
         const uint4* const ring_lane = reinterpret_cast<const uint4*>(ring) + lane;
         ChainOp next = chain_load_op(ops, table, 0, n_ops);
@@ -446,8 +449,9 @@ gemv_chain_kernel(const ChainOp* __restrict__ ops, int n_ops, unsigned int* __re
             next = chain_load_op(ops, table, op + 1, n_ops);
             const ChainGeom g = chain_geom(d);
             if (g.n_tasks == 0) continue;
-            if (!(d.v == staged_v && d.N == staged_n && d.mode() == staged_mode && d.wait_op < 0)) {
-                staged_v = d.v; staged_n = d.N; staged_mode = d.mode();
+            if (!(d.v == staged_v && d.N == staged_n && d.mode() == staged_mode &&
+                (d.wait_op < 0 || d.wait_op == staged_wait))) {
+                staged_v = d.v; staged_n = d.N; staged_mode = d.mode(); staged_wait = d.wait_op;
                 if (vec_idx >= 0) {   // done with the previous vector
                     __syncwarp();
                     if (lane == 0) mbar_arrive(vec_empty(vec_idx & 1));

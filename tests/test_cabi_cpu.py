@@ -96,3 +96,29 @@ def test_header_is_plain_c(tmp_path):
     src.write_text('#include "feather_b200.h"\nint main(void) { return feather_version() == 0; }\n')
     subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only",
                     "-I", os.path.join(ROOT, "include"), str(src)], check=True)
+
+
+def test_host_only_entry_points_of_the_newer_surface(lib):
+    """Sizes, tuning specs and the debug query are pure host code."""
+    # tuning: "key=value,..." ; unknown keys and bad values are rejected, good ones applied
+    assert lib.feather_set_tuning(b"ring_pre_kb=64,dot_ring=2") == 0
+    assert lib.feather_set_tuning(b"ring_pre_kb=128, ring_pre_kb_e4m3=-1") == 0
+    assert lib.feather_set_tuning(b"no_such_knob=1") == -1
+    assert lib.feather_set_tuning(b"dot_unroll=3") == -1
+    assert lib.feather_set_tuning(b"ring_pre_kb") == -1
+    assert lib.feather_set_tuning(None) == -1
+    assert lib.feather_debug_bounds() in (0, 1)
+    for code in (-8, -9):
+        assert lib.feather_strerror(code) not in (b"", b"unknown feather status")
+    # chain plan: counters (ticket + one per op, 16-byte granular) + 48 bytes per op
+    assert lib.feather_gemv_chain_plan_bytes(0) == 0
+    assert lib.feather_gemv_chain_plan_bytes(1) == 16 + 48
+    assert lib.feather_gemv_chain_plan_bytes(155) == 624 + 155 * 48
+    # tensor-parallel inbox: 2 call parities x ops x ranks x rows (rounded up to 16) x (sum, tag)
+    assert lib.feather_gemv_chain_inbox_floats(44, 2048, 8) == 2 * 44 * 8 * 2048 * 2
+    assert lib.feather_gemv_chain_inbox_floats(1, 100, 2) == 2 * 1 * 2 * 112 * 2
+    assert lib.feather_gemv_chain_inbox_floats(0, 2048, 8) == 0
+    # argument checks that come before any CUDA call
+    assert lib.feather_gemv_chain_plan(None, 1, None, 0, None) == -1
+    assert lib.feather_gemv_chain_fp8(None, 1, 0, None) == -1
+    assert lib.feather_gemv_fp8_sharded_wait(None, 0, 1, 1, None, None) == -1

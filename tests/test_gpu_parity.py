@@ -512,11 +512,18 @@ def test_gemv_chain_kernel_config5_token_equals_the_155_launches(fb):
     assert len(p.outs) == 15
     for got, w in zip(p.outs, want):
         assert torch.equal(got, w)
-    # the dependent form (every op re-encodes, inputs come from earlier outputs) runs too
-    d = chain.PersistentGemvChain.from_chain(chain.GemvChain(layers=2), dependent=True)
-    d.token()
-    fb.device_status()
-    assert all(int(o.view(torch.int32).abs().sum()) != 0 for o in d.outs)
+    # the model's data flow (q/k/v read the previous down output and wait for the same op, o
+    # reads q's output ...) and the fully serial one: after the launch every op's output equals
+    # the single-op call on the inputs the launch left behind (its writers' final outputs)
+    for flow, merged in (("model", False), ("model", True), ("serial", False)):
+        d = chain.PersistentGemvChain.from_chain(chain.GemvChain(layers=2, merge_projections=merged),
+                                                 dependent=flow)
+        for _ in range(2):
+            d.token()
+        fb.device_status()
+        for (m, v, shape, mode, out_mode), got in zip(d.specs, d.outs):
+            want = fb.gemv_fp8_ret_packed_gpu(m, v, shape, mode, out_mode=out_mode)
+            assert torch.equal(got.view(torch.int32), want.view(torch.int32)), (flow, merged, shape)
 
 
 def test_gemv_chain_kernel_rejects(fb):
