@@ -12,6 +12,7 @@
 
 #include "../../include/feather_b200.h"
 #include "attention_kernels.cuh"
+#include "attention_tc.cuh"
 #include "dot_kernels.cuh"
 #include "fp8_codec.cuh"
 #include "gemv_chain.cuh"
@@ -36,6 +37,8 @@ namespace feather {
 //   dot_ring         0: register-load dot kernel only; 1, 2, 3: long aligned operands take the
 //                    bulk-copy ring kernel with 6 x 32 KiB, 3 x 64 KiB or 12 x 16 KiB stages
 //   dot_pre_kb       KiB the dot ring kernel asks L2 for ahead of its stream-order wait
+//   attn_tc          attention with 32, 64 or 128 codes per row: 0 the register-fed mma.sync
+//                    kernel, 1 the tcgen05 kernel from 512 queries up, 2 the tcgen05 kernel always
 struct Tuning {
     std::atomic<int> ring_pre_kb{128};
     std::atomic<int> rows_pre{1};
@@ -44,6 +47,7 @@ struct Tuning {
     std::atomic<int> dot_ring{2};
     std::atomic<int> dot_pre_kb{64};
     std::atomic<int> ring_pre_kb_e4m3{-1};
+    std::atomic<int> attn_tc{1};
 };
 static Tuning g_tune;
 
@@ -67,6 +71,7 @@ static int apply_tuning(const char* spec) {
         else if (is("dot_ring") && val >= 0 && val <= 3) g_tune.dot_ring = (int)val;
         else if (is("dot_pre_kb") && val >= 0 && val <= 16384) g_tune.dot_pre_kb = (int)val;
         else if (is("ring_pre_kb_e4m3") && val >= -1 && val <= 16384) g_tune.ring_pre_kb_e4m3 = (int)val;
+        else if (is("attn_tc") && val >= 0 && val <= 2) g_tune.attn_tc = (int)val;
         else return FEATHER_ERR_BAD_ARG;
         p = end;
     }
@@ -576,6 +581,48 @@ static int attention_launch(const uint32_t* q, const uint32_t* k, const uint32_t
     return launch_status();
 }
 
+// The tcgen05 kernel: 128 queries per CTA, the key tiles of a query block split over a
+// cluster of 1, 2, 4 or 8 CTAs so that about two CTAs per SM are in flight.
+template <int D>
+static int attention_tc_launch(const uint32_t* q, const uint32_t* k, const uint32_t* v, float* out,
+                               long long seq_len, const DeviceInfo& dev, cudaStream_t s) {
+    using L = AtcLayout<D>;
+    auto kernel = attention_tc_kernel<D>;
+    static std::atomic<unsigned long long> configured{0};
+    if (int st = ensure_smem(kernel, L::kBytes, configured)) return st;
+    unsigned int* status = nullptr;
+    if (int st = status_word(&status)) return st;
+    const long long blocks = (seq_len + kAtcRows - 1) / kAtcRows;
+    const long long tiles = (seq_len + kAtcTile - 1) / kAtcTile;
+    int splits = 1;
+    while (splits < 8 && blocks * splits < 2ll * dev.sm_count && 2 * splits <= tiles) splits <<= 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)splits, (unsigned)blocks);
+    cfg.blockDim = dim3(kAtcThreads);
+    cfg.dynamicSmemBytes = L::kBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, q, k, v, out, (int)seq_len, status);
+    return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
+}
+
+template <int D>
+static int attention_any(const uint32_t* q, const uint32_t* k, const uint32_t* v, float* out,
+                         long long seq_len, const DeviceInfo& dev, cudaStream_t s) {
+    const int tc = g_tune.attn_tc.load(std::memory_order_relaxed);
+    // a query block is at most 65535 grid rows; cp.async moves 16-byte pieces
+    if (tc && (tc == 2 || seq_len >= 512) && seq_len <= 65535ll * kAtcRows && aligned(q, 16) &&
+        aligned(k, 16) && aligned(v, 16))
+        return attention_tc_launch<D>(q, k, v, out, seq_len, dev, s);
+    return attention_launch<D>(q, k, v, out, seq_len, dev, s);
+}
+
 // Decode (optionally through ReLU) n_elems codes: a grid of up to 16 CTAs per SM,
 // each thread walking words with four loads in flight.
 static int decode_launch(const uint32_t* src, float* dst, long long n_elems, int mode, bool ieee,
@@ -815,9 +862,9 @@ int feather_attention_fp8_e5m2(const uint32_t* q, const uint32_t* k, const uint3
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     switch (h_dim_words) {
         case 4: return attention_launch<16>(q, k, v, out, seq_len, *dev, s);
-        case 8: return attention_launch<32>(q, k, v, out, seq_len, *dev, s);
-        case 16: return attention_launch<64>(q, k, v, out, seq_len, *dev, s);
-        case 32: return attention_launch<128>(q, k, v, out, seq_len, *dev, s);
+        case 8: return attention_any<32>(q, k, v, out, seq_len, *dev, s);
+        case 16: return attention_any<64>(q, k, v, out, seq_len, *dev, s);
+        case 32: return attention_any<128>(q, k, v, out, seq_len, *dev, s);
         case 64: return attention_launch<256>(q, k, v, out, seq_len, *dev, s);
         case 128: return attention_launch<512>(q, k, v, out, seq_len, *dev, s);
         default: return h_dim_words > 128 ? FEATHER_ERR_TOO_LARGE : FEATHER_ERR_BAD_ARG;

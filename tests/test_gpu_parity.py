@@ -958,14 +958,49 @@ def test_gemv_multi_rejects(fb):
 
 
 # ------------------------------------------------------------------ attention --
+@pytest.fixture
+def attention_kernel(fb):
+    """Select the attention kernel for one test; the library's default afterwards."""
+    lib = fb._lib.load()
+    knob = {"default": b"attn_tc=1", "tcgen05": b"attn_tc=2", "mma.sync": b"attn_tc=0"}
+
+    def choose(name):
+        assert lib.feather_set_tuning(knob[name]) == 0
+    yield choose
+    assert lib.feather_set_tuning(knob["default"]) == 0
+
+
+def test_attention_kernels_agree_without_key_split(fb, attention_kernel):
+    """One key tile per query block: the tcgen05 kernel and the register-fed kernel run the
+    same arithmetic and differ by the order of a few FP32 additions at most."""
+    from feather_b200.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu as attn
+    for seq, d in ((64, 32), (50, 64), (64, 128)):
+        rng = np.random.default_rng(seq * d)
+        x = [torch.from_numpy(rng.standard_normal((seq, d)).astype(np.float16)).cuda() for _ in range(3)]
+        q, k, v = (fb.pack_fp8_tensor(t, "E5M2") for t in x)
+        attention_kernel("mma.sync")
+        a = attn(q, k, v, seq, d // 4)
+        attention_kernel("tcgen05")
+        b = attn(q, k, v, seq, d // 4)
+        fb.device_status()
+        assert O.normalised_error(b.cpu().numpy(), a.cpu().numpy()) < 2e-6
+
+
 @pytest.mark.parametrize("seq,d", [(128, 64), (100, 32), (200, 128), (64, 16), (1, 64), (1000, 128),
                                    (4096, 64), (2500, 32), (8192, 128), (130, 256), (64, 512),
                                    (1024, 256), (777, 512), (4096, 512)])
-def test_attention_vs_oracle_and_reference_outputs(fb, golden, seq, d):
+@pytest.mark.parametrize("kernel", ["default", "tcgen05", "mma.sync"])
+def test_attention_vs_oracle_and_reference_outputs(fb, golden, seq, d, kernel, attention_kernel):
     """Packed-E5M2 attention against the oracle (same tiles, same FP16 rounding of the
     probabilities), the reference kernel's own outputs where the fixture has them, and
-    torch's scaled_dot_product_attention when the key tiles are full."""
+    torch's scaled_dot_product_attention when the key tiles are full.  Every shape runs
+    through the library's own choice of kernel, through the tcgen05 kernel (rows of 32, 64
+    or 128 codes; other widths have only the register-fed kernel) and through the
+    register-fed kernel."""
     from feather_b200.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu as attn
+    if kernel != "default" and d not in (32, 64, 128):
+        pytest.skip("one kernel only for this width")
+    attention_kernel(kernel)
     g = golden("attention")
     key = f"s{seq}_d{d}"
     seed = int(g[key + "_seed"]) if key + "_seed" in g else seq + d
