@@ -11,26 +11,38 @@
 // (:97-101), one division by the sum at the end (:103-106); keys past seq_len in the last
 // tile are zero codes whose (zero) scores take part in the softmax, as in the reference.
 //
-// Mapping.  A CTA of 128 threads owns 128 query rows: thread t owns row t, which is lane
-// t of tensor memory, so the softmax needs no shuffles.  The key tiles of one query block
-// are split over the 1, 2, 4 or 8 CTAs of a thread-block cluster (contiguous ranges), each
-// with its own running maximum, sum and output; at the end every CTA leaves its partial
-// result in its own shared memory and the cluster merges them through distributed shared
-// memory (out = sum_c O_c e^(m_c - m) / sum_c l_c e^(m_c - m), CTAs in rank order), each
-// CTA writing 128 / cluster rows.  No global scratch, no atomics, deterministic.
+// Mapping.  A CTA owns 128 query rows = the 128 lanes of tensor memory.  It is eight worker
+// warps and one issuing warp.  Two worker threads share a row (warps w and w + 4 reach the
+// same 32 lanes): each takes half of a tile's keys and half of the output columns, and
+// both read all 64 scores of the row for its maximum, so the softmax needs no shuffles
+// and no exchange.  The key tiles of one query block are split over the 1, 2, 4 or 8 CTAs
+// of a thread-block cluster (contiguous ranges, as many CTAs as still run in one wave),
+// each with its own running maximum, sum and output; at the end every CTA leaves its
+// partial result in its own shared memory and the cluster merges them through distributed
+// shared memory (out = sum_c O_c 2^(m_c - m) / sum_c l_c 2^(m_c - m), CTAs in rank order),
+// each CTA writing 128 / cluster rows.  No global scratch, no atomics, deterministic.
 //
-// Per key tile:
-//   1. K codes (raw bytes: the tensor core reads E5M2 itself, kind::f8f6f4) and V codes of
-//      the NEXT tile are fetched with cp.async into the other half of a double buffer;
-//   2. one thread issues S = Q K^T (128 x 64, d / 32 instructions) into tensor-memory
-//      columns 0..63 and commits to an mbarrier;
-//   3. meanwhile all threads spread this tile's V codes to FP16 (an E5M2 code is the high
-//      byte of an FP16 number) in the layout the second product reads;
-//   4. each thread reads its row of S (tcgen05.ld 32x32b), runs the online softmax and
-//      stores the FP16 probabilities as the A operand of the second product;
-//   5. one thread issues P V (128 x d, 4 instructions, kind::f16) into columns 64..64+d-1;
-//   6. each thread reads its row of P V and folds it into its FP32 output registers
-//      (o = o * alpha + pv).
+// Tensor memory: columns 0..63 hold S = Q K^T of the current tile, columns 64..64+d-1 the
+// output, which P V accumulates into; before P(i) V(i) is issued each worker has multiplied
+// its half row of the output by alpha = 2^(old maximum - new maximum) (tcgen05.ld / .st),
+// which is the reference's acc * alpha + P V.  A warp skips that when none of its rows saw
+// a new maximum (alpha is exactly 1 then).
+//
+// Per key tile i there is ONE CTA barrier.  Before it a worker
+//   1. waits for S(i) and for P(i-1) V(i-1) (mbarriers the tensor core arrives on),
+//   2. reads its scores (tcgen05.ld 32x32b), runs the online softmax -- the maximum lives in
+//      the exponent's scale, m2 = max * log2(e) / sqrt(d), so a probability is one FMA and
+//      one ex2 -- and stores its FP16 probabilities as the A operand of the second product,
+//   3. rescales its half row of the output,
+//   4. sees its cp.async copies of tile i+1 land;
+// behind it the issuing warp issues S(i+1) (kind::f8f6f4: the tensor core reads the E5M2
+// codes themselves, d / 32 instructions) and then P(i) V(i) (kind::f16, 4 instructions),
+// each followed by a tcgen05.commit, while the workers
+//   5. start the copies of tile i+2 (K straight into the operand layout, V as stored) and
+//   6. spread the V codes of tile i+1 to FP16 (an E5M2 code is the high byte of an FP16
+//      number) in the layout the second product reads.
+// K codes, V codes and V as FP16 are double-buffered; P and S are not (their readers have
+// finished by the time they are written again, see the loop).
 //
 // Shared-memory operand layouts (no swizzle; 16-byte units; LBO / SBO of the matrix
 // descriptor):
@@ -53,7 +65,8 @@
 namespace feather {
 
 constexpr int kAtcRows = 128;      // queries per CTA = lanes of tensor memory
-constexpr int kAtcThreads = 128;
+constexpr int kAtcWorkers = 256;    // two threads per query row: each takes half the keys and half the columns
+constexpr int kAtcThreads = kAtcWorkers + 32;   // ... and a warp that issues the tensor-core instructions
 constexpr int kAtcTile = 64;       // keys per step (the reference's tile, attention.py:9)
 
 template <int D>
@@ -63,20 +76,20 @@ struct AtcLayout {
     static constexpr int kK = kQ + kQBytes;                    // 2 x [D/16][64][16 B]
     static constexpr int kKBytes = kAtcTile * D;
     static constexpr int kVraw = kK + 2 * kKBytes;             // 2 x [64][D] codes
-    static constexpr int kV = kVraw + 2 * kKBytes;             // FP16, see above
+    static constexpr int kV = kVraw + 2 * kKBytes;             // 2 x FP16, see above
     static constexpr int kVSbo = 144;
     static constexpr int kVLbo = (D / 8) * kVSbo;
     static constexpr int kVBytes = (kAtcTile / 8) * kVLbo;
-    static constexpr int kP = kV + kVBytes;                    // [8][128][16 B] FP16
+    static constexpr int kP = kV + 2 * kVBytes;                // [8][128][16 B] FP16
     static constexpr int kPBytes = kAtcRows * kAtcTile * 2;
     static constexpr int kBar = kP + kPBytes;                  // two mbarriers, tensor-memory base
     static constexpr int kTileBytes = kBar + 32;
     // the merge reuses the operand space: O as [128][D + 4] floats (the odd 16 B keep a
-    // thread-per-row's 16-byte stores free of bank conflicts), then m[128], l[128]
+    // thread-per-row's 16-byte stores free of bank conflicts), then m[128] and the two threads' l[2][128]
     static constexpr int kMergeStride = D + 4;
     static constexpr int kMergeM = kAtcRows * kMergeStride * 4;
-    static constexpr int kMergeBytes = kMergeM + 2 * kAtcRows * 4;
-    static constexpr int kWeightBytes = 9 * kAtcRows * 4;      // the merging CTA's own weights, behind it
+    static constexpr int kMergeBytes = kMergeM + 3 * kAtcRows * 4;
+    static constexpr int kWeightBytes = 0;
     static_assert(kMergeBytes + kWeightBytes <= kBar, "the merge buffers must not reach the barriers");
     static constexpr int kCols = D > 64 ? 256 : 128;           // tensor-memory columns: 64 (S) + D (P V)
     // at most 512 / kCols CTAs of this kernel per SM: ask for more than 1 / (that + 1) of 227 KiB
@@ -115,21 +128,70 @@ __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t a, uint64_t b, 
                      "  tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p; }"
                      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
-// This thread's lane of tensor memory, 32 consecutive columns from taddr.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&r)[32]) {
-    uint32_t x[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]), "=r"(x[4]), "=r"(x[5]), "=r"(x[6]), "=r"(x[7]),
-          "=r"(x[8]), "=r"(x[9]), "=r"(x[10]), "=r"(x[11]), "=r"(x[12]), "=r"(x[13]), "=r"(x[14]), "=r"(x[15]),
-          "=r"(x[16]), "=r"(x[17]), "=r"(x[18]), "=r"(x[19]), "=r"(x[20]), "=r"(x[21]), "=r"(x[22]), "=r"(x[23]),
-          "=r"(x[24]), "=r"(x[25]), "=r"(x[26]), "=r"(x[27]), "=r"(x[28]), "=r"(x[29]), "=r"(x[30]), "=r"(x[31])
-        : "r"(taddr) : "memory");
+// This thread's lane of tensor memory, N = 16 or 32 consecutive columns from taddr.
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, float (&r)[N]) {
+    static_assert(N == 16 || N == 32, "16 or 32 columns");
+    uint32_t x[N];
+    if constexpr (N == 32)
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]), "=r"(x[4]), "=r"(x[5]), "=r"(x[6]), "=r"(x[7]),
+              "=r"(x[8]), "=r"(x[9]), "=r"(x[10]), "=r"(x[11]), "=r"(x[12]), "=r"(x[13]), "=r"(x[14]), "=r"(x[15]),
+              "=r"(x[16]), "=r"(x[17]), "=r"(x[18]), "=r"(x[19]), "=r"(x[20]), "=r"(x[21]), "=r"(x[22]), "=r"(x[23]),
+              "=r"(x[24]), "=r"(x[25]), "=r"(x[26]), "=r"(x[27]), "=r"(x[28]), "=r"(x[29]), "=r"(x[30]), "=r"(x[31])
+            : "r"(taddr) : "memory");
+    else
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]), "=r"(x[4]), "=r"(x[5]), "=r"(x[6]), "=r"(x[7]),
+              "=r"(x[8]), "=r"(x[9]), "=r"(x[10]), "=r"(x[11]), "=r"(x[12]), "=r"(x[13]), "=r"(x[14]), "=r"(x[15])
+            : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < 32; ++i) r[i] = __uint_as_float(x[i]);
+    for (int i = 0; i < N; ++i) r[i] = __uint_as_float(x[i]);
+}
+// The same lane and columns, written.
+template <int N>
+__device__ __forceinline__ void tmem_st(uint32_t taddr, const float (&r)[N]) {
+    static_assert(N == 16 || N == 32, "16 or 32 columns");
+    uint32_t x[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) x[i] = __float_as_uint(r[i]);
+    if constexpr (N == 32)
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+            :: "r"(x[0]), "r"(x[1]), "r"(x[2]), "r"(x[3]), "r"(x[4]), "r"(x[5]), "r"(x[6]), "r"(x[7]),
+               "r"(x[8]), "r"(x[9]), "r"(x[10]), "r"(x[11]), "r"(x[12]), "r"(x[13]), "r"(x[14]), "r"(x[15]),
+               "r"(x[16]), "r"(x[17]), "r"(x[18]), "r"(x[19]), "r"(x[20]), "r"(x[21]), "r"(x[22]), "r"(x[23]),
+               "r"(x[24]), "r"(x[25]), "r"(x[26]), "r"(x[27]), "r"(x[28]), "r"(x[29]), "r"(x[30]), "r"(x[31]),
+               "r"(taddr) : "memory");
+    else
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+            :: "r"(x[0]), "r"(x[1]), "r"(x[2]), "r"(x[3]), "r"(x[4]), "r"(x[5]), "r"(x[6]), "r"(x[7]),
+               "r"(x[8]), "r"(x[9]), "r"(x[10]), "r"(x[11]), "r"(x[12]), "r"(x[13]), "r"(x[14]), "r"(x[15]),
+               "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// CTA barrier with an OR over a predicate; the worker warps and the issuing warp meet in it
+// from different places in the code.
+__device__ __forceinline__ bool cta_sync_or(bool pred) {
+    uint32_t r;
+    asm volatile("{ .reg .pred p, q; setp.ne.u32 p, %1, 0; bar.red.or.pred q, 0, p; selp.u32 %0, 1, 0, q; }"
+                 : "=r"(r) : "r"((uint32_t)pred) : "memory");
+    return r != 0;
 }
 __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n"
@@ -148,43 +210,46 @@ __device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t addr) {
                  : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w) : "r"(addr) : "memory");
     return x;
 }
+__device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float4 x) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"r"(addr), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w) : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float x) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(x) : "memory");
+}
 __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
     float x;
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(x) : "r"(addr) : "memory");
     return x;
 }
 
-#ifdef FEATHER_ATC_STAMPS
-// Diagnostic build only: the SM's cycle counter at points of CTA (0, 0)'s thread 0.
-__device__ unsigned long long g_atc_stamps[256];
-#define ATC_STAMP(i) do { if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && (i) < 256) g_atc_stamps[i] = (unsigned long long)clock64(); } while (0)
-#else
-#define ATC_STAMP(i) do { } while (0)
-#endif
-
 // D = codes per row: 32, 64 or 128.  Grid (splits, query blocks), cluster (splits, 1, 1),
-// 128 threads, AtcLayout<D>::kBytes of dynamic shared memory.  q, k, v 16-byte aligned.
+// 288 threads, AtcLayout<D>::kBytes of dynamic shared memory.  q, k, v 16-byte aligned.
 template <int D>
-__global__ void __launch_bounds__(kAtcThreads)
+__global__ void __launch_bounds__(kAtcThreads, 2)
 attention_tc_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict__ k,
                     const uint32_t* __restrict__ v, float* __restrict__ out, int seq_len,
                     unsigned int* status) {
     extern __shared__ __align__(128) unsigned char atc_smem[];
     using L = AtcLayout<D>;
     constexpr int KU = D / 16;                    // 16-byte units per row of codes
+    constexpr int DH = D / 2;                     // output columns per thread
+    constexpr int KH = kAtcTile / 2;              // keys per thread
     const int tid = threadIdx.x, warp = tid >> 5;
+    const int row = tid & (kAtcRows - 1);         // this thread's query row = lane of tensor memory
+    const int half = tid >> 7;                    // ... and which half of the keys and columns
     const int n_split = (int)gridDim.x, split = (int)blockIdx.x;
     const int row0 = (int)blockIdx.y * kAtcRows;
     const uint32_t sbase = smem_u32(atc_smem);
     const uint32_t bar_s = sbase + L::kBar, bar_o = bar_s + 8;
-    ATC_STAMP(0);
 
     if (tid == 0) {
         mbar_init(bar_s, 1);
         mbar_init(bar_o, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {
+    constexpr int kIssuer = kAtcWorkers / 32;     // the issuing warp: it also owns the tensor-memory allocation
+    if (warp == kIssuer) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(sbase + L::kBar + 16), "r"((uint32_t)L::kCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -193,7 +258,8 @@ attention_tc_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(atc_smem + L::kBar + 16);
-    const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 lanes
+    // a warp reaches the 32 lanes of its quarter: warps w and w + 4 share lanes 32 (w % 4) ..
+    const uint32_t tmem_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);
 
     // this CTA's key tiles: a contiguous range
     const int tiles = (seq_len + kAtcTile - 1) / kAtcTile;
@@ -201,228 +267,256 @@ attention_tc_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict__
     const int t_begin = min(split * per, tiles);
     const int n = min(tiles, t_begin + per) - t_begin;
 
+    // Copies of one key tile, 16 bytes per cp.async and consecutive threads along a row of
+    // codes (whole 128-byte lines of global memory).  K: unit (row, u) lands at
+    // (u * 64 + row) * 16, the operand layout; V: rows as they are.  A tile that reaches
+    // past seq_len gets zeros there.
     auto load_kv = [&](int tile, int buf) {
         const int key0 = tile * kAtcTile;
+        const bool whole = key0 + kAtcTile <= seq_len;
+        const char* ksrc = reinterpret_cast<const char*>(k) + (size_t)key0 * D;
+        const char* vsrc = reinterpret_cast<const char*>(v) + (size_t)key0 * D;
+        const uint32_t kdst = sbase + L::kK + buf * L::kKBytes, vdst = sbase + L::kVraw + buf * L::kKBytes;
 #pragma unroll
-        for (int c = tid; c < kAtcTile * KU; c += kAtcThreads) {
-            // K: unit c = (row c % 64, 16-byte unit c / 64) lands at c * 16
-            const int key = key0 + (c & (kAtcTile - 1));
-            const char* src = reinterpret_cast<const char*>(k) + (size_t)min(key, seq_len - 1) * D + (c >> 6) * 16;
-            cp_async_16(sbase + L::kK + buf * L::kKBytes + c * 16, src, key < seq_len ? 16 : 0);
-        }
-#pragma unroll
-        for (int c = tid; c < kAtcTile * KU; c += kAtcThreads) {
-            // V: rows as they are
-            const int key = key0 + c / KU;
-            const char* src = reinterpret_cast<const char*>(v) + (size_t)min(key, seq_len - 1) * D + (c % KU) * 16;
-            cp_async_16(sbase + L::kVraw + buf * L::kKBytes + c * 16, src, key < seq_len ? 16 : 0);
+        for (int c = tid; c < kAtcTile * KU; c += kAtcWorkers) {
+            const int r = c / KU, u = c % KU;
+            const int bytes = (whole || key0 + r < seq_len) ? 16 : 0;
+            const int from = bytes ? c * 16 : 0;
+            cp_async_16(kdst + (u * kAtcTile + r) * 16, ksrc + from, bytes);
+            cp_async_16(vdst + c * 16, vsrc + from, bytes);
         }
     };
-    if (n > 0) {
+    // One thread issues the products: S = Q K^T of a tile (d / 32 instructions of 32 codes,
+    // two 16-byte units, each) and P V (4 instructions of 16 keys, two key groups, each).
+    auto issue_qk = [&](int buf) {
 #pragma unroll
-        for (int c = tid; c < kAtcRows * KU; c += kAtcThreads) {
-            const int row = row0 + (c & (kAtcRows - 1));
-            const char* src = reinterpret_cast<const char*>(q) + (size_t)min(row, seq_len - 1) * D + (c >> 7) * 16;
-            cp_async_16(sbase + L::kQ + c * 16, src, row < seq_len ? 16 : 0);
-        }
-        load_kv(t_begin, 0);
-    }
-    cp_async_commit();
-
-    ATC_STAMP(1);
-    float o[D];
+        for (int j = 0; j < D / 32; ++j)
+            tc_mma<true>(tmem,
+                         tc_desc(sbase + L::kQ + j * 2 * (kAtcRows * 16), kAtcRows * 16, 128),
+                         tc_desc(sbase + L::kK + buf * L::kKBytes + j * 2 * (kAtcTile * 16), kAtcTile * 16, 128),
+                         kAtcIdescQK, j > 0);
+        tc_commit(bar_s);
+    };
+    auto issue_pv = [&](int buf, bool accumulate) {
 #pragma unroll
-    for (int c = 0; c < D; ++c) o[c] = 0.f;
-    float m = -INFINITY, l = 0.f;
-    const float sqrt_d = sqrtf((float)D);
-    uint32_t phase = 0;
-    bool ok = true;
-
-    for (int i = 0; i < n; ++i) {
-        const int buf = i & 1;
-        if (i + 1 < n) load_kv(t_begin + i + 1, buf ^ 1);
-        cp_async_commit();
-        cp_async_wait<1>();                 // all but the newest group: Q and tile i are here
-        fence_proxy_async_smem();           // ... and visible to the tensor core's reads
-        tc_fence_before();
-        if (__syncthreads_or(!ok)) break;
-        ATC_STAMP(8 + 6 * i);
-        if (tid == 0) {
-            tc_fence_after();
+        for (int j = 0; j < kAtcTile / 16; ++j)
+            tc_mma<false>(tmem + kAtcTile,
+                          tc_desc(sbase + L::kP + j * 2 * (kAtcRows * 16), kAtcRows * 16, 128),
+                          tc_desc(sbase + L::kV + buf * L::kVBytes + j * 2 * L::kVLbo, L::kVLbo, L::kVSbo),
+                          kAtcIdescPV<D>, accumulate || j > 0);
+        tc_commit(bar_o);
+    };
+    // V codes -> FP16 (8 codes -> one 16-byte unit) in the layout P V reads.
+    auto spread_v = [&](int buf) {
 #pragma unroll
-            for (int j = 0; j < D / 32; ++j)  // 32 codes (two 16-byte units) per instruction
-                tc_mma<true>(tmem,
-                             tc_desc(sbase + L::kQ + j * 2 * (kAtcRows * 16), kAtcRows * 16, 128),
-                             tc_desc(sbase + L::kK + buf * L::kKBytes + j * 2 * (kAtcTile * 16), kAtcTile * 16, 128),
-                             kAtcIdescQK, j > 0);
-            tc_commit(bar_s);
-        }
-        __syncwarp();
-        // ---- V codes -> FP16 (8 codes -> one 16-byte unit), the previous P V has completed ----
-#pragma unroll
-        for (int u = tid; u < kAtcTile * (D / 8); u += kAtcThreads) {
+        for (int u = tid; u < kAtcTile * (D / 8); u += kAtcWorkers) {
             const int ng = u % (D / 8), key = u / (D / 8);
             const uint2 w = *reinterpret_cast<const uint2*>(atc_smem + L::kVraw + buf * L::kKBytes + key * D + ng * 8);
             uint4 h;
             decode_word_h2<kE5M2>(w.x, h.x, h.y);
             decode_word_h2<kE5M2>(w.y, h.z, h.w);
-            *reinterpret_cast<uint4*>(atc_smem + L::kV + (key >> 3) * L::kVLbo + ng * L::kVSbo + (key & 7) * 16) = h;
+            *reinterpret_cast<uint4*>(atc_smem + L::kV + buf * L::kVBytes + (key >> 3) * L::kVLbo + ng * L::kVSbo +
+                                      (key & 7) * 16) = h;
         }
-        // ---- this row's scores and the online softmax ----
-        ATC_STAMP(9 + 6 * i);
-        ok = mbar_wait(bar_s, phase, status) && ok;
-        tc_fence_after();
-        ATC_STAMP(10 + 6 * i);
-        float s[kAtcTile];
-        {
-            float a[32], b[32];
-            tmem_ld32(tmem_row, a);
-            tmem_ld32(tmem_row + 32, b);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                s[j] = a[j];
-                s[32 + j] = b[j];
+    };
+
+    // The output accumulates in tensor memory (columns 64 .. 64 + D - 1): P(i) V(i) adds to
+    // it, and before that product is issued each thread has multiplied its half row by
+    // alpha = e^(old maximum - new maximum), as the reference's acc * alpha + P V does.
+    // The running maximum lives in the exponent's own scale: m2 = max(score) * log2(e) /
+    // sqrt(d), so that e^(score / sqrt(d) - max) is one FMA and one ex2 per score.  l sums
+    // this thread's half of the keys only; the halves meet in the merge.
+    float m2 = -INFINITY, l = 0.f;
+    const float scale2 = 1.4426950408889634f / sqrtf((float)D);
+    bool ok = true;
+    constexpr int CH = 16;                        // output columns per tensor-memory load or store (32 at a time spill registers)
+    const uint32_t tmem_o = tmem_row + kAtcTile + DH * half;
+
+    // The loop has ONE CTA barrier per tile.  At the barrier of tile i every worker has
+    // stored its part of P(i), rescaled its part of the output, stored its part of V(i + 1)
+    // as FP16 (second half of the previous trip) and has seen its copies of tile i + 1's
+    // codes land; behind the barrier the issuing warp issues S(i + 1) = Q K(i + 1)^T and then
+    // P(i) V(i), so that the tensor core has the next scores ready when the workers come
+    // back from their copies.
+    if (warp == kIssuer) {
+        // ---- the issuing warp: the same barriers as the workers, one lane issues behind each ----
+        if (n > 0) {
+            cta_sync_or(false);
+            if ((tid & 31) == 0) {
+                tc_fence_after();
+                issue_qk(0);
             }
+            __syncwarp();
         }
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-        for (int j = 0; j < kAtcTile; ++j) {
-            s[j] = __fdividef(s[j], sqrt_d);
-            mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);   // four chains instead of one of 64
-        }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        const float mn = fmaxf(m, mx);
-        const float alpha = __expf(m - mn);
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int u = 0; u < kAtcTile / 8; ++u) {
-            uint32_t p[4];
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                const float e0 = __expf(s[8 * u + 2 * x] - mn), e1 = __expf(s[8 * u + 2 * x + 1] - mn);
-                sum4[x] += e0 + e1;
-                const __half2 h = __floats2half2_rn(e0, e1);
-                p[x] = *reinterpret_cast<const uint32_t*>(&h);
+        for (int i = 0; i < n; ++i) {
+            if (cta_sync_or(false)) break;
+            if ((tid & 31) == 0) {
+                tc_fence_after();
+                if (i + 1 < n) issue_qk((i & 1) ^ 1);
+                issue_pv(i & 1, i > 0);
             }
-            *reinterpret_cast<uint4*>(atc_smem + L::kP + u * (kAtcRows * 16) + tid * 16) = make_uint4(p[0], p[1], p[2], p[3]);
+            __syncwarp();
         }
-        l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-        m = mn;
-        fence_proxy_async_smem();
-        tc_fence_before();
-        ATC_STAMP(11 + 6 * i);
-        if (__syncthreads_or(!ok)) break;
-        if (tid == 0) {
+    } else {
+        if (n > 0) {
+#pragma unroll
+            for (int c = tid; c < kAtcRows * KU; c += kAtcWorkers) {
+                const int r = row0 + (c & (kAtcRows - 1));
+                const char* src = reinterpret_cast<const char*>(q) + (size_t)min(r, seq_len - 1) * D + (c >> 7) * 16;
+                cp_async_16(sbase + L::kQ + c * 16, src, r < seq_len ? 16 : 0);
+            }
+            load_kv(t_begin, 0);
+            cp_async_commit();
+            if (n > 1) load_kv(t_begin + 1, 1);
+            cp_async_commit();
+            cp_async_wait<1>();                 // Q and tile 0
+            fence_proxy_async_smem();           // ... visible to the tensor core's reads
+            tc_fence_before();
+            cta_sync_or(false);
+            spread_v(0);
+        }
+
+        for (int i = 0; i < n; ++i) {
+            const int buf = i & 1;
+            // ---- S(i) is ready; P(i - 1) V(i - 1) has completed: P and the output are ours ----
+            ok = mbar_wait(bar_s, (uint32_t)(i & 1), status) && ok;
+            if (i > 0) ok = mbar_wait(bar_o, (uint32_t)((i - 1) & 1), status) && ok;
             tc_fence_after();
+            float s[KH];                          // this thread's 32 keys; the other 32 only feed the maximum
+            float mx4[4];
+            {
+                float other[KH];
+                tmem_ld<KH>(tmem_row + KH * (half ^ 1), other);
 #pragma unroll
-            for (int j = 0; j < kAtcTile / 16; ++j)   // 16 keys (two key groups) per instruction
-                tc_mma<false>(tmem + kAtcTile,
-                              tc_desc(sbase + L::kP + j * 2 * (kAtcRows * 16), kAtcRows * 16, 128),
-                              tc_desc(sbase + L::kV + j * 2 * L::kVLbo, L::kVLbo, L::kVSbo),
-                              kAtcIdescPV<D>, j > 0);
-            tc_commit(bar_o);
+                for (int j = 0; j < 4; ++j) mx4[j] = other[j];
+#pragma unroll
+                for (int j = 4; j < KH; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], other[j]);
+            }
+            tmem_ld<KH>(tmem_row + KH * half, s);
+#pragma unroll
+            for (int j = 0; j < KH; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], s[j]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            const float mn2 = fmaxf(m2, mx * scale2);
+            const float alpha = ex2_approx(m2 - mn2);
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int u = 0; u < KH / 8; ++u) {
+                uint32_t p[4];
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const float e0 = ex2_approx(fmaf(s[8 * u + 2 * x], scale2, -mn2));
+                    const float e1 = ex2_approx(fmaf(s[8 * u + 2 * x + 1], scale2, -mn2));
+                    sum4[x] += e0 + e1;
+                    const __half2 h = __floats2half2_rn(e0, e1);
+                    p[x] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(atc_smem + L::kP + (half * (KH / 8) + u) * (kAtcRows * 16) + row * 16) =
+                    make_uint4(p[0], p[1], p[2], p[3]);
+            }
+            l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            m2 = mn2;
+            // ---- output *= alpha, unless no row of this warp saw a new maximum (alpha = 1 everywhere) ----
+            if (i > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) {
+#pragma unroll
+                for (int c = 0; c < DH / CH; ++c) {
+                    float acc[CH];
+                    tmem_ld<CH>(tmem_o + CH * c, acc);
+#pragma unroll
+                    for (int x = 0; x < CH; ++x) acc[x] *= alpha;
+                    tmem_st<CH>(tmem_o + CH * c, acc);
+                }
+                tmem_wait_st();
+            }
+            cp_async_wait<0>();                   // this thread's copies of tile i + 1
+            fence_proxy_async_smem();             // P(i), V(i + 1) as FP16 and K(i + 1): visible to the tensor core
+            tc_fence_before();
+            if (cta_sync_or(!ok)) break;
+            // tile i + 2's codes go where tile i's were: S(i) and the spread of V(i) are done with them
+            if (i + 2 < n) load_kv(t_begin + i + 2, buf);
+            cp_async_commit();
+            if (i + 1 < n) spread_v(buf ^ 1);     // P(i - 1) V(i - 1), the last reader of that half, has completed
         }
-        __syncwarp();
-        ATC_STAMP(12 + 6 * i);
-        ok = mbar_wait(bar_o, phase, status) && ok;
+        if (n > 0 && ok) ok = mbar_wait(bar_o, (uint32_t)((n - 1) & 1), status);
         tc_fence_after();
-        ATC_STAMP(13 + 6 * i);
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-            float pv[32];
-            tmem_ld32(tmem_row + kAtcTile + 32 * c, pv);
-#pragma unroll
-            for (int x = 0; x < 32; ++x) o[32 * c + x] = fmaf(o[32 * c + x], alpha, pv[x]);
-        }
-        phase ^= 1;
     }
     cp_async_wait<0>();
-    tc_fence_before();
-    __syncthreads();                          // operands and tensor memory are no longer read
 
-    ATC_STAMP(2);
-    // ---- partial result to shared memory, merge over the cluster ----
+    // ---- partial result to shared memory (the operands are no longer read), merge over the cluster ----
     float* mo = reinterpret_cast<float*>(atc_smem);
+    if (warp != kIssuer) {
 #pragma unroll
-    for (int c = 0; c < D; c += 4)
-        *reinterpret_cast<float4*>(mo + tid * L::kMergeStride + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
-    mo[L::kMergeM / 4 + tid] = m;
-    mo[L::kMergeM / 4 + kAtcRows + tid] = l;
-    ATC_STAMP(3);
+        for (int c = 0; c < DH / CH; ++c) {
+            float acc[CH];
+            if (n > 0) {
+                tmem_ld<CH>(tmem_o + CH * c, acc);
+            } else {
+#pragma unroll
+                for (int x = 0; x < CH; ++x) acc[x] = 0.f;
+            }
+#pragma unroll
+            for (int x = 0; x < CH; x += 4)
+                *reinterpret_cast<float4*>(mo + row * L::kMergeStride + DH * half + CH * c + x) =
+                    make_float4(acc[x], acc[x + 1], acc[x + 2], acc[x + 3]);
+        }
+        if (half == 0) mo[L::kMergeM / 4 + row] = m2;
+        mo[L::kMergeM / 4 + (1 + half) * kAtcRows + row] = l;
+    }
+    tc_fence_before();
     cluster_sync();
-    ATC_STAMP(4);
-    // Every CTA merges 128 / n_split rows.  First the rows' weights: thread r of the slice
-    // reads the n_split maxima and sums of its row (all loads in flight at once), and
-    // leaves e^(m_c - m) per CTA and the total sum in this CTA's own shared memory, past
-    // the part its peers read.
+    // Every CTA merges 128 / n_split rows: four columns per item, consecutive threads along
+    // a row (remote reads and global stores are contiguous runs).  A thread first reads the
+    // n_split maxima and sums of its row, then the n_split pieces of its item, four loads
+    // in flight at a time, and weighs them with 2^(m_c - m), CTAs in rank order.
     const int rows_per = kAtcRows / n_split;
     uint32_t peer[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) peer[c] = map_cluster(sbase, (uint32_t)min(c, n_split - 1));
-    float* weight = reinterpret_cast<float*>(atc_smem + L::kMergeBytes);   // [8][128], then the sums [128]
-    if (tid < rows_per) {
-        const int r = split * rows_per + tid;
-        float mc[8], lc[8];
+    constexpr int kGroups = D / 4;
+    for (int idx = tid; idx < rows_per * kGroups && warp != kIssuer; idx += kAtcWorkers) {
+        const int rl = idx / kGroups, g = idx % kGroups;
+        const int rr = split * rows_per + rl;             // row of the query block
+        float w[8], lc[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-            mc[c] = c < n_split ? ld_cluster_f32(peer[c] + L::kMergeM + r * 4) : -INFINITY;
-            lc[c] = c < n_split ? ld_cluster_f32(peer[c] + L::kMergeM + (kAtcRows + r) * 4) : 0.f;
+            w[c] = c < n_split ? ld_cluster_f32(peer[c] + L::kMergeM + rr * 4) : -INFINITY;
+            lc[c] = c < n_split ? ld_cluster_f32(peer[c] + L::kMergeM + (kAtcRows + rr) * 4) +
+                                      ld_cluster_f32(peer[c] + L::kMergeM + (2 * kAtcRows + rr) * 4)
+                                : 0.f;
         }
+        if (row0 + rr >= seq_len) continue;
         float mm = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) mm = fmaxf(mm, mc[c]);
+        for (int c = 0; c < 8; ++c) mm = fmaxf(mm, w[c]);
         float lsum = 0.f;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {            // CTAs in rank order: a fixed summation order
-            const float scale = expf(mc[c] - mm);   // a CTA without tiles: e^(-inf) = 0
-            lsum += lc[c] * scale;
-            weight[c * kAtcRows + tid] = scale;
+        for (int c = 0; c < 8; ++c) {
+            w[c] = ex2_approx(w[c] - mm);                 // a CTA without tiles: 2^(-inf) = 0
+            lsum += lc[c] * w[c];
         }
-        weight[8 * kAtcRows + tid] = lsum;
-    }
-    __syncthreads();
-    // Then the outputs, four columns per item and consecutive threads along a row (remote
-    // reads and global stores are contiguous runs); two items per thread at a time so that
-    // up to 16 remote 16-byte loads are in flight.
-    constexpr int kBatch = 2, kGroups = D / 4;
-    for (int base = 0; base < rows_per * kGroups; base += kBatch * kAtcThreads) {
-        float4 x[kBatch][8];
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int b = 0; b < kBatch; ++b) {
-            const int idx = base + b * kAtcThreads + tid;
-            const int rl = idx / kGroups, g = idx % kGroups;
-            const uint32_t off = (uint32_t)((split * rows_per + rl) * L::kMergeStride + 4 * g) * 4;
+        for (int c0 = 0; c0 < 8; c0 += 4) {               // four 16-byte remote loads in flight
+            float4 x[4];
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                x[b][c] = (c < n_split && rl < rows_per) ? ld_cluster_f32x4(peer[c] + off) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+            for (int c = 0; c < 4; ++c)
+                x[c] = c0 + c < n_split ? ld_cluster_f32x4(peer[c0 + c] + (uint32_t)(rr * L::kMergeStride + 4 * g) * 4)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int b = 0; b < kBatch; ++b) {
-            const int idx = base + b * kAtcThreads + tid;
-            const int rl = idx / kGroups, g = idx % kGroups;
-            const int row = row0 + split * rows_per + rl;
-            if (rl >= rows_per || row >= seq_len) continue;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const float w = weight[c * kAtcRows + rl];
-                acc.x += x[b][c].x * w;
-                acc.y += x[b][c].y * w;
-                acc.z += x[b][c].z * w;
-                acc.w += x[b][c].w * w;
+            for (int c = 0; c < 4; ++c) {
+                acc.x += x[c].x * w[c0 + c];
+                acc.y += x[c].y * w[c0 + c];
+                acc.z += x[c].z * w[c0 + c];
+                acc.w += x[c].w * w[c0 + c];
             }
-            const float lsum = weight[8 * kAtcRows + rl];
-            *reinterpret_cast<float4*>(out + (size_t)row * D + 4 * g) =
-                make_float4(__fdiv_rn(acc.x, lsum), __fdiv_rn(acc.y, lsum), __fdiv_rn(acc.z, lsum), __fdiv_rn(acc.w, lsum));
         }
+        *reinterpret_cast<float4*>(out + (size_t)(row0 + rr) * D + 4 * g) =
+            make_float4(__fdiv_rn(acc.x, lsum), __fdiv_rn(acc.y, lsum), __fdiv_rn(acc.z, lsum), __fdiv_rn(acc.w, lsum));
     }
-    ATC_STAMP(5);
     cluster_sync();                           // nobody leaves while a peer reads its memory
-    if (warp == 0) {
+    if (warp == kIssuer) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)L::kCols) : "memory");
     }
-    ATC_STAMP(6);
 }
 
 }  // namespace feather

@@ -38,7 +38,8 @@ namespace feather {
 //                    bulk-copy ring kernel with 6 x 32 KiB, 3 x 64 KiB or 12 x 16 KiB stages
 //   dot_pre_kb       KiB the dot ring kernel asks L2 for ahead of its stream-order wait
 //   attn_tc          attention with 32, 64 or 128 codes per row: 0 the register-fed mma.sync
-//                    kernel, 1 the tcgen05 kernel from 512 queries up, 2 the tcgen05 kernel always
+//                    kernel, 1 the tcgen05 kernel from 4096 / 2560 / 512 queries up, 2 the
+//                    tcgen05 kernel always
 struct Tuning {
     std::atomic<int> ring_pre_kb{128};
     std::atomic<int> rows_pre{1};
@@ -582,7 +583,7 @@ static int attention_launch(const uint32_t* q, const uint32_t* k, const uint32_t
 }
 
 // The tcgen05 kernel: 128 queries per CTA, the key tiles of a query block split over a
-// cluster of 1, 2, 4 or 8 CTAs so that about two CTAs per SM are in flight.
+// cluster of 1, 2, 4 or 8 CTAs, as many as still run in one wave of two CTAs per SM.
 template <int D>
 static int attention_tc_launch(const uint32_t* q, const uint32_t* k, const uint32_t* v, float* out,
                                long long seq_len, const DeviceInfo& dev, cudaStream_t s) {
@@ -595,7 +596,7 @@ static int attention_tc_launch(const uint32_t* q, const uint32_t* k, const uint3
     const long long blocks = (seq_len + kAtcRows - 1) / kAtcRows;
     const long long tiles = (seq_len + kAtcTile - 1) / kAtcTile;
     int splits = 1;
-    while (splits < 8 && blocks * splits < 2ll * dev.sm_count && 2 * splits <= tiles) splits <<= 1;
+    while (splits < 8 && blocks * splits * 2 <= 2ll * dev.sm_count && 2 * splits <= tiles) splits <<= 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)splits, (unsigned)blocks);
     cfg.blockDim = dim3(kAtcThreads);
@@ -616,8 +617,11 @@ template <int D>
 static int attention_any(const uint32_t* q, const uint32_t* k, const uint32_t* v, float* out,
                          long long seq_len, const DeviceInfo& dev, cudaStream_t s) {
     const int tc = g_tune.attn_tc.load(std::memory_order_relaxed);
+    // Measured on B200: below these lengths the register-fed kernel (16 queries per CTA, no
+    // cluster, no tensor-memory allocation) is as fast or faster.
+    constexpr long long kFrom = D >= 128 ? 512 : D >= 64 ? 2560 : 4096;
     // a query block is at most 65535 grid rows; cp.async moves 16-byte pieces
-    if (tc && (tc == 2 || seq_len >= 512) && seq_len <= 65535ll * kAtcRows && aligned(q, 16) &&
+    if (tc && (tc == 2 || seq_len >= kFrom) && seq_len <= 65535ll * kAtcRows && aligned(q, 16) &&
         aligned(k, 16) && aligned(v, 16))
         return attention_tc_launch<D>(q, k, v, out, seq_len, dev, s);
     return attention_launch<D>(q, k, v, out, seq_len, dev, s);
