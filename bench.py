@@ -57,6 +57,16 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s of a cuBLAS GEMM timed alone (the burst figure), measured or fallback."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
+
+
 _POLLER = r"""
 import sys, time
 import pynvml as nv
@@ -682,16 +692,28 @@ def run_ours(args) -> None:
                                             "GB/s": round(rb / ms_r / 1e6, 1),
                                             "frac_of_peak": round(rb / ms_r / 1e6 / peak, 4)}
         del relu_out
-        # packed-E5M2 attention (single head, non-causal), tensor-core bound: 4 * seq^2 * d flops
+        # packed-E5M2 attention (single head, non-causal), tensor-core bound: 4 * seq^2 * d flops,
+        # half of them (Q K^T) on E5M2 operands and half (P V) on FP16.  The library's choice
+        # (the tcgen05 kernel at these lengths) with the register-fed mma.sync kernel beside it.
         from feather_b200.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu as attn
-        for seq, d in ((4096, 128), (8192, 64)):
+        tpeak, tpeak_kind = measured_tensor_peak()
+        lib = fb._lib.load()
+        for seq, d in ((4096, 128), (8192, 64), (8192, 128)):
             gen.manual_seed(31)
             qkv = [fb.pack_fp8_tensor(torch.randn(seq, d, device=dev, generator=gen, dtype=torch.float16), "E5M2")
                    for _ in range(3)]
             o_attn = torch.empty(seq, d, dtype=torch.float32, device=dev)
             ms_a = time_calls(torch, lambda: attn(qkv[0], qkv[1], qkv[2], seq, d // 4, out=o_attn), 50, 5)
+            lib.feather_set_tuning(b"attn_tc=0")
+            try:
+                ms_old = time_calls(torch, lambda: attn(qkv[0], qkv[1], qkv[2], seq, d // 4, out=o_attn), 20, 3)
+            finally:
+                lib.feather_set_tuning(b"attn_tc=1")
+            tf = 4.0 * seq * seq * d / ms_a / 1e9
             extra[f"attention_e5m2_seq{seq}_d{d}"] = {
-                "us_per_call": round(ms_a * 1e3, 2), "TFLOP/s": round(4.0 * seq * seq * d / ms_a / 1e9, 1)}
+                "us_per_call": round(ms_a * 1e3, 2), "TFLOP/s": round(tf, 1),
+                "frac_of_bf16_peak": round(tf / tpeak, 4), "peak_kind": tpeak_kind,
+                "kernel": "tcgen05", "mma_sync_kernel_us": round(ms_old * 1e3, 2)}
         # encoder: fp16 16384^2 -> E5M2 (reads 2 B, writes 1 B per element)
         gen.manual_seed(9)
         src = torch.randn(M, N, device=dev, generator=gen, dtype=torch.float16)
