@@ -33,22 +33,27 @@
 //   2. reads its scores (tcgen05.ld 32x32b), runs the online softmax -- the maximum lives in
 //      the exponent's scale, m2 = max * log2(e) / sqrt(d), so a probability is one FMA and
 //      one ex2 -- and stores its FP16 probabilities as the A operand of the second product,
-//   3. rescales its half row of the output,
-//   4. sees its cp.async copies of tile i+1 land;
-// behind it the issuing warp issues S(i+1) (kind::f8f6f4: the tensor core reads the E5M2
-// codes themselves, d / 32 instructions) and then P(i) V(i) (kind::f16, 4 instructions),
-// each followed by a tcgen05.commit, while the workers
-//   5. start the copies of tile i+2 (K straight into the operand layout, V as stored) and
-//   6. spread the V codes of tile i+1 to FP16 (an E5M2 code is the high byte of an FP16
-//      number) in the layout the second product reads.
+//   3. rescales its half row of the output;
+// behind it one lane of the issuing warp issues S(i+1) (kind::f8f6f4: the tensor core reads
+// the E5M2 codes themselves, d / 32 instructions) and then P(i) V(i) (kind::f16, 4
+// instructions), each followed by a tcgen05.commit, and starts the copies of tile i+2:
+// two tensor-map copies (cp.async.bulk.tensor.2d), K into the swizzled operand layout and
+// V as stored, which count their bytes on the buffer's mbarrier; rows past seq_len arrive
+// as zeros.  The workers meanwhile
+//   4. wait for the codes of tile i+1 and spread its V to FP16 (an E5M2 code is the high
+//      byte of an FP16 number) in the layout the second product reads.
 // K codes, V codes and V as FP16 are double-buffered; P and S are not (their readers have
-// finished by the time they are written again, see the loop).
+// finished by the time they are written again, see the loop).  No worker thread touches
+// global memory inside the loop.
 //
-// Shared-memory operand layouts (no swizzle; 16-byte units; LBO / SBO of the matrix
-// descriptor):
-//   * Q, K (K-major, 1 byte per element) and P (K-major, FP16): [16-byte unit along the
-//     contraction][row][16 B]: rows are 16 B apart (an 8-row core matrix is 128 contiguous
-//     bytes, SBO = 128) and the units along the contraction are rows * 16 B apart (LBO);
+// Shared-memory operand layouts (16-byte units; LBO / SBO of the matrix descriptor):
+//   * Q, K (K-major, 1 byte per element): rows of d bytes as they are in global memory, the
+//     16-byte units of a row swizzled over d bytes (128-, 64- or 32-byte swizzle) by the
+//     tensor-map copy and un-swizzled by the tensor core; 8-row groups 8 d bytes apart
+//     (SBO), a step of 32 codes along the contraction is 32 bytes further along the row;
+//   * P (K-major FP16, no swizzle): [16-byte unit along the contraction][row][16 B]: rows are
+//     16 B apart (an 8-row core matrix is 128 contiguous bytes, SBO = 128) and the units
+//     along the contraction are 128 * 16 B apart (LBO);
 //   * V (MN-major FP16: the model dimension runs fastest, as V is stored): a core matrix
 //     is 8 keys x 8 columns (128 B, key rows 16 B apart); column groups follow 144 B apart
 //     (SBO; the odd 16 B keep the conversion's stores free of bank conflicts) and key
@@ -59,7 +64,7 @@
 // memory.  Shared memory per CTA is sized so that the CTAs resident on one SM never ask
 // for more than its 512 tensor-memory columns.
 #pragma once
-#include "gemv_mma.cuh"    // cp.async wrappers
+#include <cuda.h>           // CUtensorMap and its enumerations (types only: nothing of libcuda is linked)
 #include "gemv_ring.cuh"   // mbarrier wrappers, bounded waits
 
 namespace feather {
@@ -71,9 +76,9 @@ constexpr int kAtcTile = 64;       // keys per step (the reference's tile, atten
 
 template <int D>
 struct AtcLayout {
-    static constexpr int kQ = 0;                               // [D/16][128][16 B]
+    static constexpr int kQ = 0;                               // [128][D] codes, 16-byte units swizzled over D bytes
     static constexpr int kQBytes = kAtcRows * D;
-    static constexpr int kK = kQ + kQBytes;                    // 2 x [D/16][64][16 B]
+    static constexpr int kK = kQ + kQBytes;                    // 2 x [64][D], swizzled like Q
     static constexpr int kKBytes = kAtcTile * D;
     static constexpr int kVraw = kK + 2 * kKBytes;             // 2 x [64][D] codes
     static constexpr int kV = kVraw + 2 * kKBytes;             // 2 x FP16, see above
@@ -82,8 +87,12 @@ struct AtcLayout {
     static constexpr int kVBytes = (kAtcTile / 8) * kVLbo;
     static constexpr int kP = kV + 2 * kVBytes;                // [8][128][16 B] FP16
     static constexpr int kPBytes = kAtcRows * kAtcTile * 2;
-    static constexpr int kBar = kP + kPBytes;                  // two mbarriers, tensor-memory base
-    static constexpr int kTileBytes = kBar + 32;
+    static constexpr int kBar = kP + kPBytes;                  // mbarriers S, P V; tensor-memory base; mbarriers tile codes x 2
+    static constexpr int kTileBytes = kBar + 64;
+    // operand rows of D bytes are swizzled over D bytes: descriptor layout type and the
+    // 8-row group stride (SBO); the tensor maps that fill them use the same swizzle
+    static constexpr uint32_t kSwizzle = D == 128 ? 2u : D == 64 ? 4u : 6u;   // 128 B, 64 B, 32 B
+    static constexpr uint32_t kGroup = 8 * D;
     // the merge reuses the operand space: O as [128][D + 4] floats (the odd 16 B keep a
     // thread-per-row's 16-byte stores free of bank conflicts), then m[128] and the two threads' l[2][128]
     static constexpr int kMergeStride = D + 4;
@@ -109,6 +118,19 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 __device__ __forceinline__ uint64_t tc_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(sbo >> 4) << 32) |
            (1ull << 46);
+}
+// The same for a K-major operand whose rows are swizzled (layout type in bits 61-63: 2, 4, 6
+// for 128, 64, 32 bytes): the leading offset is not used (1), `group` is the stride between
+// 8-row groups, and a step along the contraction inside a row adds its bytes to addr.
+__device__ __forceinline__ uint64_t tc_desc_swizzled(uint32_t addr, uint32_t group, uint32_t layout) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(group >> 4) << 32) | (1ull << 46) |
+           ((uint64_t)layout << 61);
+}
+// One box of a 2-D tensor map (x: bytes along a row, y: row) into this CTA's shared memory,
+// completion counted in bytes on `bar`.  x must be a multiple of 16.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 // Instruction descriptors: FP32 accumulator (bits 4-5 = 1), operand formats (bits 7-9 and
 // 10-12: E5M2 = 1 for kind::f8f6f4, FP16 = 0 for kind::f16), B MN-major (bit 16), N / 8 (bits
@@ -223,16 +245,51 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
     return x;
 }
 
+// Host side: a row-major matrix of `rows` x d bytes as a 2-D tensor map with boxes of
+// d bytes x box_rows rows, rows swizzled over d bytes (d = 32, 64, 128) or not; elements
+// outside the matrix read as zeros.  False if the driver does not offer the encoder or
+// refuses the arguments (base 16-byte aligned, d a multiple of 16).
+typedef CUresult (*AtcEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline AtcEncodeTiled atc_encoder() {
+    static const AtcEncodeTiled fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult found;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &found) != cudaSuccess ||
+            found != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<AtcEncodeTiled>(p);
+    }();
+    return fn;
+}
+inline bool atc_make_map(CUtensorMap* map, const void* base, int d, long long rows, int box_rows, bool swizzled) {
+    const AtcEncodeTiled encode = atc_encoder();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)d};
+    const cuuint32_t box[2] = {(cuuint32_t)d, (cuuint32_t)box_rows};
+    const cuuint32_t steps[2] = {1, 1};
+    const CUtensorMapSwizzle sw = !swizzled ? CU_TENSOR_MAP_SWIZZLE_NONE
+                                  : d == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : d == 64  ? CU_TENSOR_MAP_SWIZZLE_64B
+                                             : CU_TENSOR_MAP_SWIZZLE_32B;
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, steps,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // D = codes per row: 32, 64 or 128.  Grid (splits, query blocks), cluster (splits, 1, 1),
-// 288 threads, AtcLayout<D>::kBytes of dynamic shared memory.  q, k, v 16-byte aligned.
+// 288 threads, AtcLayout<D>::kBytes of dynamic shared memory.  map_q, map_k, map_v: the
+// seq_len x D byte matrices as 2-D tensor maps with boxes of 128, 64 and 64 rows, Q and K
+// swizzled over D bytes, V not (atc_make_map below); rows past seq_len read as zeros.
 template <int D>
 __global__ void __launch_bounds__(kAtcThreads, 2)
-attention_tc_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict__ k,
-                    const uint32_t* __restrict__ v, float* __restrict__ out, int seq_len,
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, float* __restrict__ out, int seq_len,
                     unsigned int* status) {
-    extern __shared__ __align__(128) unsigned char atc_smem[];
+    extern __shared__ __align__(1024) unsigned char atc_smem[];
     using L = AtcLayout<D>;
-    constexpr int KU = D / 16;                    // 16-byte units per row of codes
     constexpr int DH = D / 2;                     // output columns per thread
     constexpr int KH = kAtcTile / 2;              // keys per thread
     const int tid = threadIdx.x, warp = tid >> 5;
@@ -241,11 +298,17 @@ attention_tc_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict__
     const int n_split = (int)gridDim.x, split = (int)blockIdx.x;
     const int row0 = (int)blockIdx.y * kAtcRows;
     const uint32_t sbase = smem_u32(atc_smem);
-    const uint32_t bar_s = sbase + L::kBar, bar_o = bar_s + 8;
+    const uint32_t bar_s = sbase + L::kBar, bar_o = bar_s + 8, bar_kv = bar_s + 32;   // bar_kv + 8: second buffer
+    if (sbase & 1023u) {                          // the swizzled operands want 1 KiB alignment (every CTA alike)
+        if (tid == 0) atomicOr(status, 2u);
+        return;
+    }
 
     if (tid == 0) {
         mbar_init(bar_s, 1);
         mbar_init(bar_o, 1);
+        mbar_init(bar_kv, 1);
+        mbar_init(bar_kv + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     constexpr int kIssuer = kAtcWorkers / 32;     // the issuing warp: it also owns the tensor-memory allocation
@@ -267,33 +330,22 @@ attention_tc_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict__
     const int t_begin = min(split * per, tiles);
     const int n = min(tiles, t_begin + per) - t_begin;
 
-    // Copies of one key tile, 16 bytes per cp.async and consecutive threads along a row of
-    // codes (whole 128-byte lines of global memory).  K: unit (row, u) lands at
-    // (u * 64 + row) * 16, the operand layout; V: rows as they are.  A tile that reaches
-    // past seq_len gets zeros there.
-    auto load_kv = [&](int tile, int buf) {
-        const int key0 = tile * kAtcTile;
-        const bool whole = key0 + kAtcTile <= seq_len;
-        const char* ksrc = reinterpret_cast<const char*>(k) + (size_t)key0 * D;
-        const char* vsrc = reinterpret_cast<const char*>(v) + (size_t)key0 * D;
-        const uint32_t kdst = sbase + L::kK + buf * L::kKBytes, vdst = sbase + L::kVraw + buf * L::kKBytes;
-#pragma unroll
-        for (int c = tid; c < kAtcTile * KU; c += kAtcWorkers) {
-            const int r = c / KU, u = c % KU;
-            const int bytes = (whole || key0 + r < seq_len) ? 16 : 0;
-            const int from = bytes ? c * 16 : 0;
-            cp_async_16(kdst + (u * kAtcTile + r) * 16, ksrc + from, bytes);
-            cp_async_16(vdst + c * 16, vsrc + from, bytes);
-        }
+    // One lane of the issuing warp does everything asynchronous.  The codes of key tile t
+    // (K into the swizzled operand layout, V as stored) arrive by two tensor-map copies that
+    // count their bytes on the buffer's mbarrier; its phase for tile t is t / 2.
+    auto load_kv = [&](int t, int buf, uint32_t more_bytes = 0) {
+        mbar_arrive_expect_tx(bar_kv + 8 * buf, 2 * L::kKBytes + more_bytes);
+        tma_load_2d(sbase + L::kK + buf * L::kKBytes, &map_k, 0, (t_begin + t) * kAtcTile, bar_kv + 8 * buf);
+        tma_load_2d(sbase + L::kVraw + buf * L::kKBytes, &map_v, 0, (t_begin + t) * kAtcTile, bar_kv + 8 * buf);
     };
-    // One thread issues the products: S = Q K^T of a tile (d / 32 instructions of 32 codes,
-    // two 16-byte units, each) and P V (4 instructions of 16 keys, two key groups, each).
+    // The products: S = Q K^T of a tile (d / 32 instructions of 32 codes each: 32 bytes further
+    // along the swizzled rows) and P V (4 instructions of 16 keys, two key groups, each).
     auto issue_qk = [&](int buf) {
 #pragma unroll
         for (int j = 0; j < D / 32; ++j)
             tc_mma<true>(tmem,
-                         tc_desc(sbase + L::kQ + j * 2 * (kAtcRows * 16), kAtcRows * 16, 128),
-                         tc_desc(sbase + L::kK + buf * L::kKBytes + j * 2 * (kAtcTile * 16), kAtcTile * 16, 128),
+                         tc_desc_swizzled(sbase + L::kQ + j * 32, L::kGroup, L::kSwizzle),
+                         tc_desc_swizzled(sbase + L::kK + buf * L::kKBytes + j * 32, L::kGroup, L::kSwizzle),
                          kAtcIdescQK, j > 0);
         tc_commit(bar_s);
     };
@@ -339,40 +391,33 @@ attention_tc_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict__
     // P(i) V(i), so that the tensor core has the next scores ready when the workers come
     // back from their copies.
     if (warp == kIssuer) {
-        // ---- the issuing warp: the same barriers as the workers, one lane issues behind each ----
-        if (n > 0) {
-            cta_sync_or(false);
-            if ((tid & 31) == 0) {
-                tc_fence_after();
-                issue_qk(0);
-            }
-            __syncwarp();
+        // ---- the issuing warp: the workers' tile barriers, one lane issues behind each ----
+        bool okk = true;
+        if (n > 0 && (tid & 31) == 0) {
+            load_kv(0, 0, L::kQBytes);                       // Q rides on the first buffer's first phase
+            tma_load_2d(sbase + L::kQ, &map_q, 0, row0, bar_kv);
+            if (n > 1) load_kv(1, 1);
+            okk = mbar_wait(bar_kv, 0, status);
+            issue_qk(0);
         }
+        __syncwarp();
         for (int i = 0; i < n; ++i) {
             if (cta_sync_or(false)) break;
             if ((tid & 31) == 0) {
                 tc_fence_after();
-                if (i + 1 < n) issue_qk((i & 1) ^ 1);
+                if (i + 1 < n) {
+                    okk = mbar_wait(bar_kv + 8 * ((i + 1) & 1), (uint32_t)(((i + 1) >> 1) & 1), status) && okk;
+                    issue_qk((i + 1) & 1);
+                }
                 issue_pv(i & 1, i > 0);
+                // tile i + 2's codes go where tile i's were: S(i) and the spread of V(i) are done with them
+                if (i + 2 < n) load_kv(i + 2, i & 1);
             }
             __syncwarp();
         }
     } else {
         if (n > 0) {
-#pragma unroll
-            for (int c = tid; c < kAtcRows * KU; c += kAtcWorkers) {
-                const int r = row0 + (c & (kAtcRows - 1));
-                const char* src = reinterpret_cast<const char*>(q) + (size_t)min(r, seq_len - 1) * D + (c >> 7) * 16;
-                cp_async_16(sbase + L::kQ + c * 16, src, r < seq_len ? 16 : 0);
-            }
-            load_kv(t_begin, 0);
-            cp_async_commit();
-            if (n > 1) load_kv(t_begin + 1, 1);
-            cp_async_commit();
-            cp_async_wait<1>();                 // Q and tile 0
-            fence_proxy_async_smem();           // ... visible to the tensor core's reads
-            tc_fence_before();
-            cta_sync_or(false);
+            ok = mbar_wait(bar_kv, 0, status);
             spread_v(0);
         }
 
@@ -427,20 +472,17 @@ attention_tc_kernel(const uint32_t* __restrict__ q, const uint32_t* __restrict__
                 }
                 tmem_wait_st();
             }
-            cp_async_wait<0>();                   // this thread's copies of tile i + 1
-            fence_proxy_async_smem();             // P(i), V(i + 1) as FP16 and K(i + 1): visible to the tensor core
+            fence_proxy_async_smem();             // P(i) and V(i + 1) as FP16: visible to the tensor core
             tc_fence_before();
             if (cta_sync_or(!ok)) break;
-            // tile i + 2's codes go where tile i's were: S(i) and the spread of V(i) are done with them
-            if (i + 2 < n) load_kv(t_begin + i + 2, buf);
-            cp_async_commit();
-            if (i + 1 < n) spread_v(buf ^ 1);     // P(i - 1) V(i - 1), the last reader of that half, has completed
+            if (i + 1 < n) {                      // P(i - 1) V(i - 1), the last reader of that half, has completed
+                ok = mbar_wait(bar_kv + 8 * (buf ^ 1), (uint32_t)(((i + 1) >> 1) & 1), status) && ok;
+                spread_v(buf ^ 1);
+            }
         }
         if (n > 0 && ok) ok = mbar_wait(bar_o, (uint32_t)((n - 1) & 1), status);
         tc_fence_after();
     }
-    cp_async_wait<0>();
-
     // ---- partial result to shared memory (the operands are no longer read), merge over the cluster ----
     float* mo = reinterpret_cast<float*>(atc_smem);
     if (warp != kIssuer) {

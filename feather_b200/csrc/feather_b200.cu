@@ -609,7 +609,11 @@ static int attention_tc_launch(const uint32_t* q, const uint32_t* k, const uint3
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, q, k, v, out, (int)seq_len, status);
+    CUtensorMap map_q, map_k, map_v;
+    if (!atc_make_map(&map_q, q, D, seq_len, kAtcRows, true) || !atc_make_map(&map_k, k, D, seq_len, kAtcTile, true) ||
+        !atc_make_map(&map_v, v, D, seq_len, kAtcTile, false))
+        return attention_launch<D>(q, k, v, out, seq_len, dev, s);   // no encoder in this driver: the other kernel
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, map_q, map_k, map_v, out, (int)seq_len, status);
     return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
 }
 
