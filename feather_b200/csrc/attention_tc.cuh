@@ -284,7 +284,7 @@ inline bool atc_make_map(CUtensorMap* map, const void* base, int d, long long ro
 // seq_len x D byte matrices as 2-D tensor maps with boxes of 128, 64 and 64 rows, Q and K
 // swizzled over D bytes, V not (atc_make_map below); rows past seq_len read as zeros.
 template <int D>
-__global__ void __launch_bounds__(kAtcThreads, 2)
+__global__ void __launch_bounds__(kAtcThreads, D > 64 ? 2 : 3)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, float* __restrict__ out, int seq_len,
                     unsigned int* status) {
@@ -304,26 +304,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         return;
     }
 
-    if (tid == 0) {
-        mbar_init(bar_s, 1);
-        mbar_init(bar_o, 1);
-        mbar_init(bar_kv, 1);
-        mbar_init(bar_kv + 8, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    constexpr int kIssuer = kAtcWorkers / 32;     // the issuing warp: it also owns the tensor-memory allocation
-    if (warp == kIssuer) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(sbase + L::kBar + 16), "r"((uint32_t)L::kCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(atc_smem + L::kBar + 16);
-    // a warp reaches the 32 lanes of its quarter: warps w and w + 4 share lanes 32 (w % 4) ..
-    const uint32_t tmem_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-
     // this CTA's key tiles: a contiguous range
     const int tiles = (seq_len + kAtcTile - 1) / kAtcTile;
     const int per = (tiles + n_split - 1) / n_split;
@@ -338,6 +318,32 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tma_load_2d(sbase + L::kK + buf * L::kKBytes, &map_k, 0, (t_begin + t) * kAtcTile, bar_kv + 8 * buf);
         tma_load_2d(sbase + L::kVraw + buf * L::kKBytes, &map_v, 0, (t_begin + t) * kAtcTile, bar_kv + 8 * buf);
     };
+    constexpr int kIssuer = kAtcWorkers / 32;     // the issuing warp: it also owns the tensor-memory allocation
+    if (warp == kIssuer) {
+        if ((tid & 31) == 0) {
+            mbar_init(bar_s, 1);
+            mbar_init(bar_o, 1);
+            mbar_init(bar_kv, 1);
+            mbar_init(bar_kv + 8, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            if (n > 0) {                          // the first copies leave before anything else is set up
+                load_kv(0, 0, L::kQBytes);        // Q rides on the first buffer's first phase
+                tma_load_2d(sbase + L::kQ, &map_q, 0, row0, bar_kv);
+                if (n > 1) load_kv(1, 1);
+            }
+        }
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(sbase + L::kBar + 16), "r"((uint32_t)L::kCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(atc_smem + L::kBar + 16);
+    // a warp reaches the 32 lanes of its quarter: warps w and w + 4 share lanes 32 (w % 4) ..
+    const uint32_t tmem_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+
     // The products: S = Q K^T of a tile (d / 32 instructions of 32 codes each: 32 bytes further
     // along the swizzled rows) and P V (4 instructions of 16 keys, two key groups, each).
     auto issue_qk = [&](int buf) {
@@ -394,9 +400,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         // ---- the issuing warp: the workers' tile barriers, one lane issues behind each ----
         bool okk = true;
         if (n > 0 && (tid & 31) == 0) {
-            load_kv(0, 0, L::kQBytes);                       // Q rides on the first buffer's first phase
-            tma_load_2d(sbase + L::kQ, &map_q, 0, row0, bar_kv);
-            if (n > 1) load_kv(1, 1);
             okk = mbar_wait(bar_kv, 0, status);
             issue_qk(0);
         }
@@ -505,16 +508,29 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
     tc_fence_before();
     cluster_sync();
-    // Every CTA merges 128 / n_split rows: four columns per item, consecutive threads along
+    // Every CTA merges its share of the 128 rows (128 / n_split, rounded up): four columns per item, consecutive threads along
     // a row (remote reads and global stores are contiguous runs).  A thread first reads the
     // n_split maxima and sums of its row, then the n_split pieces of its item, four loads
     // in flight at a time, and weighs them with 2^(m_c - m), CTAs in rank order.
-    const int rows_per = kAtcRows / n_split;
+    const int rows_per = (kAtcRows + n_split - 1) / n_split;          // the last CTA may own fewer
+    const int rows_here = max(0, min(rows_per, kAtcRows - split * rows_per));
     uint32_t peer[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c) peer[c] = map_cluster(sbase, (uint32_t)min(c, n_split - 1));
     constexpr int kGroups = D / 4;
-    for (int idx = tid; idx < rows_per * kGroups && warp != kIssuer; idx += kAtcWorkers) {
+    if (n_split == 1) {
+        // nothing to merge: this CTA's own rows, plain shared-memory loads
+        const float* mo_l = mo + L::kMergeM / 4 + kAtcRows;
+        for (int idx = tid; idx < kAtcRows * kGroups && warp != kIssuer; idx += kAtcWorkers) {
+            const int rr = idx / kGroups, g = idx % kGroups;
+            if (row0 + rr >= seq_len) break;
+            const float lsum = mo_l[rr] + mo_l[kAtcRows + rr];
+            const float4 x = *reinterpret_cast<const float4*>(mo + rr * L::kMergeStride + 4 * g);
+            *reinterpret_cast<float4*>(out + (size_t)(row0 + rr) * D + 4 * g) =
+                make_float4(__fdiv_rn(x.x, lsum), __fdiv_rn(x.y, lsum), __fdiv_rn(x.z, lsum), __fdiv_rn(x.w, lsum));
+        }
+    }
+    for (int idx = tid; idx < rows_here * kGroups && warp != kIssuer && n_split > 1; idx += kAtcWorkers) {
         const int rl = idx / kGroups, g = idx % kGroups;
         const int rr = split * rows_per + rl;             // row of the query block
         float w[8], lc[8];

@@ -583,7 +583,7 @@ static int attention_launch(const uint32_t* q, const uint32_t* k, const uint32_t
 }
 
 // The tcgen05 kernel: 128 queries per CTA, the key tiles of a query block split over a
-// cluster of 1, 2, 4 or 8 CTAs, as many as still run in one wave of two CTAs per SM.
+// cluster of 1 .. 8 CTAs.
 template <int D>
 static int attention_tc_launch(const uint32_t* q, const uint32_t* k, const uint32_t* v, float* out,
                                long long seq_len, const DeviceInfo& dev, cudaStream_t s) {
@@ -595,8 +595,13 @@ static int attention_tc_launch(const uint32_t* q, const uint32_t* k, const uint3
     if (int st = status_word(&status)) return st;
     const long long blocks = (seq_len + kAtcRows - 1) / kAtcRows;
     const long long tiles = (seq_len + kAtcTile - 1) / kAtcTile;
-    int splits = 1;
-    while (splits < 8 && blocks * splits * 2 <= 2ll * dev.sm_count && 2 * splits <= tiles) splits <<= 1;
+    // as many CTAs per query block as still run in one wave (2 CTAs per SM with rows of 128
+    // codes, 3 with narrower ones), at most 8 (a portable cluster) and at least 2 tiles each
+    const long long per_sm = D > 64 ? 2 : 3;
+    long long splits = per_sm * dev.sm_count / blocks;
+    if (splits > 8) splits = 8;
+    if (splits > tiles / 2) splits = tiles / 2;
+    if (splits < 1) splits = 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)splits, (unsigned)blocks);
     cfg.blockDim = dim3(kAtcThreads);
