@@ -509,9 +509,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     tc_fence_before();
     cluster_sync();
     // Every CTA merges its share of the 128 rows (128 / n_split, rounded up): four columns per item, consecutive threads along
-    // a row (remote reads and global stores are contiguous runs).  A thread first reads the
-    // n_split maxima and sums of its row, then the n_split pieces of its item, four loads
-    // in flight at a time, and weighs them with 2^(m_c - m), CTAs in rank order.
+    // a row (remote reads and global stores are contiguous runs).  A thread reads the
+    // n_split maxima and sums of its row and the n_split pieces of its item and weighs
+    // them with 2^(m_c - m), CTAs in rank order.
     const int rows_per = (kAtcRows + n_split - 1) / n_split;          // the last CTA may own fewer
     const int rows_here = max(0, min(rows_per, kAtcRows - split * rows_per));
     uint32_t peer[8];
@@ -533,39 +533,36 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     for (int idx = tid; idx < rows_here * kGroups && warp != kIssuer && n_split > 1; idx += kAtcWorkers) {
         const int rl = idx / kGroups, g = idx % kGroups;
         const int rr = split * rows_per + rl;             // row of the query block
-        float w[8], lc[8];
+        // every remote load of the item leaves before the first is used: one round trip
+        float w[8], la[8], lb[8];
+        float4 x[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-            w[c] = c < n_split ? ld_cluster_f32(peer[c] + L::kMergeM + rr * 4) : -INFINITY;
-            lc[c] = c < n_split ? ld_cluster_f32(peer[c] + L::kMergeM + (kAtcRows + rr) * 4) +
-                                      ld_cluster_f32(peer[c] + L::kMergeM + (2 * kAtcRows + rr) * 4)
-                                : 0.f;
+            if (c < n_split) {
+                w[c] = ld_cluster_f32(peer[c] + L::kMergeM + rr * 4);
+                la[c] = ld_cluster_f32(peer[c] + L::kMergeM + (kAtcRows + rr) * 4);
+                lb[c] = ld_cluster_f32(peer[c] + L::kMergeM + (2 * kAtcRows + rr) * 4);
+                x[c] = ld_cluster_f32x4(peer[c] + (uint32_t)(rr * L::kMergeStride + 4 * g) * 4);
+            } else {
+                w[c] = -INFINITY;
+                la[c] = lb[c] = 0.f;
+                x[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
         if (row0 + rr >= seq_len) continue;
         float mm = -INFINITY;
 #pragma unroll
         for (int c = 0; c < 8; ++c) mm = fmaxf(mm, w[c]);
         float lsum = 0.f;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            w[c] = ex2_approx(w[c] - mm);                 // a CTA without tiles: 2^(-inf) = 0
-            lsum += lc[c] * w[c];
-        }
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int c0 = 0; c0 < 8; c0 += 4) {               // four 16-byte remote loads in flight
-            float4 x[4];
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                x[c] = c0 + c < n_split ? ld_cluster_f32x4(peer[c0 + c] + (uint32_t)(rr * L::kMergeStride + 4 * g) * 4)
-                                        : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                acc.x += x[c].x * w[c0 + c];
-                acc.y += x[c].y * w[c0 + c];
-                acc.z += x[c].z * w[c0 + c];
-                acc.w += x[c].w * w[c0 + c];
-            }
+        for (int c = 0; c < 8; ++c) {
+            const float wc = ex2_approx(w[c] - mm);       // a CTA without tiles: 2^(-inf) = 0
+            lsum += (la[c] + lb[c]) * wc;
+            acc.x += x[c].x * wc;
+            acc.y += x[c].y * wc;
+            acc.z += x[c].z * wc;
+            acc.w += x[c].w * wc;
         }
         *reinterpret_cast<float4*>(out + (size_t)(row0 + rr) * D + 4 * g) =
             make_float4(__fdiv_rn(acc.x, lsum), __fdiv_rn(acc.y, lsum), __fdiv_rn(acc.z, lsum), __fdiv_rn(acc.w, lsum));

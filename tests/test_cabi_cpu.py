@@ -105,6 +105,9 @@ def test_host_only_entry_points_of_the_newer_surface(lib):
     assert lib.feather_set_tuning(b"ring_pre_kb=128, ring_pre_kb_e4m3=-1") == 0
     assert lib.feather_set_tuning(b"no_such_knob=1") == -1
     assert lib.feather_set_tuning(b"dot_unroll=3") == -1
+    assert lib.feather_set_tuning(b"attn_tc=0") == 0 and lib.feather_set_tuning(b"attn_tc=2") == 0
+    assert lib.feather_set_tuning(b"attn_tc=3") == -1
+    assert lib.feather_set_tuning(b"attn_tc=1") == 0
     assert lib.feather_set_tuning(b"ring_pre_kb") == -1
     assert lib.feather_set_tuning(None) == -1
     assert lib.feather_debug_bounds() in (0, 1)
