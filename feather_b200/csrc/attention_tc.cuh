@@ -91,8 +91,12 @@ struct AtcLayout {
     static constexpr int kTileBytes = kBar + 64;
     // operand rows of D bytes are swizzled over D bytes: descriptor layout type and the
     // 8-row group stride (SBO); the tensor maps that fill them use the same swizzle
-    static constexpr uint32_t kSwizzle = D == 128 ? 2u : D == 64 ? 4u : 6u;   // 128 B, 64 B, 32 B
-    static constexpr uint32_t kGroup = 8 * D;
+    // Rows wider than 128 bytes are held as D / 128 column segments of 128 bytes, one
+    // swizzled [rows][128 B] region after the other.
+    static constexpr int kSeg = D < 128 ? D : 128;             // bytes of a row per segment
+    static constexpr int kSegs = D / kSeg;
+    static constexpr uint32_t kSwizzle = kSeg == 128 ? 2u : kSeg == 64 ? 4u : 6u;   // 128 B, 64 B, 32 B
+    static constexpr uint32_t kGroup = 8 * kSeg;
     // the merge reuses the operand space: O as [128][D + 4] floats (the odd 16 B keep a
     // thread-per-row's 16-byte stores free of bank conflicts), then m[128] and the two threads' l[2][128]
     static constexpr int kMergeStride = D + 4;
@@ -100,7 +104,7 @@ struct AtcLayout {
     static constexpr int kMergeBytes = kMergeM + 3 * kAtcRows * 4;
     static constexpr int kWeightBytes = 0;
     static_assert(kMergeBytes + kWeightBytes <= kBar, "the merge buffers must not reach the barriers");
-    static constexpr int kCols = D > 64 ? 256 : 128;           // tensor-memory columns: 64 (S) + D (P V)
+    static constexpr int kCols = D > 128 ? 512 : D > 64 ? 256 : 128;   // tensor-memory columns: 64 (S) + D (P V)
     // at most 512 / kCols CTAs of this kernel per SM: ask for more than 1 / (that + 1) of 227 KiB
     static constexpr int kMinBytes = (227 * 1024) / (512 / kCols + 1) + 1024;
     static constexpr int kBytes = kTileBytes > kMinBytes ? kTileBytes : kMinBytes;
@@ -246,7 +250,8 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
 }
 
 // Host side: a row-major matrix of `rows` x d bytes as a 2-D tensor map with boxes of
-// d bytes x box_rows rows, rows swizzled over d bytes (d = 32, 64, 128) or not; elements
+// d bytes x box_rows rows (swizzled: at most 128 bytes wide, rows swizzled over 32, 64 or
+// 128 bytes; wider rows are fetched as 128-byte column segments) or not swizzled; elements
 // outside the matrix read as zeros.  False if the driver does not offer the encoder or
 // refuses the arguments (base 16-byte aligned, d a multiple of 16).
 typedef CUresult (*AtcEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -264,14 +269,15 @@ inline AtcEncodeTiled atc_encoder() {
     return fn;
 }
 inline bool atc_make_map(CUtensorMap* map, const void* base, int d, long long rows, int box_rows, bool swizzled) {
+    const int box_bytes = swizzled && d > 128 ? 128 : d;   // swizzled boxes are at most one 128-byte segment wide
     const AtcEncodeTiled encode = atc_encoder();
     if (!encode) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)d};
-    const cuuint32_t box[2] = {(cuuint32_t)d, (cuuint32_t)box_rows};
+    const cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
     const cuuint32_t steps[2] = {1, 1};
     const CUtensorMapSwizzle sw = !swizzled ? CU_TENSOR_MAP_SWIZZLE_NONE
-                                  : d == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : d >= 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                                   : d == 64  ? CU_TENSOR_MAP_SWIZZLE_64B
                                              : CU_TENSOR_MAP_SWIZZLE_32B;
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, steps,
@@ -279,12 +285,12 @@ inline bool atc_make_map(CUtensorMap* map, const void* base, int d, long long ro
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// D = codes per row: 32, 64 or 128.  Grid (splits, query blocks), cluster (splits, 1, 1),
+// D = codes per row: 32, 64, 128 or 256.  Grid (splits, query blocks), cluster (splits, 1, 1),
 // 288 threads, AtcLayout<D>::kBytes of dynamic shared memory.  map_q, map_k, map_v: the
 // seq_len x D byte matrices as 2-D tensor maps with boxes of 128, 64 and 64 rows, Q and K
 // swizzled over D bytes, V not (atc_make_map below); rows past seq_len read as zeros.
 template <int D>
-__global__ void __launch_bounds__(kAtcThreads, D > 64 ? 2 : 3)
+__global__ void __launch_bounds__(kAtcThreads, D > 128 ? 1 : D > 64 ? 2 : 3)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, float* __restrict__ out, int seq_len,
                     unsigned int* status) {
@@ -315,7 +321,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // count their bytes on the buffer's mbarrier; its phase for tile t is t / 2.
     auto load_kv = [&](int t, int buf, uint32_t more_bytes = 0) {
         mbar_arrive_expect_tx(bar_kv + 8 * buf, 2 * L::kKBytes + more_bytes);
-        tma_load_2d(sbase + L::kK + buf * L::kKBytes, &map_k, 0, (t_begin + t) * kAtcTile, bar_kv + 8 * buf);
+#pragma unroll
+        for (int g = 0; g < L::kSegs; ++g)
+            tma_load_2d(sbase + L::kK + buf * L::kKBytes + g * (kAtcTile * L::kSeg), &map_k, g * L::kSeg,
+                        (t_begin + t) * kAtcTile, bar_kv + 8 * buf);
         tma_load_2d(sbase + L::kVraw + buf * L::kKBytes, &map_v, 0, (t_begin + t) * kAtcTile, bar_kv + 8 * buf);
     };
     constexpr int kIssuer = kAtcWorkers / 32;     // the issuing warp: it also owns the tensor-memory allocation
@@ -328,7 +337,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             if (n > 0) {                          // the first copies leave before anything else is set up
                 load_kv(0, 0, L::kQBytes);        // Q rides on the first buffer's first phase
-                tma_load_2d(sbase + L::kQ, &map_q, 0, row0, bar_kv);
+#pragma unroll
+                for (int g = 0; g < L::kSegs; ++g)
+                    tma_load_2d(sbase + L::kQ + g * (kAtcRows * L::kSeg), &map_q, g * L::kSeg, row0, bar_kv);
                 if (n > 1) load_kv(1, 1);
             }
         }
@@ -348,11 +359,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // along the swizzled rows) and P V (4 instructions of 16 keys, two key groups, each).
     auto issue_qk = [&](int buf) {
 #pragma unroll
-        for (int j = 0; j < D / 32; ++j)
+        for (int j = 0; j < D / 32; ++j) {
+            constexpr int kPer = L::kSeg / 32;    // steps per column segment
             tc_mma<true>(tmem,
-                         tc_desc_swizzled(sbase + L::kQ + j * 32, L::kGroup, L::kSwizzle),
-                         tc_desc_swizzled(sbase + L::kK + buf * L::kKBytes + j * 32, L::kGroup, L::kSwizzle),
+                         tc_desc_swizzled(sbase + L::kQ + (j / kPer) * (kAtcRows * L::kSeg) + (j % kPer) * 32,
+                                          L::kGroup, L::kSwizzle),
+                         tc_desc_swizzled(sbase + L::kK + buf * L::kKBytes + (j / kPer) * (kAtcTile * L::kSeg) +
+                                              (j % kPer) * 32, L::kGroup, L::kSwizzle),
                          kAtcIdescQK, j > 0);
+        }
         tc_commit(bar_s);
     };
     auto issue_pv = [&](int buf, bool accumulate) {

@@ -595,9 +595,10 @@ static int attention_tc_launch(const uint32_t* q, const uint32_t* k, const uint3
     if (int st = status_word(&status)) return st;
     const long long blocks = (seq_len + kAtcRows - 1) / kAtcRows;
     const long long tiles = (seq_len + kAtcTile - 1) / kAtcTile;
-    // as many CTAs per query block as still run in one wave (2 CTAs per SM with rows of 128
-    // codes, 3 with narrower ones), at most 8 (a portable cluster) and at least 2 tiles each
-    const long long per_sm = D > 64 ? 2 : 3;
+    // as many CTAs per query block as still run in one wave (1 CTA per SM with rows of 256
+    // codes, 2 with 128, 3 with narrower ones), at most 8 (a portable cluster) and at least
+    // 2 tiles each
+    const long long per_sm = D > 128 ? 1 : D > 64 ? 2 : 3;
     long long splits = per_sm * dev.sm_count / blocks;
     if (splits > 8) splits = 8;
     if (splits > tiles / 2) splits = tiles / 2;
@@ -628,7 +629,7 @@ static int attention_any(const uint32_t* q, const uint32_t* k, const uint32_t* v
     const int tc = g_tune.attn_tc.load(std::memory_order_relaxed);
     // Measured on B200: below these lengths the register-fed kernel (16 queries per CTA, no
     // cluster, no tensor-memory allocation) is as fast or faster.
-    constexpr long long kFrom = D >= 128 ? 512 : D >= 64 ? 2560 : 4096;
+    constexpr long long kFrom = D >= 256 ? 256 : D >= 128 ? 512 : D >= 64 ? 2560 : 4096;
     // a query block is at most 65535 grid rows; cp.async moves 16-byte pieces
     if (tc && (tc == 2 || seq_len >= kFrom) && seq_len <= 65535ll * kAtcRows && aligned(q, 16) &&
         aligned(k, 16) && aligned(v, 16))
@@ -878,7 +879,7 @@ int feather_attention_fp8_e5m2(const uint32_t* q, const uint32_t* k, const uint3
         case 8: return attention_any<32>(q, k, v, out, seq_len, *dev, s);
         case 16: return attention_any<64>(q, k, v, out, seq_len, *dev, s);
         case 32: return attention_any<128>(q, k, v, out, seq_len, *dev, s);
-        case 64: return attention_launch<256>(q, k, v, out, seq_len, *dev, s);
+        case 64: return attention_any<256>(q, k, v, out, seq_len, *dev, s);
         case 128: return attention_launch<512>(q, k, v, out, seq_len, *dev, s);
         default: return h_dim_words > 128 ? FEATHER_ERR_TOO_LARGE : FEATHER_ERR_BAD_ARG;
     }
