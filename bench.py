@@ -698,7 +698,7 @@ def run_ours(args) -> None:
         from feather_b200.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu as attn
         tpeak, tpeak_kind = measured_tensor_peak()
         lib = fb._lib.load()
-        for seq, d in ((4096, 128), (8192, 64), (8192, 128)):
+        for seq, d in ((4096, 128), (8192, 64), (8192, 128), (4096, 256), (4096, 512)):
             gen.manual_seed(31)
             qkv = [fb.pack_fp8_tensor(torch.randn(seq, d, device=dev, generator=gen, dtype=torch.float16), "E5M2")
                    for _ in range(3)]

@@ -76,18 +76,24 @@ constexpr int kAtcTile = 64;       // keys per step (the reference's tile, atten
 
 template <int D>
 struct AtcLayout {
-    static constexpr int kQ = 0;                               // [128][D] codes, 16-byte units swizzled over D bytes
+    // Rows of 512 codes: the output's columns are split over a pair of CTAs (kHalves = 2):
+    // both compute the same S and P, each multiplies P with its half of V's columns.
+    static constexpr int kHalves = D > 256 ? 2 : 1;
+    static constexpr int kDo = D / kHalves;                    // output columns of a CTA
+    static constexpr int kKBufs = D > 256 ? 1 : 2;             // 512 codes: no room for a second K tile
+    static constexpr int kQ = 0;                               // [128][D] codes, 16-byte units swizzled
     static constexpr int kQBytes = kAtcRows * D;
-    static constexpr int kK = kQ + kQBytes;                    // 2 x [64][D], swizzled like Q
+    static constexpr int kK = kQ + kQBytes;                    // kKBufs x [64][D], swizzled like Q
     static constexpr int kKBytes = kAtcTile * D;
-    static constexpr int kVraw = kK + 2 * kKBytes;             // 2 x [64][D] codes
-    static constexpr int kV = kVraw + 2 * kKBytes;             // 2 x FP16, see above
+    static constexpr int kVraw = kK + kKBufs * kKBytes;        // 2 x [64][kDo] codes
+    static constexpr int kVrawBytes = kAtcTile * kDo;
+    static constexpr int kV = kVraw + 2 * kVrawBytes;          // 2 x FP16, see above
     static constexpr int kVSbo = 144;
-    static constexpr int kVLbo = (D / 8) * kVSbo;
+    static constexpr int kVLbo = (kDo / 8) * kVSbo;
     static constexpr int kVBytes = (kAtcTile / 8) * kVLbo;
     static constexpr int kP = kV + 2 * kVBytes;                // [8][128][16 B] FP16
     static constexpr int kPBytes = kAtcRows * kAtcTile * 2;
-    static constexpr int kBar = kP + kPBytes;                  // mbarriers S, P V; tensor-memory base; mbarriers tile codes x 2
+    static constexpr int kBar = kP + kPBytes;                  // mbarriers: S, P V; tensor-memory base; K x 2, V codes x 2
     static constexpr int kTileBytes = kBar + 64;
     // operand rows of D bytes are swizzled over D bytes: descriptor layout type and the
     // 8-row group stride (SBO); the tensor maps that fill them use the same swizzle
@@ -97,14 +103,14 @@ struct AtcLayout {
     static constexpr int kSegs = D / kSeg;
     static constexpr uint32_t kSwizzle = kSeg == 128 ? 2u : kSeg == 64 ? 4u : 6u;   // 128 B, 64 B, 32 B
     static constexpr uint32_t kGroup = 8 * kSeg;
-    // the merge reuses the operand space: O as [128][D + 4] floats (the odd 16 B keep a
+    // the merge reuses the operand space: O as [128][kDo + 4] floats (the odd 16 B keep a
     // thread-per-row's 16-byte stores free of bank conflicts), then m[128] and the two threads' l[2][128]
-    static constexpr int kMergeStride = D + 4;
+    static constexpr int kMergeStride = kDo + 4;
     static constexpr int kMergeM = kAtcRows * kMergeStride * 4;
     static constexpr int kMergeBytes = kMergeM + 3 * kAtcRows * 4;
     static constexpr int kWeightBytes = 0;
     static_assert(kMergeBytes + kWeightBytes <= kBar, "the merge buffers must not reach the barriers");
-    static constexpr int kCols = D > 128 ? 512 : D > 64 ? 256 : 128;   // tensor-memory columns: 64 (S) + D (P V)
+    static constexpr int kCols = kDo > 128 ? 512 : kDo > 64 ? 256 : 128;   // tensor-memory columns: 64 (S) + kDo (P V)
     // at most 512 / kCols CTAs of this kernel per SM: ask for more than 1 / (that + 1) of 227 KiB
     static constexpr int kMinBytes = (227 * 1024) / (512 / kCols + 1) + 1024;
     static constexpr int kBytes = kTileBytes > kMinBytes ? kTileBytes : kMinBytes;
@@ -141,7 +147,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 // 17-22), M / 16 (bits 24-28).
 constexpr uint32_t kAtcIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((kAtcTile / 8) << 17) | ((kAtcRows / 16) << 24);
 template <int D>
-constexpr uint32_t kAtcIdescPV = (1u << 4) | (1u << 16) | ((uint32_t)(D / 8) << 17) | ((kAtcRows / 16) << 24);
+constexpr uint32_t kAtcIdescPV = (1u << 4) | (1u << 16) | ((uint32_t)(D / 8) << 17) | ((kAtcRows / 16) << 24);   // D: columns of the product
 
 template <bool F8>
 __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
@@ -250,8 +256,8 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
 }
 
 // Host side: a row-major matrix of `rows` x d bytes as a 2-D tensor map with boxes of
-// d bytes x box_rows rows (swizzled: at most 128 bytes wide, rows swizzled over 32, 64 or
-// 128 bytes; wider rows are fetched as 128-byte column segments) or not swizzled; elements
+// box_bytes x box_rows (swizzled over box_bytes = 32, 64 or 128, or not swizzled and up to
+// 256 bytes wide); elements
 // outside the matrix read as zeros.  False if the driver does not offer the encoder or
 // refuses the arguments (base 16-byte aligned, d a multiple of 16).
 typedef CUresult (*AtcEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -268,43 +274,48 @@ inline AtcEncodeTiled atc_encoder() {
     }();
     return fn;
 }
-inline bool atc_make_map(CUtensorMap* map, const void* base, int d, long long rows, int box_rows, bool swizzled) {
-    const int box_bytes = swizzled && d > 128 ? 128 : d;   // swizzled boxes are at most one 128-byte segment wide
+inline bool atc_make_map(CUtensorMap* map, const void* base, int d, long long rows, int box_bytes, int box_rows,
+                         bool swizzled) {
     const AtcEncodeTiled encode = atc_encoder();
     if (!encode) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)d, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)d};
     const cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
     const cuuint32_t steps[2] = {1, 1};
-    const CUtensorMapSwizzle sw = !swizzled ? CU_TENSOR_MAP_SWIZZLE_NONE
-                                  : d >= 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                                  : d == 64  ? CU_TENSOR_MAP_SWIZZLE_64B
-                                             : CU_TENSOR_MAP_SWIZZLE_32B;
+    const CUtensorMapSwizzle sw = !swizzled         ? CU_TENSOR_MAP_SWIZZLE_NONE
+                                  : box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : box_bytes == 64  ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                     : CU_TENSOR_MAP_SWIZZLE_32B;
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, steps,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// D = codes per row: 32, 64, 128 or 256.  Grid (splits, query blocks), cluster (splits, 1, 1),
+// D = codes per row: 32, 64, 128, 256 or 512.  Grid (splits, query blocks * kHalves), cluster
+// (splits, kHalves, 1) with kHalves = 2 for 512 codes (the pair shares a query block), else 1;
 // 288 threads, AtcLayout<D>::kBytes of dynamic shared memory.  map_q, map_k, map_v: the
-// seq_len x D byte matrices as 2-D tensor maps with boxes of 128, 64 and 64 rows, Q and K
-// swizzled over D bytes, V not (atc_make_map below); rows past seq_len read as zeros.
+// seq_len x D byte matrices as 2-D tensor maps with boxes of kSeg x 128, kSeg x 64 (swizzled)
+// and kDo x 64 (not swizzled) bytes x rows (atc_make_map above); rows past seq_len read as
+// zeros.
 template <int D>
-__global__ void __launch_bounds__(kAtcThreads, D > 128 ? 1 : D > 64 ? 2 : 3)
+__global__ void __launch_bounds__(kAtcThreads, D > 128 ? 1 : D > 64 ? 2 : 3)   // CTAs per SM, see AtcLayout::kCols
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, float* __restrict__ out, int seq_len,
                     unsigned int* status) {
     extern __shared__ __align__(1024) unsigned char atc_smem[];
     using L = AtcLayout<D>;
-    constexpr int DH = D / 2;                     // output columns per thread
+    constexpr int DO = L::kDo;                    // output columns of this CTA
+    constexpr int DH = DO / 2;                    // output columns per thread
     constexpr int KH = kAtcTile / 2;              // keys per thread
     const int tid = threadIdx.x, warp = tid >> 5;
     const int row = tid & (kAtcRows - 1);         // this thread's query row = lane of tensor memory
     const int half = tid >> 7;                    // ... and which half of the keys and columns
     const int n_split = (int)gridDim.x, split = (int)blockIdx.x;
-    const int row0 = (int)blockIdx.y * kAtcRows;
+    const int row0 = (int)(blockIdx.y / L::kHalves) * kAtcRows;
+    const int col0 = (int)(blockIdx.y % L::kHalves) * DO;      // this CTA's first output column
     const uint32_t sbase = smem_u32(atc_smem);
-    const uint32_t bar_s = sbase + L::kBar, bar_o = bar_s + 8, bar_kv = bar_s + 32;   // bar_kv + 8: second buffer
+    const uint32_t bar_s = sbase + L::kBar, bar_o = bar_s + 8;
+    const uint32_t bar_k = bar_s + 32, bar_v = bar_s + 48;     // + 8: the second buffer's
     if (sbase & 1023u) {                          // the swizzled operands want 1 KiB alignment (every CTA alike)
         if (tid == 0) atomicOr(status, 2u);
         return;
@@ -317,30 +328,42 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int n = min(tiles, t_begin + per) - t_begin;
 
     // One lane of the issuing warp does everything asynchronous.  The codes of key tile t
-    // (K into the swizzled operand layout, V as stored) arrive by two tensor-map copies that
-    // count their bytes on the buffer's mbarrier; its phase for tile t is t / 2.
-    auto load_kv = [&](int t, int buf, uint32_t more_bytes = 0) {
-        mbar_arrive_expect_tx(bar_kv + 8 * buf, 2 * L::kKBytes + more_bytes);
+    // arrive by tensor-map copies that count their bytes on mbarriers: K into the swizzled
+    // operand layout (buffer and phase of tile t: t % 2 and t / 2 with two buffers, 0 and t
+    // with one), this CTA's columns of V as stored (buffer t % 2, phase t / 2).
+    auto k_bar = [&](int t) { return bar_k + (L::kKBufs == 2 ? 8 * (t & 1) : 0); };
+    auto k_parity = [&](int t) { return (uint32_t)((L::kKBufs == 2 ? t >> 1 : t) & 1); };
+    auto k_at = [&](int t) { return sbase + L::kK + (L::kKBufs == 2 ? (t & 1) * L::kKBytes : 0); };
+    auto load_k = [&](int t, uint32_t more_bytes = 0) {
+        mbar_arrive_expect_tx(k_bar(t), L::kKBytes + more_bytes);
 #pragma unroll
         for (int g = 0; g < L::kSegs; ++g)
-            tma_load_2d(sbase + L::kK + buf * L::kKBytes + g * (kAtcTile * L::kSeg), &map_k, g * L::kSeg,
-                        (t_begin + t) * kAtcTile, bar_kv + 8 * buf);
-        tma_load_2d(sbase + L::kVraw + buf * L::kKBytes, &map_v, 0, (t_begin + t) * kAtcTile, bar_kv + 8 * buf);
+            tma_load_2d(k_at(t) + g * (kAtcTile * L::kSeg), &map_k, g * L::kSeg, (t_begin + t) * kAtcTile, k_bar(t));
+    };
+    auto load_v = [&](int t) {
+        mbar_arrive_expect_tx(bar_v + 8 * (t & 1), L::kVrawBytes);
+        tma_load_2d(sbase + L::kVraw + (t & 1) * L::kVrawBytes, &map_v, col0, (t_begin + t) * kAtcTile, bar_v + 8 * (t & 1));
     };
     constexpr int kIssuer = kAtcWorkers / 32;     // the issuing warp: it also owns the tensor-memory allocation
     if (warp == kIssuer) {
         if ((tid & 31) == 0) {
             mbar_init(bar_s, 1);
             mbar_init(bar_o, 1);
-            mbar_init(bar_kv, 1);
-            mbar_init(bar_kv + 8, 1);
+            mbar_init(bar_k, 1);
+            mbar_init(bar_k + 8, 1);
+            mbar_init(bar_v, 1);
+            mbar_init(bar_v + 8, 1);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             if (n > 0) {                          // the first copies leave before anything else is set up
-                load_kv(0, 0, L::kQBytes);        // Q rides on the first buffer's first phase
+                load_k(0, L::kQBytes);            // Q rides on the first K tile's barrier
 #pragma unroll
                 for (int g = 0; g < L::kSegs; ++g)
-                    tma_load_2d(sbase + L::kQ + g * (kAtcRows * L::kSeg), &map_q, g * L::kSeg, row0, bar_kv);
-                if (n > 1) load_kv(1, 1);
+                    tma_load_2d(sbase + L::kQ + g * (kAtcRows * L::kSeg), &map_q, g * L::kSeg, row0, k_bar(0));
+                load_v(0);
+                if (n > 1) {
+                    if (L::kKBufs == 2) load_k(1);
+                    load_v(1);
+                }
             }
         }
         __syncwarp();
@@ -357,15 +380,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     // The products: S = Q K^T of a tile (d / 32 instructions of 32 codes each: 32 bytes further
     // along the swizzled rows) and P V (4 instructions of 16 keys, two key groups, each).
-    auto issue_qk = [&](int buf) {
+    auto issue_qk = [&](int t) {
 #pragma unroll
         for (int j = 0; j < D / 32; ++j) {
             constexpr int kPer = L::kSeg / 32;    // steps per column segment
             tc_mma<true>(tmem,
                          tc_desc_swizzled(sbase + L::kQ + (j / kPer) * (kAtcRows * L::kSeg) + (j % kPer) * 32,
                                           L::kGroup, L::kSwizzle),
-                         tc_desc_swizzled(sbase + L::kK + buf * L::kKBytes + (j / kPer) * (kAtcTile * L::kSeg) +
-                                              (j % kPer) * 32, L::kGroup, L::kSwizzle),
+                         tc_desc_swizzled(k_at(t) + (j / kPer) * (kAtcTile * L::kSeg) + (j % kPer) * 32,
+                                          L::kGroup, L::kSwizzle),
                          kAtcIdescQK, j > 0);
         }
         tc_commit(bar_s);
@@ -376,15 +399,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tc_mma<false>(tmem + kAtcTile,
                           tc_desc(sbase + L::kP + j * 2 * (kAtcRows * 16), kAtcRows * 16, 128),
                           tc_desc(sbase + L::kV + buf * L::kVBytes + j * 2 * L::kVLbo, L::kVLbo, L::kVSbo),
-                          kAtcIdescPV<D>, accumulate || j > 0);
+                          kAtcIdescPV<DO>, accumulate || j > 0);
         tc_commit(bar_o);
     };
     // V codes -> FP16 (8 codes -> one 16-byte unit) in the layout P V reads.
     auto spread_v = [&](int buf) {
 #pragma unroll
-        for (int u = tid; u < kAtcTile * (D / 8); u += kAtcWorkers) {
-            const int ng = u % (D / 8), key = u / (D / 8);
-            const uint2 w = *reinterpret_cast<const uint2*>(atc_smem + L::kVraw + buf * L::kKBytes + key * D + ng * 8);
+        for (int u = tid; u < kAtcTile * (DO / 8); u += kAtcWorkers) {
+            const int ng = u % (DO / 8), key = u / (DO / 8);
+            const uint2 w = *reinterpret_cast<const uint2*>(atc_smem + L::kVraw + buf * L::kVrawBytes + key * DO + ng * 8);
             uint4 h;
             decode_word_h2<kE5M2>(w.x, h.x, h.y);
             decode_word_h2<kE5M2>(w.y, h.z, h.w);
@@ -415,8 +438,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         // ---- the issuing warp: the workers' tile barriers, one lane issues behind each ----
         bool okk = true;
         if (n > 0 && (tid & 31) == 0) {
-            okk = mbar_wait(bar_kv, 0, status);
+            okk = mbar_wait(k_bar(0), k_parity(0), status);
             issue_qk(0);
+            if (L::kKBufs == 1 && n > 1) {        // the one K buffer is free once S(0) is done
+                okk = mbar_wait(bar_s, 0, status) && okk;
+                load_k(1);
+            }
         }
         __syncwarp();
         for (int i = 0; i < n; ++i) {
@@ -424,18 +451,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if ((tid & 31) == 0) {
                 tc_fence_after();
                 if (i + 1 < n) {
-                    okk = mbar_wait(bar_kv + 8 * ((i + 1) & 1), (uint32_t)(((i + 1) >> 1) & 1), status) && okk;
-                    issue_qk((i + 1) & 1);
+                    okk = mbar_wait(k_bar(i + 1), k_parity(i + 1), status) && okk;
+                    issue_qk(i + 1);
                 }
                 issue_pv(i & 1, i > 0);
                 // tile i + 2's codes go where tile i's were: S(i) and the spread of V(i) are done with them
-                if (i + 2 < n) load_kv(i + 2, i & 1);
+                if (i + 2 < n) {
+                    load_v(i + 2);
+                    if (L::kKBufs == 1) okk = mbar_wait(bar_s, (uint32_t)((i + 1) & 1), status) && okk;   // S(i + 1) done
+                    load_k(i + 2);
+                }
             }
             __syncwarp();
         }
     } else {
         if (n > 0) {
-            ok = mbar_wait(bar_kv, 0, status);
+            ok = mbar_wait(bar_v, 0, status);
             spread_v(0);
         }
 
@@ -494,7 +525,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tc_fence_before();
             if (cta_sync_or(!ok)) break;
             if (i + 1 < n) {                      // P(i - 1) V(i - 1), the last reader of that half, has completed
-                ok = mbar_wait(bar_kv + 8 * (buf ^ 1), (uint32_t)(((i + 1) >> 1) & 1), status) && ok;
+                ok = mbar_wait(bar_v + 8 * (buf ^ 1), (uint32_t)(((i + 1) >> 1) & 1), status) && ok;
                 spread_v(buf ^ 1);
             }
         }
@@ -531,8 +562,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int rows_here = max(0, min(rows_per, kAtcRows - split * rows_per));
     uint32_t peer[8];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) peer[c] = map_cluster(sbase, (uint32_t)min(c, n_split - 1));
-    constexpr int kGroups = D / 4;
+    for (int c = 0; c < 8; ++c)               // the CTAs with this CTA's columns: cluster rank = split + n_split * column half
+        peer[c] = map_cluster(sbase, (uint32_t)(min(c, n_split - 1) + n_split * (int)(blockIdx.y % L::kHalves)));
+    constexpr int kGroups = DO / 4;
     if (n_split == 1) {
         // nothing to merge: this CTA's own rows, plain shared-memory loads
         const float* mo_l = mo + L::kMergeM / 4 + kAtcRows;
@@ -541,7 +573,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (row0 + rr >= seq_len) break;
             const float lsum = mo_l[rr] + mo_l[kAtcRows + rr];
             const float4 x = *reinterpret_cast<const float4*>(mo + rr * L::kMergeStride + 4 * g);
-            *reinterpret_cast<float4*>(out + (size_t)(row0 + rr) * D + 4 * g) =
+            *reinterpret_cast<float4*>(out + (size_t)(row0 + rr) * D + col0 + 4 * g) =
                 make_float4(__fdiv_rn(x.x, lsum), __fdiv_rn(x.y, lsum), __fdiv_rn(x.z, lsum), __fdiv_rn(x.w, lsum));
         }
     }
@@ -579,7 +611,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             acc.z += x[c].z * wc;
             acc.w += x[c].w * wc;
         }
-        *reinterpret_cast<float4*>(out + (size_t)(row0 + rr) * D + 4 * g) =
+        *reinterpret_cast<float4*>(out + (size_t)(row0 + rr) * D + col0 + 4 * g) =
             make_float4(__fdiv_rn(acc.x, lsum), __fdiv_rn(acc.y, lsum), __fdiv_rn(acc.z, lsum), __fdiv_rn(acc.w, lsum));
     }
     cluster_sync();                           // nobody leaves while a peer reads its memory

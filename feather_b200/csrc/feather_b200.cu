@@ -583,7 +583,7 @@ static int attention_launch(const uint32_t* q, const uint32_t* k, const uint32_t
 }
 
 // The tcgen05 kernel: 128 queries per CTA, the key tiles of a query block split over a
-// cluster of 1 .. 8 CTAs.
+// cluster of 1 .. 8 CTAs (rows of 512 codes: times the pair of CTAs that split the output's columns).
 template <int D>
 static int attention_tc_launch(const uint32_t* q, const uint32_t* k, const uint32_t* v, float* out,
                                long long seq_len, const DeviceInfo& dev, cudaStream_t s) {
@@ -599,25 +599,26 @@ static int attention_tc_launch(const uint32_t* q, const uint32_t* k, const uint3
     // codes, 2 with 128, 3 with narrower ones), at most 8 (a portable cluster) and at least
     // 2 tiles each
     const long long per_sm = D > 128 ? 1 : D > 64 ? 2 : 3;
-    long long splits = per_sm * dev.sm_count / blocks;
-    if (splits > 8) splits = 8;
+    long long splits = per_sm * dev.sm_count / (blocks * L::kHalves);
+    if (splits > 8 / L::kHalves) splits = 8 / L::kHalves;
     if (splits > tiles / 2) splits = tiles / 2;
     if (splits < 1) splits = 1;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)splits, (unsigned)blocks);
+    cfg.gridDim = dim3((unsigned)splits, (unsigned)(blocks * L::kHalves));
     cfg.blockDim = dim3(kAtcThreads);
     cfg.dynamicSmemBytes = L::kBytes;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)splits;
-    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.y = L::kHalves;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     CUtensorMap map_q, map_k, map_v;
-    if (!atc_make_map(&map_q, q, D, seq_len, kAtcRows, true) || !atc_make_map(&map_k, k, D, seq_len, kAtcTile, true) ||
-        !atc_make_map(&map_v, v, D, seq_len, kAtcTile, false))
+    if (!atc_make_map(&map_q, q, D, seq_len, L::kSeg, kAtcRows, true) ||
+        !atc_make_map(&map_k, k, D, seq_len, L::kSeg, kAtcTile, true) ||
+        !atc_make_map(&map_v, v, D, seq_len, L::kDo, kAtcTile, false))
         return attention_launch<D>(q, k, v, out, seq_len, dev, s);   // no encoder in this driver: the other kernel
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, map_q, map_k, map_v, out, (int)seq_len, status);
     return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
@@ -630,8 +631,8 @@ static int attention_any(const uint32_t* q, const uint32_t* k, const uint32_t* v
     // Measured on B200: below these lengths the register-fed kernel (16 queries per CTA, no
     // cluster, no tensor-memory allocation) is as fast or faster.
     constexpr long long kFrom = D >= 256 ? 256 : D >= 128 ? 512 : D >= 64 ? 2560 : 4096;
-    // a query block is at most 65535 grid rows; cp.async moves 16-byte pieces
-    if (tc && (tc == 2 || seq_len >= kFrom) && seq_len <= 65535ll * kAtcRows && aligned(q, 16) &&
+    // the grid's second dimension is at most 65535; the tensor maps want 16-byte alignment
+    if (tc && (tc == 2 || seq_len >= kFrom) && seq_len <= 32767ll * kAtcRows && aligned(q, 16) &&
         aligned(k, 16) && aligned(v, 16))
         return attention_tc_launch<D>(q, k, v, out, seq_len, dev, s);
     return attention_launch<D>(q, k, v, out, seq_len, dev, s);
@@ -880,7 +881,7 @@ int feather_attention_fp8_e5m2(const uint32_t* q, const uint32_t* k, const uint3
         case 16: return attention_any<64>(q, k, v, out, seq_len, *dev, s);
         case 32: return attention_any<128>(q, k, v, out, seq_len, *dev, s);
         case 64: return attention_any<256>(q, k, v, out, seq_len, *dev, s);
-        case 128: return attention_launch<512>(q, k, v, out, seq_len, *dev, s);
+        case 128: return attention_any<512>(q, k, v, out, seq_len, *dev, s);
         default: return h_dim_words > 128 ? FEATHER_ERR_TOO_LARGE : FEATHER_ERR_BAD_ARG;
     }
 }

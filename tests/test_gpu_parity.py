@@ -996,11 +996,11 @@ def test_attention_vs_oracle_and_reference_outputs(fb, golden, seq, d, kernel, a
     """Packed-E5M2 attention against the oracle (same tiles, same FP16 rounding of the
     probabilities), the reference kernel's own outputs where the fixture has them, and
     torch's scaled_dot_product_attention when the key tiles are full.  Every shape runs
-    through the library's own choice of kernel, through the tcgen05 kernel (rows of 32, 64,
-    128 or 256 codes; other widths have only the register-fed kernel) and through the
+    through the library's own choice of kernel, through the tcgen05 kernel (rows of 32 to
+    512 codes; rows of 16 have only the register-fed kernel) and through the
     register-fed kernel."""
     from feather_b200.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu as attn
-    if kernel != "default" and d not in (32, 64, 128, 256):
+    if kernel != "default" and d not in (32, 64, 128, 256, 512):
         pytest.skip("one kernel only for this width")
     attention_kernel(kernel)
     g = golden("attention")
