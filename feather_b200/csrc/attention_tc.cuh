@@ -59,6 +59,12 @@
 //     (SBO; the odd 16 B keep the conversion's stores free of bank conflicts) and key
 //     groups (d / 8) * 144 B apart (LBO).
 //
+// Rows of 256 codes are two swizzled 128-byte column segments per operand and one CTA per
+// SM.  Rows of 512 codes need 64 + 512 tensor-memory columns, more than an SM has: a pair of
+// CTAs in the cluster shares the query block, both compute the same S and P, each multiplies
+// P with its half of V's columns and owns that half of the output; with Q at 64 KB their K
+// tile is single-buffered (the copy of the next tile waits for S of the current one).
+//
 // Every wait is bounded (mbar_wait raises the status word and gives up after the limit);
 // a CTA that gave up still walks every CTA and cluster barrier and frees its tensor
 // memory.  Shared memory per CTA is sized so that the CTAs resident on one SM never ask

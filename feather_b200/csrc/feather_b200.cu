@@ -37,9 +37,9 @@ namespace feather {
 //   dot_ring         0: register-load dot kernel only; 1, 2, 3: long aligned operands take the
 //                    bulk-copy ring kernel with 6 x 32 KiB, 3 x 64 KiB or 12 x 16 KiB stages
 //   dot_pre_kb       KiB the dot ring kernel asks L2 for ahead of its stream-order wait
-//   attn_tc          attention with 32, 64 or 128 codes per row: 0 the register-fed mma.sync
-//                    kernel, 1 the tcgen05 kernel from 4096 / 2560 / 512 queries up, 2 the
-//                    tcgen05 kernel always
+//   attn_tc          attention with 32 .. 512 codes per row: 0 the register-fed mma.sync
+//                    kernel, 1 the tcgen05 kernel from 4096 / 2560 / 512 / 256 / 256 queries
+//                    up, 2 the tcgen05 kernel always
 struct Tuning {
     std::atomic<int> ring_pre_kb{128};
     std::atomic<int> rows_pre{1};

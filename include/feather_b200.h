@@ -445,9 +445,10 @@ int feather_gemv_chain_fp8_tp(const void* plan, int32_t n_ops, uint32_t flags, i
  *   dot_pre_kb=K        as ring_pre_kb, for the dot ring kernel
  *   dot_unroll=1|2|4    16-byte loads per operand a dot thread keeps in flight
  *   dot_ctas_per_sm=C   dot grid in CTAs per SM (1 .. 16)
- *   attn_tc=0|1|2       attention on rows of 32, 64 or 128 codes: 0 the register-fed
+ *   attn_tc=0|1|2       attention on rows of 32 .. 512 codes: 0 the register-fed
  *                       mma.sync kernel, 1 (default) the tcgen05 kernel from 4096 /
- *                       2560 / 512 queries up, 2 the tcgen05 kernel for every length
+ *                       2560 / 512 / 256 / 256 queries up, 2 the tcgen05 kernel for
+ *                       every length
  * The environment variable FEATHER_KERNEL, if set, is applied once with the
  * same syntax when the library first touches a device.  Process-wide, takes
  * effect for later launches.  FEATHER_ERR_BAD_ARG for an unknown key or value;
