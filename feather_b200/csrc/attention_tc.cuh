@@ -218,6 +218,30 @@ __device__ __forceinline__ void tmem_st(uint32_t taddr, const float (&r)[N]) {
                "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Two FP32 operations in one instruction (the lanes round like the scalar forms).
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -322,6 +346,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t sbase = smem_u32(atc_smem);
     const uint32_t bar_s = sbase + L::kBar, bar_o = bar_s + 8;
     const uint32_t bar_k = bar_s + 32, bar_v = bar_s + 48;     // + 8: the second buffer's
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may be scheduled as SMs free up
     if (sbase & 1023u) {                          // the swizzled operands want 1 KiB alignment (every CTA alike)
         if (tid == 0) atomicOr(status, 2u);
         return;
@@ -360,6 +385,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             mbar_init(bar_v, 1);
             mbar_init(bar_v + 8, 1);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            // Launched with programmatic stream serialization, the grid may start while the
+            // kernel before it in the stream still runs: nothing of global memory is read
+            // before that kernel has completed (Q, K, V may be its results) ...
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             if (n > 0) {                          // the first copies leave before anything else is set up
                 load_k(0, L::kQBytes);            // Q rides on the first K tile's barrier
 #pragma unroll
@@ -498,22 +527,29 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float mn2 = fmaxf(m2, mx * scale2);
             const float alpha = ex2_approx(m2 - mn2);
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            // pairs of scores through the packed FP32 forms: one FMA and one add per two scores
+            const uint64_t scale_pair = f2_pack(scale2, scale2), minus_max = f2_pack(-mn2, -mn2);
+            uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};      // four pairs of partial sums (+0.0f bits)
 #pragma unroll
             for (int u = 0; u < KH / 8; ++u) {
                 uint32_t p[4];
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
-                    const float e0 = ex2_approx(fmaf(s[8 * u + 2 * x], scale2, -mn2));
-                    const float e1 = ex2_approx(fmaf(s[8 * u + 2 * x + 1], scale2, -mn2));
-                    sum4[x] += e0 + e1;
+                    float a0, a1;
+                    f2_unpack(f2_fma(f2_pack(s[8 * u + 2 * x], s[8 * u + 2 * x + 1]), scale_pair, minus_max), a0, a1);
+                    const float e0 = ex2_approx(a0), e1 = ex2_approx(a1);
+                    sum2[x] = f2_add(sum2[x], f2_pack(e0, e1));
                     const __half2 h = __floats2half2_rn(e0, e1);
                     p[x] = *reinterpret_cast<const uint32_t*>(&h);
                 }
                 *reinterpret_cast<uint4*>(atc_smem + L::kP + (half * (KH / 8) + u) * (kAtcRows * 16) + row * 16) =
                     make_uint4(p[0], p[1], p[2], p[3]);
             }
-            l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            {
+                float lo, hi;
+                f2_unpack(f2_add(f2_add(sum2[0], sum2[1]), f2_add(sum2[2], sum2[3])), lo, hi);
+                l = l * alpha + (lo + hi);
+            }
             m2 = mn2;
             // ---- output *= alpha, unless no row of this warp saw a new maximum (alpha = 1 everywhere) ----
             if (i > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.f)) {
@@ -521,8 +557,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 for (int c = 0; c < DH / CH; ++c) {
                     float acc[CH];
                     tmem_ld<CH>(tmem_o + CH * c, acc);
+                    const uint64_t alpha_pair = f2_pack(alpha, alpha);
 #pragma unroll
-                    for (int x = 0; x < CH; ++x) acc[x] *= alpha;
+                    for (int x = 0; x < CH; x += 2) f2_unpack(f2_mul(f2_pack(acc[x], acc[x + 1]), alpha_pair), acc[x], acc[x + 1]);
                     tmem_st<CH>(tmem_o + CH * c, acc);
                 }
                 tmem_wait_st();
@@ -560,6 +597,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
     tc_fence_before();
     cluster_sync();
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // ... and nothing is written (it may write `out` too)
     // Every CTA merges its share of the 128 rows (128 / n_split, rounded up): four columns per item, consecutive threads along
     // a row (remote reads and global stores are contiguous runs).  A thread reads the
     // n_split maxima and sums of its row and the n_split pieces of its item and weighs

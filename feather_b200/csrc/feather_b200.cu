@@ -608,13 +608,15 @@ static int attention_tc_launch(const uint32_t* q, const uint32_t* k, const uint3
     cfg.blockDim = dim3(kAtcThreads);
     cfg.dynamicSmemBytes = L::kBytes;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)splits;
     attr[0].val.clusterDim.y = L::kHalves;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     CUtensorMap map_q, map_k, map_v;
     if (!atc_make_map(&map_q, q, D, seq_len, L::kSeg, kAtcRows, true) ||
         !atc_make_map(&map_k, k, D, seq_len, L::kSeg, kAtcTile, true) ||
