@@ -1024,6 +1024,51 @@ def test_attention_vs_oracle_and_reference_outputs(fb, golden, seq, d, kernel, a
     assert torch.equal(attn(q, k, v, seq, d // 4), out)          # deterministic
 
 
+def test_attention_operands_off_the_16_byte_grid(fb, attention_kernel):
+    """The tcgen05 kernel fetches its operands by tensor-map copies, which want 16-byte
+    aligned bases; operands that start 4 bytes off take the register-fed kernel instead and
+    give its result."""
+    from feather_b200.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu as attn
+    seq, d = 640, 128
+    rng = np.random.default_rng(5)
+    x = [torch.from_numpy(rng.standard_normal((seq, d)).astype(np.float16)).cuda() for _ in range(3)]
+    q, k, v = (fb.pack_fp8_tensor(t, "E5M2").reshape(-1) for t in x)
+    attention_kernel("mma.sync")
+    want = attn(q, k, v, seq, d // 4)
+    attention_kernel("tcgen05")
+    shifted = []
+    for t in (q, k, v):
+        buf = torch.empty(t.numel() + 1, dtype=t.dtype, device=t.device)
+        buf[1:].copy_(t)
+        shifted.append(buf[1:])
+    assert shifted[0].data_ptr() % 16 == 4
+    assert torch.equal(attn(*shifted, seq, d // 4), want)
+    fb.device_status()
+
+
+def test_attention_back_to_back_launches_keep_stream_order(fb, attention_kernel):
+    """The tcgen05 kernel is launched with programmatic stream serialization: a grid may
+    start while the kernel before it still runs.  Operands produced by the kernel right
+    before it, and a shared output buffer written by consecutive launches, must behave as
+    if the launches ran one after the other."""
+    from feather_b200.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu as attn
+    attention_kernel("tcgen05")
+    seq, d = 2048, 128
+    g = torch.Generator(device="cuda").manual_seed(11)
+    xs = [[torch.randn(seq, d, device="cuda", generator=g, dtype=torch.float16) for _ in range(3)] for _ in range(2)]
+    packed = [[fb.pack_fp8_tensor(t, "E5M2") for t in x] for x in xs]
+    want = [attn(*p, seq, d // 4).clone() for p in packed]
+    torch.cuda.synchronize()
+    out = torch.empty(seq, d, dtype=torch.float32, device="cuda")
+    for i in range(21):                       # alternating operands into ONE output: the last launch wins
+        attn(*packed[i % 2], seq, d // 4, out=out)
+    assert torch.equal(out, want[0])
+    for i in range(6):                        # operands packed by the kernels right before the launch
+        fresh = [fb.pack_fp8_tensor(t, "E5M2") for t in xs[i % 2]]
+        assert torch.equal(attn(*fresh, seq, d // 4), want[i % 2])
+    fb.device_status()
+
+
 def test_attention_rejects(fb):
     from feather_b200.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu as attn
     w = torch.zeros(64 * 16, dtype=torch.int32, device="cuda")
