@@ -15,12 +15,12 @@
 // warps and one issuing warp.  Two worker threads share a row (warps w and w + 4 reach the
 // same 32 lanes): each takes half of a tile's keys and half of the output columns, and
 // both read all 64 scores of the row for its maximum, so the softmax needs no shuffles
-// and no exchange.  The key tiles of one query block are split over the 1, 2, 4 or 8 CTAs
-// of a thread-block cluster (contiguous ranges, as many CTAs as still run in one wave),
+// and no exchange.  The key tiles of one query block are split over the 1 .. 8 CTAs of a
+// thread-block cluster (contiguous ranges, as many CTAs as still run in one wave),
 // each with its own running maximum, sum and output; at the end every CTA leaves its
 // partial result in its own shared memory and the cluster merges them through distributed
 // shared memory (out = sum_c O_c 2^(m_c - m) / sum_c l_c 2^(m_c - m), CTAs in rank order),
-// each CTA writing 128 / cluster rows.  No global scratch, no atomics, deterministic.
+// each CTA writing its share of the 128 rows.  No global scratch, no atomics, deterministic.
 //
 // Tensor memory: columns 0..63 hold S = Q K^T of the current tile, columns 64..64+d-1 the
 // output, which P V accumulates into; before P(i) V(i) is issued each worker has multiplied
@@ -32,7 +32,8 @@
 //   1. waits for S(i) and for P(i-1) V(i-1) (mbarriers the tensor core arrives on),
 //   2. reads its scores (tcgen05.ld 32x32b), runs the online softmax -- the maximum lives in
 //      the exponent's scale, m2 = max * log2(e) / sqrt(d), so a probability is one FMA and
-//      one ex2 -- and stores its FP16 probabilities as the A operand of the second product,
+//      one ex2, the FMAs and the sums two at a time in the packed FP32 forms -- and stores
+//      its FP16 probabilities as the A operand of the second product,
 //   3. rescales its half row of the output;
 // behind it one lane of the issuing warp issues S(i+1) (kind::f8f6f4: the tensor core reads
 // the E5M2 codes themselves, d / 32 instructions) and then P(i) V(i) (kind::f16, 4
@@ -101,10 +102,10 @@ struct AtcLayout {
     static constexpr int kPBytes = kAtcRows * kAtcTile * 2;
     static constexpr int kBar = kP + kPBytes;                  // mbarriers: S, P V; tensor-memory base; K x 2, V codes x 2
     static constexpr int kTileBytes = kBar + 64;
-    // operand rows of D bytes are swizzled over D bytes: descriptor layout type and the
-    // 8-row group stride (SBO); the tensor maps that fill them use the same swizzle
-    // Rows wider than 128 bytes are held as D / 128 column segments of 128 bytes, one
-    // swizzled [rows][128 B] region after the other.
+    // Operand rows are swizzled over kSeg = min(D, 128) bytes; rows wider than 128 bytes are
+    // held as D / 128 column segments, one swizzled [rows][128 B] region after the other.
+    // kSwizzle is the descriptor's layout type, kGroup the 8-row group stride (SBO); the
+    // tensor maps that fill the regions use the same swizzle.
     static constexpr int kSeg = D < 128 ? D : 128;             // bytes of a row per segment
     static constexpr int kSegs = D / kSeg;
     static constexpr uint32_t kSwizzle = kSeg == 128 ? 2u : kSeg == 64 ? 4u : 6u;   // 128 B, 64 B, 32 B
@@ -114,15 +115,14 @@ struct AtcLayout {
     static constexpr int kMergeStride = kDo + 4;
     static constexpr int kMergeM = kAtcRows * kMergeStride * 4;
     static constexpr int kMergeBytes = kMergeM + 3 * kAtcRows * 4;
-    static constexpr int kWeightBytes = 0;
-    static_assert(kMergeBytes + kWeightBytes <= kBar, "the merge buffers must not reach the barriers");
+    static_assert(kMergeBytes <= kBar, "the merge buffer must not reach the barriers");
     static constexpr int kCols = kDo > 128 ? 512 : kDo > 64 ? 256 : 128;   // tensor-memory columns: 64 (S) + kDo (P V)
     // at most 512 / kCols CTAs of this kernel per SM: ask for more than 1 / (that + 1) of 227 KiB
     static constexpr int kMinBytes = (227 * 1024) / (512 / kCols + 1) + 1024;
     static constexpr int kBytes = kTileBytes > kMinBytes ? kTileBytes : kMinBytes;
 };
 
-// ---- tcgen05 / cp.async / cluster wrappers ----
+// ---- tcgen05 / tensor-map copy / cluster wrappers ----
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
