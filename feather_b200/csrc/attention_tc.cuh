@@ -598,10 +598,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     tc_fence_before();
     cluster_sync();
     asm volatile("griddepcontrol.wait;" ::: "memory");   // ... and nothing is written (it may write `out` too)
-    // Every CTA merges its share of the 128 rows (128 / n_split, rounded up): four columns per item, consecutive threads along
-    // a row (remote reads and global stores are contiguous runs).  A thread reads the
-    // n_split maxima and sums of its row and the n_split pieces of its item and weighs
-    // them with 2^(m_c - m), CTAs in rank order.
+    // Every CTA merges its share of the 128 rows (128 / n_split, rounded up): four columns
+    // per item, consecutive threads along a row (remote reads and global stores are
+    // contiguous runs).  A thread reads the n_split maxima and sums of its row and the
+    // n_split pieces of its item and weighs them with 2^(m_c - m), CTAs in rank order.
     const int rows_per = (kAtcRows + n_split - 1) / n_split;          // the last CTA may own fewer
     const int rows_here = max(0, min(rows_per, kAtcRows - split * rows_per));
     uint32_t peer[8];
