@@ -18,6 +18,7 @@
 #include "gemv_chain.cuh"
 #include "gemv_kernels.cuh"
 #include "gemv_multi.cuh"
+#include "gemv_multi_tc.cuh"
 #include "gemv_mma.cuh"
 #include "gemv_ring.cuh"
 
@@ -40,6 +41,8 @@ namespace feather {
 //   attn_tc          attention with 32 .. 512 codes per row: 0 the register-fed mma.sync
 //                    kernel, 1 the tcgen05 kernel from 4096 / 2560 / 512 / 256 / 256 queries
 //                    up, 2 the tcgen05 kernel always
+//   multi_tc         E5M2 GEMV against several vectors, large matrices with rows of a multiple of
+//                    128 codes: 1 the tcgen05 kernel (16 vectors per pass), 0 the mma.sync kernel
 struct Tuning {
     std::atomic<int> ring_pre_kb{128};
     std::atomic<int> rows_pre{1};
@@ -49,6 +52,7 @@ struct Tuning {
     std::atomic<int> dot_pre_kb{64};
     std::atomic<int> ring_pre_kb_e4m3{-1};
     std::atomic<int> attn_tc{1};
+    std::atomic<int> multi_tc{1};
 };
 static Tuning g_tune;
 
@@ -73,6 +77,7 @@ static int apply_tuning(const char* spec) {
         else if (is("dot_pre_kb") && val >= 0 && val <= 16384) g_tune.dot_pre_kb = (int)val;
         else if (is("ring_pre_kb_e4m3") && val >= -1 && val <= 16384) g_tune.ring_pre_kb_e4m3 = (int)val;
         else if (is("attn_tc") && val >= 0 && val <= 2) g_tune.attn_tc = (int)val;
+        else if (is("multi_tc") && (val == 0 || val == 1)) g_tune.multi_tc = (int)val;
         else return FEATHER_ERR_BAD_ARG;
         p = end;
     }
@@ -513,6 +518,39 @@ static int gemv_mma_launch(const uint32_t* m, const uint32_t* v, float* out, lon
     return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
 }
 
+// E5M2, rows of a multiple of 128 codes, 16-byte aligned operands: up to 16 vectors per pass
+// on the tcgen05 kernel.  One CTA per SM, its rows walked in equal blocks of at most 128.
+static int gemv_multi_tc_launch(const uint32_t* m, const uint32_t* v, float* out, long long M, long long N,
+                                int nb, const DeviceInfo& dev, cudaStream_t s) {
+    auto kernel = gemv_multi_tc_kernel;
+    static std::atomic<unsigned long long> configured{0};
+    if (int st = ensure_smem(kernel, kMtcSmemBytes, configured)) return st;
+    unsigned int* status = nullptr;
+    if (int st = status_word(&status)) return st;
+    long long grid = dev.sm_count;
+    if (grid > (M + 15) / 16) grid = (M + 15) / 16;
+    const long long rows_cta = (M + grid - 1) / grid;
+    const long long n_blk = (rows_cta + kMtcSlotRows - 1) / kMtcSlotRows;
+    const long long blk_rows = (rows_cta + n_blk - 1) / n_blk;
+    CUtensorMap map_m, map_v;
+    if (!atc_make_map(&map_m, m, (int)N, M, kMtcBox, (int)blk_rows, true) ||
+        !atc_make_map(&map_v, v, (int)N, nb, kMtcBox, kMtcVectors, true))
+        return FEATHER_ERR_LAUNCH;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kMtcThreads);
+    cfg.dynamicSmemBytes = kMtcSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, map_m, map_v, out, (int)M, (int)N, nb, (int)rows_cta,
+                                             (int)blk_rows, (int)n_blk, status);
+    return e == cudaSuccess ? launch_status() : FEATHER_ERR_LAUNCH;
+}
+
 template <int MODE>
 static int gemv_multi_dispatch(const uint32_t* m, const uint32_t* v, float* out, long long M,
                                long long N, int B, const DeviceInfo& dev, cudaStream_t s,
@@ -523,6 +561,18 @@ static int gemv_multi_dispatch(const uint32_t* m, const uint32_t* v, float* out,
             if (int st = gemv_launch<MODE>(m, v + b * n_words, out + (long long)b * M, M, N, dev, s,
                                            static_matrix))
                 return st;
+        return FEATHER_OK;
+    }
+    if (MODE == kE5M2 && M >= 64ll * dev.sm_count && N % kMtcStep == 0 && N <= 0x7FFFFFFF && aligned(v, 16) &&
+        atc_encoder() && g_tune.multi_tc.load(std::memory_order_relaxed)) {
+        // large E5M2 matrices: the tensor core reads the codes themselves, 16 vectors per pass
+        for (int b0 = 0; b0 < B; b0 += kMtcVectors) {
+            const int nb = B - b0 < kMtcVectors ? B - b0 : kMtcVectors;
+            const int st = nb == 1 ? gemv_launch<MODE>(m, v + b0 * n_words, out + (long long)b0 * M, M, N, dev, s,
+                                                       static_matrix)
+                                   : gemv_multi_tc_launch(m, v + b0 * n_words, out + (long long)b0 * M, M, N, nb, dev, s);
+            if (st) return st;
+        }
         return FEATHER_OK;
     }
     if (M >= 64ll * dev.sm_count) {

@@ -910,7 +910,8 @@ def test_relu_all_codes_ragged_and_large_vs_oracle(fb, golden, mode):
                                          ((37, 2064), 4), ((300, 40000), 4), ((4801, 8192), 4),
                                          ((32000, 2048), 9), ((64, 16), 1), ((33, 20), 3), ((2048, 5632), 5),
                                          ((9472, 4096), 8), ((9500, 8208), 5), ((9473, 2048), 2),
-                                         ((12000, 16400), 3), ((9472, 528), 11)])
+                                         ((12000, 16400), 3), ((9472, 528), 11), ((20000, 2048), 16),
+                                         ((9999, 1536), 13), ((19000, 512), 33)])
 def test_gemv_multi_vs_oracle_and_single_gemv(fb, c_oracle, mode, shape, batch):
     """B vectors in one pass: every out[b] against the f64 oracle, and against
     the single-vector GEMV -- bit for bit where both take FP32-FMA kernels with
@@ -939,6 +940,30 @@ def test_gemv_multi_vs_oracle_and_single_gemv(fb, c_oracle, mode, shape, batch):
     out = torch.zeros(batch, M, device="cuda")
     fb.gemv_fp8_multi_acc_fp32_gpu(mw, vw, (M, N), mode, batch=batch, out=out, static_matrix=True)
     assert torch.equal(out, Y)
+
+
+def test_gemv_multi_e5m2_kernels_agree(fb):
+    """Large E5M2 matrices with rows of a multiple of 512 codes take the tcgen05 kernel (16
+    vectors per pass); the mma.sync kernel beside it (8 per pass) gives the same sums to
+    rounding, and both are within the bound of the float64 result."""
+    M, N, B = 16384, 16384, 16
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    mw = fb.pack_fp8_tensor(torch.randn(M, N, device="cuda", generator=gen, dtype=torch.float16), "E5M2")
+    vw = fb.pack_fp8_tensor(torch.randn(B, N, device="cuda", generator=gen, dtype=torch.float16), "E5M2")
+    lib = fb._lib.load()
+    try:
+        assert lib.feather_set_tuning(b"multi_tc=0") == 0
+        a = fb.gemv_fp8_multi_acc_fp32_gpu(mw, vw, (M, N), "E5M2")
+    finally:
+        assert lib.feather_set_tuning(b"multi_tc=1") == 0
+    b = fb.gemv_fp8_multi_acc_fp32_gpu(mw, vw, (M, N), "E5M2")
+    fb.device_status()
+    assert O.normalised_error(b.cpu().numpy(), a.cpu().numpy()) < 1e-5
+    A = fb.unpack_fp8_tensor(mw, "E5M2").reshape(M, N).double()
+    V = fb.unpack_fp8_tensor(vw, "E5M2").reshape(B, N).double()
+    exact = (A @ V.T).T.cpu().numpy()
+    assert O.normalised_error(b.cpu().numpy(), exact) < 5e-6
+    assert O.normalised_error(a.cpu().numpy(), exact) < 5e-6
 
 
 def test_gemv_multi_rejects(fb):
