@@ -606,8 +606,10 @@ def run_ours(args) -> None:
         # several vectors in one pass over the matrix (feather_gemv_fp8_multi), both
         # formats; "matrix_GB/s" counts the matrix once, "vs_single_calls" is batch x
         # the single-vector time of this run divided by the multi-vector time
+        # (E5M2 at this shape takes the tcgen05 kernel, 16 vectors per pass; E4M3 the mma.sync
+        # kernel, 8 per pass)
         for name, mset, mmode, single_ms in (("e4m3", m4, "E4M3", ms4), ("e5m2", mats, mode, kern_ms)):
-            for nb in (4, 8):
+            for nb in (4, 8, 16):
                 gen.manual_seed(21)
                 Vn = fb.pack_fp8_tensor(torch.randn(nb, N, device=dev, generator=gen, dtype=torch.float16),
                                         mmode)

@@ -445,6 +445,9 @@ int feather_gemv_chain_fp8_tp(const void* plan, int32_t n_ops, uint32_t flags, i
  *   dot_pre_kb=K        as ring_pre_kb, for the dot ring kernel
  *   dot_unroll=1|2|4    16-byte loads per operand a dot thread keeps in flight
  *   dot_ctas_per_sm=C   dot grid in CTAs per SM (1 .. 16)
+ *   multi_tc=0|1        E5M2 GEMV against several vectors, large matrices with rows of
+ *                       a multiple of 512 codes: 1 (default) the tcgen05 kernel, 16
+ *                       vectors per pass; 0 the mma.sync kernel, 8 per pass
  *   attn_tc=0|1|2       attention on rows of 32 .. 512 codes: 0 the register-fed
  *                       mma.sync kernel, 1 (default) the tcgen05 kernel from 4096 /
  *                       2560 / 512 / 256 / 256 queries up, 2 the tcgen05 kernel for
