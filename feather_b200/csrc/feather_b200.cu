@@ -39,7 +39,7 @@ namespace feather {
 //                    bulk-copy ring kernel with 6 x 32 KiB, 3 x 64 KiB or 12 x 16 KiB stages
 //   dot_pre_kb       KiB the dot ring kernel asks L2 for ahead of its stream-order wait
 //   attn_tc          attention with 32 .. 512 codes per row: 0 the register-fed mma.sync
-//                    kernel, 1 the tcgen05 kernel from 4096 / 2560 / 512 / 256 / 256 queries
+//                    kernel, 1 the tcgen05 kernel from 1024 / 1024 / 256 / 128 / 128 queries
 //                    up, 2 the tcgen05 kernel always
 //   multi_tc         E5M2 GEMV against several vectors, large matrices with rows of a multiple of
 //                    128 codes: 1 the tcgen05 kernel (16 vectors per pass), 0 the mma.sync kernel
@@ -682,7 +682,7 @@ static int attention_any(const uint32_t* q, const uint32_t* k, const uint32_t* v
     const int tc = g_tune.attn_tc.load(std::memory_order_relaxed);
     // Measured on B200: below these lengths the register-fed kernel (16 queries per CTA, no
     // cluster, no tensor-memory allocation) is as fast or faster.
-    constexpr long long kFrom = D >= 256 ? 256 : D >= 128 ? 512 : D >= 64 ? 2560 : 4096;
+    constexpr long long kFrom = D >= 256 ? 128 : D >= 128 ? 256 : 1024;
     // the grid's second dimension is at most 65535; the tensor maps want 16-byte alignment
     if (tc && (tc == 2 || seq_len >= kFrom) && seq_len <= 32767ll * kAtcRows && aligned(q, 16) &&
         aligned(k, 16) && aligned(v, 16))

@@ -449,8 +449,8 @@ int feather_gemv_chain_fp8_tp(const void* plan, int32_t n_ops, uint32_t flags, i
  *                       a multiple of 512 codes: 1 (default) the tcgen05 kernel, 16
  *                       vectors per pass; 0 the mma.sync kernel, 8 per pass
  *   attn_tc=0|1|2       attention on rows of 32 .. 512 codes: 0 the register-fed
- *                       mma.sync kernel, 1 (default) the tcgen05 kernel from 4096 /
- *                       2560 / 512 / 256 / 256 queries up, 2 the tcgen05 kernel for
+ *                       mma.sync kernel, 1 (default) the tcgen05 kernel from 1024 /
+ *                       1024 / 256 / 128 / 128 queries up, 2 the tcgen05 kernel for
  *                       every length
  * The environment variable FEATHER_KERNEL, if set, is applied once with the
  * same syntax when the library first touches a device.  Process-wide, takes
