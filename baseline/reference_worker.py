@@ -69,6 +69,22 @@ def parity(args) -> dict:
     for name in args.cases.split(","):
         t0 = time.time()
         a, b, mode = W.make(name, "cuda")
+        if W.is_attention(name):
+            # feather/routines/attention.py:110-179 on the reference packer's words of q, k, v
+            from feather.routines import attention as A
+            seq, d = a[0].shape
+            words = [P.pack_fp8_tensor(t, mode=mode) for t in a]
+            dev = [w.view(torch.uint32).to("cuda") for w in words]
+            rec = {"q_sha": _sha(words[0].numpy().view(np.uint32)), "k_sha": _sha(words[1].numpy().view(np.uint32)),
+                   "v_sha": _sha(words[2].numpy().view(np.uint32))}
+            try:
+                rec["out"] = A.flash_attention_fp8_e5m2_acc_fp32_gpu(dev[0], dev[1], dev[2], seq, d // 4).cpu().numpy()
+                torch.cuda.synchronize()
+            except Exception as e:      # e.g. the kernel's tiles do not fit this GPU
+                rec["failed"] = type(e).__name__ + ": " + str(e)[:300]
+            np.savez(os.path.join(args.outdir, name + ".npz"), **rec)
+            done[name] = {"seconds": round(time.time() - t0, 2), "failed": "failed" in rec}
+            continue
         aw = P.pack_fp8_tensor(a, mode=mode)          # CPU uint32, feather/packers/fp8.py:260
         bw = P.pack_fp8_tensor(b, mode=mode)
         t_pack = time.time() - t0

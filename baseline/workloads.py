@@ -23,6 +23,13 @@ CASES = {
     # feather/benchmark/bench_dot.py:15
     "dot_e5m2_1500000": ("dot", 1_500_000, 33, "E5M2"),
     "dot_e5m2_10000": ("dot", 10_000, 34, "E5M2"),
+    # feather/benchmark/bench_attention.py:14-15: sequence lengths up to 8192, widths 64, 256, 512
+    # (plus 128, and a length that leaves the last key tile ragged)
+    "attn_s4096_d128": ("attn", (4096, 128), 60, "E5M2"),
+    "attn_s8192_d64": ("attn", (8192, 64), 61, "E5M2"),
+    "attn_s4096_d256": ("attn", (4096, 256), 62, "E5M2"),
+    "attn_s2500_d64": ("attn", (2500, 64), 63, "E5M2"),
+    "attn_s1024_d512": ("attn", (1024, 512), 64, "E5M2"),
 }
 
 
@@ -41,9 +48,13 @@ def c3_matrix(shape, gen: torch.Generator, device) -> torch.Tensor:
 
 
 def make(name: str, device="cuda"):
-    """Returns (A, v, mode) for a GEMV case or (x1, x2, mode) for a dot case."""
+    """Returns (A, v, mode) for a GEMV case, (x1, x2, mode) for a dot case, ((q, k, v), None,
+    mode) for an attention case."""
     kind, shape, seed, mode = CASES[name]
     gen = torch.Generator(device=device).manual_seed(seed)
+    if kind == "attn":
+        return (tuple(torch.randn(*shape, device=device, generator=gen, dtype=torch.float16) for _ in range(3)),
+                None, mode)
     if kind == "n01":
         M, N = shape
         return (torch.randn(M, N, device=device, generator=gen, dtype=torch.float16),
@@ -63,3 +74,7 @@ def make(name: str, device="cuda"):
 
 def is_dot(name: str) -> bool:
     return CASES[name][0] == "dot"
+
+
+def is_attention(name: str) -> bool:
+    return CASES[name][0] == "attn"

@@ -4,7 +4,8 @@ The reference package, installed unmodified under baseline/_ref by
 baseline/install_reference.sh, runs in a process of its own
 (baseline/reference_worker.py): its packer (feather/packers/fp8.py:260-281)
 packs the seeded workload, its Triton kernels (feather/routines/gemv.py:136-235,
-feather/routines/dot.py:220-260) compute on those words.  This process
+feather/routines/dot.py:220-260, feather/routines/attention.py:110-179) compute on
+those words.  This process
 generates the same workload from the same seed, packs it with the CUDA encoder
 and runs the CUDA kernels through the C ABI:
 
@@ -13,7 +14,9 @@ and runs the CUDA kernels through the C ABI:
 * GEMV results must agree within 1e-5 of the result's scale (FP32 accumulation,
   order-dependent -- the tolerance the path is specified with); dot likewise,
   the scale being sum |a_i * b_i| (the reference's own float atomics already
-  make its last bits vary from run to run).
+  make its last bits vary from run to run);
+* attention results (both CUDA kernels) must agree with the reference kernel's within 5e-4
+  of the result's scale, the tolerance of the fixtures (probabilities rounded to FP16).
 
 Skipped when the reference install or Triton is not there.
 """
@@ -36,6 +39,7 @@ WORKER = os.path.join(ROOT, "baseline", "reference_worker.py")
 GEMV_CASES = ["c1_e5m2_4096", "c1_e4m3_4096", "c2_e5m2_16384", "c3_e4m3_8192x8192",
               "c3_e4m3_16384x8192", "c3_e4m3_16384x16384"] + [n for n in W.CASES if n.startswith("int_")]
 DOT_CASES = ["dot_e5m2_2pow26", "dot_e5m2_1500000", "dot_e5m2_10000"]
+ATTENTION_CASES = [n for n in W.CASES if n.startswith("attn_")]
 
 
 def run_worker(*argv, timeout=1500):
@@ -52,7 +56,7 @@ def reference_results(tmp_path_factory):
     if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "feather", "routines")):
         pytest.skip("baseline/_ref is not installed (baseline/install_reference.sh)")
     out = tmp_path_factory.mktemp("reference")
-    res = run_worker("parity", "--cases", ",".join(GEMV_CASES + DOT_CASES), "--outdir", str(out))
+    res = run_worker("parity", "--cases", ",".join(GEMV_CASES + DOT_CASES + ATTENTION_CASES), "--outdir", str(out))
     if "unavailable" in res:
         pytest.skip("the reference cannot run here: " + res["unavailable"])
     return lambda name: np.load(os.path.join(str(out), name + ".npz"))
@@ -116,4 +120,29 @@ def test_dot_against_the_reference_kernel(fb, reference_results, case):
     for r in ref["out"]:   # two runs of the reference (atomics: not bit-stable)
         assert abs(got - float(r)) / scale < TOL
     assert fb.dot_fp8_e5m2_acc_fp32_gpu(aw, bw).item() == got
+    fb.device_status()
+
+
+@pytest.mark.parametrize("case", ATTENTION_CASES)
+def test_attention_full_size_against_the_reference_kernel(fb, reference_results, case):
+    from feather_b200.routines.attention import flash_attention_fp8_e5m2_acc_fp32_gpu as attn
+    ref = reference_results(case)
+    (q, k, v), _, mode = W.make(case, "cuda")
+    seq, d = q.shape
+    packed = [fb.pack_fp8_tensor(t, mode) for t in (q, k, v)]
+    for words, key in zip(packed, "qkv"):
+        assert sha(host_words(words)) == str(ref[key + "_sha"]), "packed buffer differs from the reference packer's"
+    if "failed" in ref.files:
+        pytest.skip("the reference kernel does not run this shape here: " + str(ref["failed"])[:120])
+    y_ref = ref["out"]
+    assert np.isfinite(y_ref).all()
+    lib = fb._lib.load()
+    for knob in (b"attn_tc=2", b"attn_tc=0"):        # the tcgen05 kernel, the mma.sync kernel
+        assert lib.feather_set_tuning(knob) == 0
+        try:
+            y = attn(*packed, seq, d // 4).cpu().numpy()
+        finally:
+            assert lib.feather_set_tuning(b"attn_tc=1") == 0
+        err = np.abs(y.astype(np.float64) - y_ref).max() / np.abs(y_ref).max()
+        assert err < 5e-4, f"{case} ({knob.decode()}): {err:.3e} of the result's scale away from the reference kernel"
     fb.device_status()
