@@ -189,26 +189,36 @@ __device__ __forceinline__ float4 decode4(uint32_t w) {
     return decode_word_ordered<MODE>(w);  // E5M2: both semantics coincide
 }
 
-// One packed word per thread and step, four steps in flight: the word loads of a
-// warp are one 128-byte line, its float4 stores one 512-byte run.  RELU: the
+// One packed word per thread and step, eight steps in flight: the word loads of a
+// warp are one 128-byte line, its float4 stores one 512-byte run.  Measured on B200, 2^26
+// codes to FP32 (67 MB read, 268 MB written): steps a whole grid apart 62.2 us; consecutive
+// lines per warp, four per trip 58.6 us, eight 55.6 us (16 CTAs per SM) / 54.6 us (32 per
+// SM or one trip per warp), sixteen 55.3 us; 8 CTAs per SM 61 - 63 us.  RELU: the
 // reference's ReLU-on-unpack (feather/routines/activations.py:8-29), max(0, x)
 // with the compiled kernel's semantics of max: a NaN code gives 0, -0 gives +0.
+constexpr int kDecodeLines = 8;   // 128-byte lines of codes a warp takes per trip
 template <int MODE, bool IEEE, bool RELU>
 __global__ void __launch_bounds__(256)
 decode_kernel(const uint32_t* __restrict__ src, float* __restrict__ dst, long long n_elems) {
     const long long n_words = (n_elems + 3) >> 2;
-    const long long stride = (long long)gridDim.x * blockDim.x;
     const bool vec = (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
-    for (long long w0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; w0 < n_words; w0 += 4 * stride) {
-        uint32_t x[4];
+    // A warp takes eight consecutive 128-byte lines of codes per trip (lane l the words l,
+    // l + 32, ... of them) and writes 4 KB of consecutive floats, a CTA 32 KB: long runs per
+    // open DRAM page.
+    const int lane = threadIdx.x & 31;
+    const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    constexpr int U = kDecodeLines;
+    for (long long base = warp * (32 * U); base < n_words; base += warps * (32 * U)) {
+        uint32_t x[U];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const long long w = w0 + u * stride;
+        for (int u = 0; u < U; ++u) {
+            const long long w = base + 32 * u + lane;
             x[u] = w < n_words ? __ldg(src + w) : 0u;
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const long long w = w0 + u * stride;
+        for (int u = 0; u < U; ++u) {
+            const long long w = base + 32 * u + lane;
             if (w >= n_words) break;
             float4 f = decode4<MODE, IEEE>(x[u]);
             if (RELU) f = make_float4(fmaxf(0.f, f.x), fmaxf(0.f, f.y), fmaxf(0.f, f.z), fmaxf(0.f, f.w));
@@ -690,13 +700,13 @@ static int attention_any(const uint32_t* q, const uint32_t* k, const uint32_t* v
     return attention_launch<D>(q, k, v, out, seq_len, dev, s);
 }
 
-// Decode (optionally through ReLU) n_elems codes: a grid of up to 16 CTAs per SM,
-// each thread walking words with four loads in flight.
+// Decode (optionally through ReLU) n_elems codes: a grid of up to 32 CTAs per SM,
+// each warp walking runs of eight 128-byte lines.
 static int decode_launch(const uint32_t* src, float* dst, long long n_elems, int mode, bool ieee,
                          bool relu, const DeviceInfo& dev, cudaStream_t s) {
     const long long n_words = (n_elems + 3) / 4;
-    long long blocks = (n_words + 4 * 256 - 1) / (4 * 256);
-    const long long cap = (long long)dev.sm_count * 16;
+    long long blocks = (n_words + kDecodeLines * 256 - 1) / (kDecodeLines * 256);
+    const long long cap = (long long)dev.sm_count * 32;
     if (blocks > cap) blocks = cap;
     const unsigned g = (unsigned)blocks;
     if (mode == FEATHER_MODE_E5M2) {
